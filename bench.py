@@ -1,0 +1,435 @@
+#!/usr/bin/env python
+"""Benchmark of the TurboQuant KV-cache hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE config 1): decode attention of one long sequence shaped like a
+hybrid model's full-attention layer - head_dim 256, 4 kv heads, 16 query heads,
+32768 compressed tokens (3-bit keys, 2-bit values), bf16, plus an exact bf16 ring
+of up to 128 recent tokens.  A step = append one new token through the store
+path (ring write; a full ring is compressed into the store as one 128-token
+chunk) + one decode-attention call.  The steps rotate over 8 independent layers
+so that the bytes touched between two visits of a layer (8 x 25.8 MB) exceed the
+126 MB L2: every step streams its compressed history from HBM.
+
+`value` is KV tokens attended per second with everything resident in HBM (steps
+replayed from CUDA graphs); `e2e` is the same metric through the Python API with
+host buffers, H2D/D2H copies inside the timed region.  With N > 1 every rank runs
+its own sequences (weak scaling, no data-path collective) and the time is the max
+over ranks.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WL = dict(name="config1: decode D=256 Hkv=4 Hq=16 N=32768 ring=128 key3b/val2b bf16",
+          D=256, H=4, Qh=16, N=32768, ring=128, key_bits=3, value_bits=2, layers=8)
+METRIC = "decode_attention_kv_tokens_per_s"
+UNIT = "tokens/s"
+N_NEW = 256  # distinct new tokens / queries per layer, reused cyclically
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the GPU works."""
+
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def start(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# --------------------------------------------------------------------------------------
+# CUDA arm
+# --------------------------------------------------------------------------------------
+
+class Layer:
+    """One layer's compressed store, exact ring and synthetic token stream."""
+
+    def __init__(self, idx: int, rank: int, dev):
+        from turboquant_b200 import CompressedKVStore
+        w = WL
+        self.store = CompressedKVStore(w["D"], w["H"], w["key_bits"], w["value_bits"], device=dev, layer_idx=idx,
+                                       capacity_tokens=w["N"] + 64 * w["ring"])
+        g = torch.Generator(device=dev)
+        g.manual_seed(1001 + 97 * rank + idx)
+        ch = torch.exp(0.5 * torch.randn(w["D"], generator=g, device=dev))
+        shape = (w["H"], w["D"])
+        for pos in range(0, w["N"], 8192):
+            n = min(8192, w["N"] - pos)
+            k = (torch.randn(n, *shape, generator=g, device=dev) * ch).to(torch.bfloat16)
+            v = torch.randn(n, *shape, generator=g, device=dev).to(torch.bfloat16)
+            self.store.append_chunk(k, v)
+        self.new_k = (torch.randn(N_NEW, *shape, generator=g, device=dev) * ch).to(torch.bfloat16)
+        self.new_v = torch.randn(N_NEW, *shape, generator=g, device=dev).to(torch.bfloat16)
+        self.query = torch.randn(N_NEW, 1, w["Qh"], w["D"], generator=g, device=dev).to(torch.bfloat16)
+        self.ring_k = (torch.randn(w["ring"], *shape, generator=g, device=dev) * ch).to(torch.bfloat16)
+        self.ring_v = torch.randn(w["ring"], *shape, generator=g, device=dev).to(torch.bfloat16)
+        # staggered fill so that ring flushes are spread over the run at their natural rate
+        self.ring_pos = w["ring"] - 16 * idx
+        self.ring_len = torch.full((1,), self.ring_pos, dtype=torch.int32, device=dev)
+        self.out = torch.empty(1, w["Qh"], w["D"], dtype=torch.bfloat16, device=dev)
+        self.steps = 0
+
+
+class Runner:
+    def __init__(self, rank: int, dev):
+        from turboquant_b200 import _engine as E
+        self.E, self.dev = E, dev
+        self.layers = [Layer(i, rank, dev) for i in range(WL["layers"])]
+        self.splits = E.choose_splits(1, WL["H"], WL["N"], E.sm_count(dev))
+        self.launches = 0      # kernels of this library
+        self.tokens = 0        # KV tokens attended
+        self.bytes = 0         # algorithmic bytes of the decode kernel
+
+    def decode(self, L: Layer, q, prepared=False):
+        E, w = self.E, WL
+        E.decode(L.store.consts, L.store.pool, L.store.workspace, q, L.store.block_table.unsqueeze(0),
+                 L.store.seq_len_device, L.store.num_tokens, ring_k=L.ring_k, ring_v=L.ring_v, ring_lens=L.ring_len,
+                 max_ring_len=L.ring_pos, ring_stride_seq=0, ring_stride_token=w["H"] * w["D"],
+                 num_splits=self.splits, out=L.out, query_prepared=prepared)
+        self.launches += 1 if prepared else 2
+        self.tokens += L.store.num_tokens + L.ring_pos
+        self.bytes += self.decode_bytes(L)
+
+    @staticmethod
+    def decode_bytes(L: Layer) -> int:
+        w = WL
+        return L.store.memory_bytes() + L.ring_pos * w["H"] * w["D"] * 2 * 2
+
+    def step(self, s: int):
+        """Global step s: layer s % L appends a token and decodes."""
+        w = WL
+        L = self.layers[s % w["layers"]]
+        i = L.steps % N_NEW
+        if L.ring_pos >= w["ring"]:                      # ring full: compress it as one chunk
+            L.store.append_chunk(L.ring_k, L.ring_v)
+            self.launches += 1
+            L.ring_pos = 0
+        L.ring_k[L.ring_pos].copy_(L.new_k[i])
+        L.ring_v[L.ring_pos].copy_(L.new_v[i])
+        L.ring_pos += 1
+        L.ring_len.fill_(L.ring_pos)
+        self.decode(L, L.query[i])
+        L.steps += 1
+
+    def capture(self, first: int, count: int, chunk: int = 256):
+        """CUDA graphs replaying steps [first, first+count); host state advances now."""
+        graphs = []
+        s = first
+        while s < first + count:
+            n = min(chunk, first + count - s)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for j in range(s, s + n):
+                    self.step(j)
+            graphs.append(g)
+            s += n
+        return graphs
+
+
+def _dist():
+    ws = int(os.environ.get("WORLD_SIZE", "1"))
+    if ws > 1:
+        import torch.distributed as dist
+        if not dist.is_initialized():
+            dist.init_process_group("nccl", device_id=torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
+        return dist, dist.get_rank(), ws
+    return None, 0, 1
+
+
+def measure_store(dev):
+    """Store path on a config-3 chunk: 8192 tokens x 8 kv heads x 128, bf16, 3b keys / 2b values."""
+    from turboquant_b200 import CompressedKVStore
+    t, h, d = 8192, 8, 128
+    st = CompressedKVStore(d, h, 3, 2, device=dev, capacity_tokens=8 * t)
+    g = torch.Generator(device=dev)
+    g.manual_seed(3)
+    ks = [(torch.randn(t, h, d, generator=g, device=dev)).to(torch.bfloat16) for _ in range(4)]
+    vs = [torch.randn(t, h, d, generator=g, device=dev).to(torch.bfloat16) for _ in range(4)]
+    st.append_chunk(ks[0], vs[0])
+    st.reset()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(4):
+        st.append_chunk(ks[i], vs[i])
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / 4
+    nbytes = t * h * (2 * d * 2 + st.consts.bytes_per_token)
+    return {"workload": "config3 chunk: 8192 tok x 8 heads x 128 bf16, key3b/val2b", "ms_per_chunk": ms,
+            "gbs": nbytes / ms / 1e6, "token_heads_per_s": t * h / ms * 1e3}
+
+
+def cpu_baseline(steps: int, warmup: int, n_hist: int):
+    """The oracle (a torch-CPU restatement of the reference's path) on the host cores."""
+    from oracle import tq_oracle as O
+    from turboquant_b200.codebook import get_codebook_tensors
+    w = WL
+    cent, bnd = get_codebook_tensors(w["D"], w["key_bits"] - 1, "cpu")
+    st = O.OracleStore(w["D"], w["H"], w["key_bits"], w["value_bits"], cent, bnd, layer_idx=0)
+    k, v = O.synth_kv(n_hist + w["ring"] + steps + warmup + 1, w["H"], w["D"], seed=1001, dtype=torch.bfloat16)
+    q = O.synth_query(steps + warmup + 1, w["Qh"], w["D"], seed=7, dtype=torch.bfloat16)
+    t0 = time.perf_counter()
+    for pos in range(0, n_hist, 8192):
+        st.append_chunk(k[pos:pos + 8192][: n_hist - pos], v[pos:pos + 8192][: n_hist - pos])
+    store_s = time.perf_counter() - t0
+    ring_k, ring_v = [k[n_hist:n_hist + w["ring"]]], [v[n_hist:n_hist + w["ring"]]]
+    ring_n = w["ring"]
+    tokens, t_start = 0, None
+    for s in range(warmup + steps):
+        if s == warmup:
+            t_start, tokens = time.perf_counter(), 0
+        if ring_n >= w["ring"]:      # flush the ring as one chunk (capture.py:89-96)
+            st.append_chunk(torch.cat(ring_k), torch.cat(ring_v))
+            ring_k, ring_v, ring_n = [], [], 0
+        i = n_hist + w["ring"] + s
+        ring_k.append(k[i:i + 1])
+        ring_v.append(v[i:i + 1])
+        ring_n += 1
+        flat = st.get_flat_cache()
+        O.hybrid_attention(q[s:s + 1], flat, torch.cat(ring_k), torch.cat(ring_v), w["H"], st.pi, st.s, cent)
+        tokens += flat.num_tokens + ring_n
+    dt = time.perf_counter() - t_start
+    return {"value": tokens / dt, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{steps} full decode steps over {n_hist} compressed tokens + ring on the host CPU "
+                      f"(torch {torch.__version__}); store of the history took {store_s:.2f} s "
+                      f"= {n_hist * w['H'] / store_s:.0f} token-heads/s",
+            "ms_per_step": dt / steps * 1e3}
+
+
+def run_reference(args):
+    if int(os.environ.get("RANK", "0")) != 0:   # under torchrun only rank 0 measures the host CPU
+        return
+    n_hist = WL["N"] if args.steps <= 100 else 8192
+    base = cpu_baseline(args.steps, args.warmup, n_hist)
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WL["name"], "history_tokens_per_step": n_hist,
+                       "note": "reference path = dequantise all history to fp32, then einsum/softmax/einsum on CPU"},
+            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def run_ours(args):
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this path has no CPU fallback")
+    dist, rank, world = _dist()
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    w = WL
+    sampler = ClockSampler(local)
+
+    runner = Runner(rank, dev)
+    nl = w["layers"]
+    for s in range(nl):                      # eager pass: sizes workspaces, sets kernel attributes
+        runner.step(s)
+    torch.cuda.synchronize()
+    warm = runner.capture(nl, args.warmup)
+    runner.launches = runner.tokens = runner.bytes = 0
+    timed = runner.capture(nl + args.warmup, args.steps)
+    launches, tokens, dec_bytes = runner.launches, runner.tokens, runner.bytes
+
+    sampler.start()
+    for g in warm:
+        g.replay()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for g in timed:
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    agg_tokens = tokens
+    if dist is not None:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        tk = torch.tensor([float(tokens)], device=dev, dtype=torch.float64)
+        dist.all_reduce(tk)
+        agg_tokens = float(tk.item())
+    status = max(L.store.workspace.status() for L in runner.layers)
+
+    # ---- roofline of the decode kernel: decode-only launches, queries already prepared ----
+    reps = 8
+    for L in runner.layers:
+        runner.decode(L, L.query[0])
+    runner.bytes = 0
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for r in range(reps):
+            for L in runner.layers:
+                runner.decode(L, L.query[0], prepared=True)
+    bytes_per_launch = runner.bytes / (reps * nl)
+    g.replay()
+    torch.cuda.synchronize()
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0.record()
+    for _ in range(5):
+        g.replay()
+    k1.record()
+    torch.cuda.synchronize()
+    kern_ms = k0.elapsed_time(k1) / (5 * reps * nl)
+    peak, peak_kind = _peaks()
+    achieved = bytes_per_launch / kern_ms / 1e6
+
+    # ---- end to end through the Python API with host buffers ----
+    from turboquant_b200 import KVCaptureEngine, compute_hybrid_attention
+    e2e_steps = max(8, min(args.steps, 256))
+    engines = []
+    for L in runner.layers:
+        eng = KVCaptureEngine(L.store, ring_capacity=w["ring"], device=dev)
+        eng.ring.write(L.ring_k[:L.ring_pos], L.ring_v[:L.ring_pos], L.ring_pos)
+        engines.append(eng)
+    hk = torch.randn(N_NEW, 1, w["H"], w["D"]).to(torch.bfloat16).pin_memory()
+    hv = torch.randn(N_NEW, 1, w["H"], w["D"]).to(torch.bfloat16).pin_memory()
+    hq = torch.randn(N_NEW, 1, w["Qh"], w["D"]).to(torch.bfloat16).pin_memory()
+    hout = torch.empty(1, w["Qh"], w["D"], dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step(s):
+        eng = engines[s % nl]
+        i = s % N_NEW
+        k = hk[i].to(dev, non_blocking=True)
+        v = hv[i].to(dev, non_blocking=True)
+        q = hq[i].to(dev, non_blocking=True)
+        eng.ingest_decode(k, v, 1)
+        rk, rv = eng.ring.peek()
+        out = compute_hybrid_attention(q, eng.store, rk, rv, w["Qh"])
+        hout.copy_(out, non_blocking=True)
+        return eng.total_tokens
+
+    for s in range(nl):
+        e2e_step(s)
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    e2e_tokens = 0
+    t0 = time.perf_counter()
+    for s in range(nl, nl + e2e_steps):
+        e2e_tokens += e2e_step(s)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if dist is not None:
+        t = torch.tensor([e2e_s], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+        tk = torch.tensor([float(e2e_tokens)], device=dev, dtype=torch.float64)
+        dist.all_reduce(tk)
+        e2e_tokens = float(tk.item())
+    clocks = sampler.stop()
+
+    store = measure_store(dev) if rank == 0 else None
+    base = cpu_baseline(3, 1, w["N"]) if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": agg_tokens / ms * 1e3, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": w["name"], "layers_rotating": nl,
+                       "l2": "inputs larger than L2: 8 layers x 25.8 MB compressed history visited round-robin",
+                       "splits_per_kv_head": runner.splits, "steps_replayed_from": "CUDA graphs",
+                       "parallelism": f"dp{world} (independent sequences per GPU, no collective on the data path)"},
+            "hbm_gbs": dec_bytes / ms / 1e6 * world,
+            "roofline": {"bound": "hbm", "kernel": "tq_decode_kernel", "achieved": achieved, "peak": peak,
+                         "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
+                         "frac_of_nominal_8TBs": achieved / 8000.0, "us_per_launch": kern_ms * 1e3,
+                         "bytes_per_launch": bytes_per_launch, "traffic": None},
+            "e2e": {"value": e2e_tokens / e2e_s, "unit": UNIT, "steps": e2e_steps,
+                    "ms_per_step": e2e_s / e2e_steps * 1e3,
+                    "h2d_bytes_per_step": (2 * w["H"] + w["Qh"]) * w["D"] * 2,
+                    "d2h_bytes_per_step": w["Qh"] * w["D"] * 2},
+            "gpu_launches": launches, "device_status": status, "clocks": clocks, "store": store,
+        }
+        if base is not None:
+            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=512)
+    ap.add_argument("--warmup", type=int, default=16)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,133 @@
+"""Write path in front of the store: a ring of exact recent tokens and the
+engine that decides when to flush it (reference capture.py:21-240).
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .store import CompressedKVStore
+
+
+class RingBuffer:
+    """Fixed-capacity buffer of the most recent tokens, (capacity, H, D).
+
+    Same contract as the reference: `write` returns everything that had to be
+    drained to make room (the whole buffer at once), else None.
+    """
+
+    __slots__ = ("capacity", "num_kv_heads", "head_dim", "device", "dtype", "_k", "_v", "_pos", "_total_written")
+
+    def __init__(self, capacity: int, num_kv_heads: int, head_dim: int, device, dtype: torch.dtype = torch.bfloat16):
+        self.capacity, self.num_kv_heads, self.head_dim = capacity, num_kv_heads, head_dim
+        self.device, self.dtype = device, dtype
+        self._k = torch.zeros(capacity, num_kv_heads, head_dim, device=device, dtype=dtype)
+        self._v = torch.zeros(capacity, num_kv_heads, head_dim, device=device, dtype=dtype)
+        self._pos = 0
+        self._total_written = 0
+
+    @property
+    def size(self) -> int:
+        return self._pos
+
+    @property
+    def is_full(self) -> bool:
+        return self._pos >= self.capacity
+
+    @property
+    def total_written(self) -> int:
+        return self._total_written
+
+    def write(self, key: torch.Tensor, value: torch.Tensor, num_tokens: int):
+        drained_k, drained_v = [], []
+        done = 0
+        while done < num_tokens:
+            if self._pos >= self.capacity:
+                drained_k.append(self._k[: self._pos].clone())
+                drained_v.append(self._v[: self._pos].clone())
+                self._pos = 0
+            n = min(num_tokens - done, self.capacity - self._pos)
+            self._k[self._pos: self._pos + n] = key[done: done + n]
+            self._v[self._pos: self._pos + n] = value[done: done + n]
+            self._pos += n
+            done += n
+        self._total_written += num_tokens
+        if drained_k:
+            return torch.cat(drained_k, 0), torch.cat(drained_v, 0)
+        return None
+
+    def drain(self):
+        if self._pos == 0:
+            return None
+        k, v = self._k[: self._pos].clone(), self._v[: self._pos].clone()
+        self._pos = 0
+        return k, v
+
+    def peek(self):
+        if self._pos == 0:
+            return None
+        return self._k[: self._pos], self._v[: self._pos]
+
+    def reset(self) -> None:
+        self._pos = 0
+        self._total_written = 0
+
+
+class KVCaptureEngine:
+    """Feeds a CompressedKVStore: prefill goes to the store except the last
+    `ring_capacity` tokens, decode tokens go to the ring, a full ring is
+    compressed as one chunk when the next token arrives."""
+
+    def __init__(self, store: CompressedKVStore, ring_capacity: int = 128, device=None,
+                 dtype: torch.dtype = torch.bfloat16):
+        self.store = store
+        self.ring = RingBuffer(ring_capacity, store.num_kv_heads, store.head_dim, device or store.device, dtype)
+        self._prefill_done = False
+
+    @property
+    def total_compressed_tokens(self) -> int:
+        return self.store.num_tokens
+
+    @property
+    def total_buffered_tokens(self) -> int:
+        return self.ring.size
+
+    @property
+    def total_tokens(self) -> int:
+        return self.total_compressed_tokens + self.total_buffered_tokens
+
+    def ingest_prefill(self, key: torch.Tensor, value: torch.Tensor, num_tokens: int) -> None:
+        cap = self.ring.capacity
+        if num_tokens <= cap:
+            self.ring.write(key[:num_tokens], value[:num_tokens], num_tokens)
+        else:
+            n = num_tokens - cap
+            self.store.append_chunk(key[:n], value[:n])
+            self.ring.write(key[n:num_tokens], value[n:num_tokens], cap)
+        self._prefill_done = True
+
+    def ingest_prefill_from_paged_cache(self, kv_cache_tensor: torch.Tensor, num_tokens: int,
+                                        block_table: torch.Tensor, block_size: int) -> None:
+        """kv_cache_tensor (2, num_blocks, block_size, H, D); block_table maps logical to physical blocks."""
+        n_blocks = (num_tokens + block_size - 1) // block_size
+        phys = block_table[:n_blocks].long()
+        k = kv_cache_tensor[0].index_select(0, phys).reshape(-1, *kv_cache_tensor.shape[3:])[:num_tokens]
+        v = kv_cache_tensor[1].index_select(0, phys).reshape(-1, *kv_cache_tensor.shape[3:])[:num_tokens]
+        self.ingest_prefill(k, v, num_tokens)
+
+    def ingest_decode(self, key: torch.Tensor, value: torch.Tensor, num_tokens: int) -> None:
+        overflow = self.ring.write(key[:num_tokens], value[:num_tokens], num_tokens)
+        if overflow is not None:
+            self.store.append_chunk(*overflow)
+
+    def flush(self) -> None:
+        data = self.ring.drain()
+        if data is not None:
+            self.store.append_chunk(*data)
+
+    def reset(self) -> None:
+        self.ring.reset()
+        self.store.reset()
+        self._prefill_done = False

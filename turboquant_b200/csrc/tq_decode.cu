@@ -1,0 +1,732 @@
+// Read path: query preparation, split-sequence decode attention over pool
+// block records plus the exact ring, and the unscaled score kernel.
+//
+// Algebra (reference triton_kernels.py:49-53,138 and quantizer.py:274-302):
+//   <q, k_hat> = norm * <q Pi^T, centroid[idx]> + qjl_scale * rnorm * <q S^T, signs>
+// so the query is rotated once and the keys are never dequantised.
+//
+// One CTA owns one (sequence, kv head, split): it streams its share of the
+// sequence's block records through shared memory with bulk (TMA) copies on a
+// 3-stage mbarrier ring, keeps an online softmax for all G query heads of the
+// kv head and accumulates the dequantised values.  Extra CTAs do the same for
+// the exact ring tokens.  Every CTA writes a partial (m, l, acc); the last one
+// to finish for a (sequence, kv head) - found with an atomic ticket, no
+// waiting - merges the partials and writes the output.
+#include "tq_common.cuh"
+
+namespace {
+
+constexpr int DEC_THREADS = 128;
+constexpr int TILE_BLOCKS = 4;
+constexpr int TILE_TOK = TILE_BLOCKS * TQ_BLOCK_TOKENS;  // 64
+constexpr int NSTAGE = 3;
+constexpr int RING_TOK = 32;  // ring tokens per ring CTA
+
+struct DecodeParams {
+    const uint8_t* pool;
+    int64_t num_blocks;
+    int H, Qh, G;
+    const int32_t* block_table;
+    int bt_stride;
+    const int32_t* seq_lens;
+    int min_history;
+    const float* qprep;  // [B][Qh][2][D] rotated / sketched query
+    const void* query;
+    int q_dtype;
+    const void* ring_k;
+    const void* ring_v;
+    int ring_dtype;
+    const int32_t* ring_lens;
+    int64_t ring_stride_seq, ring_stride_token;
+    float scale, qjl_scale;
+    TqCodebook cb;
+    void* out;
+    float* partials;
+    int32_t* tickets;
+    int32_t* status;
+    int num_splits, ring_splits;
+};
+
+struct ScoreParams {
+    const uint8_t* pool;
+    int64_t num_blocks;
+    int H;
+    const int32_t* block_table;
+    int64_t n_tokens;
+    const float* qprep;  // [H][n_q][2][D]
+    int n_q;
+    float qjl_scale;
+    TqCodebook cb;
+    float* logits;  // [H][n_q][n_tokens]
+    int32_t* status;
+};
+
+// q_rot = q @ Pi^T and q_sketch = q @ S^T for up to 4 query vectors per CTA.
+__global__ void tq_qprep_kernel(const void* __restrict__ q, int dt, int64_t nvec, int D,
+                                const float* __restrict__ pi_t, const float* __restrict__ s_t,
+                                float* __restrict__ out) {
+    extern __shared__ float qsm[];  // [4][D]
+    const int64_t v0 = (int64_t)blockIdx.x * 4;
+    const int nv = (int)min((int64_t)4, nvec - v0);
+    const int j = threadIdx.x;
+    for (int v = 0; v < 4; ++v) qsm[v * D + j] = v < nv ? tq_load_any(q, (v0 + v) * D + j, dt) : 0.f;
+    __syncthreads();
+    float ar[4] = {0.f, 0.f, 0.f, 0.f}, as[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < D; ++k) {
+        const float pv = __ldg(pi_t + (size_t)k * D + j);
+        const float sv = __ldg(s_t + (size_t)k * D + j);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            const float qv = qsm[v * D + k];
+            ar[v] = fmaf(qv, pv, ar[v]);
+            as[v] = fmaf(qv, sv, as[v]);
+        }
+    }
+    for (int v = 0; v < nv; ++v) {
+        out[((v0 + v) * 2 + 0) * D + j] = ar[v];
+        out[((v0 + v) * 2 + 1) * D + j] = as[v];
+    }
+}
+
+// Partial logits of one token over dims [dim0, dim0 + D/2) for GP query heads.
+template <int D, int MSE_BITS, int GP>
+__device__ __forceinline__ void token_half_scores(const uint8_t* rec, const TqLayout& L, int tl, int half,
+                                                  const float* __restrict__ qr, const float* __restrict__ qs,
+                                                  const float* __restrict__ cent, float qjl_scale, float (&out)[GP]) {
+    constexpr int WIDTH = MSE_BITS == 2 ? 2 : 4;
+    constexpr int DIMS_PER_CW = 32 / WIDTH;       // dims per 32-bit code word
+    constexpr int CW_PER_SW = 32 / DIMS_PER_CW;   // code words per 32-bit sign word
+    constexpr uint32_t MASK = (1u << WIDTH) - 1u;
+    const uint32_t* cw = reinterpret_cast<const uint32_t*>(rec + L.off_kcodes + tl * L.kcode_row) + half * (D / 2) / DIMS_PER_CW;
+    const uint32_t* sw = reinterpret_cast<const uint32_t*>(rec + L.off_ksigns + tl * L.ksign_row) + half * (D / 64);
+    float am[GP], aq[GP];
+#pragma unroll
+    for (int g = 0; g < GP; ++g) am[g] = aq[g] = 0.f;
+    int j = half * (D / 2);
+#pragma unroll 1
+    for (int s = 0; s < D / 64; ++s) {
+        uint32_t sg = sw[s];
+#pragma unroll
+        for (int c = 0; c < CW_PER_SW; ++c) {
+            uint32_t w = cw[s * CW_PER_SW + c];
+#pragma unroll 4
+            for (int i = 0; i < DIMS_PER_CW; ++i, ++j) {
+                const float cv = cent[w & MASK];
+                w >>= WIDTH;
+                const float sv = (sg & 1u) ? 1.f : -1.f;
+                sg >>= 1;
+                const float* qrj = qr + j * GP;
+                const float* qsj = qs + j * GP;
+#pragma unroll
+                for (int g4 = 0; g4 < GP / 4; ++g4) {
+                    const float4 a = *reinterpret_cast<const float4*>(qrj + 4 * g4);
+                    const float4 b = *reinterpret_cast<const float4*>(qsj + 4 * g4);
+                    am[4 * g4 + 0] = fmaf(a.x, cv, am[4 * g4 + 0]);
+                    am[4 * g4 + 1] = fmaf(a.y, cv, am[4 * g4 + 1]);
+                    am[4 * g4 + 2] = fmaf(a.z, cv, am[4 * g4 + 2]);
+                    am[4 * g4 + 3] = fmaf(a.w, cv, am[4 * g4 + 3]);
+                    aq[4 * g4 + 0] = fmaf(b.x, sv, aq[4 * g4 + 0]);
+                    aq[4 * g4 + 1] = fmaf(b.y, sv, aq[4 * g4 + 1]);
+                    aq[4 * g4 + 2] = fmaf(b.z, sv, aq[4 * g4 + 2]);
+                    aq[4 * g4 + 3] = fmaf(b.w, sv, aq[4 * g4 + 3]);
+                }
+            }
+        }
+    }
+    const float norm = __half2float(reinterpret_cast<const __half*>(rec + L.off_knorm)[tl]);
+    const float rn = __half2float(reinterpret_cast<const __half*>(rec + L.off_krnorm)[tl]) * qjl_scale;
+#pragma unroll
+    for (int g = 0; g < GP; ++g) out[g] = norm * am[g] + rn * aq[g];
+}
+
+// Issue the bulk copies of one tile (up to 4 block records) into a stage.
+__device__ __forceinline__ void issue_tile(uint8_t* stage, uint64_t* bar, const uint8_t* pool, int64_t num_blocks,
+                                           const int32_t* bt, int first_blk, int nblk_total, int H, int h,
+                                           int block_bytes, int32_t* status) {
+    const int nb = min(TILE_BLOCKS, nblk_total - first_blk);
+    tq_mbar_expect_tx(bar, (uint32_t)(nb * block_bytes));
+    for (int i = 0; i < nb; ++i) {
+        int64_t phys = bt[first_blk + i];
+        if (phys < 0 || phys >= num_blocks) {
+            if (status) atomicCAS(status, 0, (int)TQ_ERR_RANGE);
+            phys = 0;
+        }
+        tq_bulk_g2s(stage + i * block_bytes, pool + (phys * H + h) * (int64_t)block_bytes, (uint32_t)block_bytes, bar);
+    }
+}
+
+// Shared by the history and ring parts: store the partial, take a ticket, and
+// let the last CTA of this (sequence, kv head) merge and write the output.
+template <int D, int GP>
+__device__ __forceinline__ void finish_and_merge(const DecodeParams& p, int b, int h, int slot_idx,
+                                                 const float (&acc)[GP][D / DEC_THREADS], const float* m_run,
+                                                 const float* l_run, float* wsm /* [nslot*GP + 2*GP] */) {
+    constexpr int DPT = D / DEC_THREADS;
+    constexpr int PS = GP * (D + 2);
+    const int tid = threadIdx.x;
+    const int nslot = p.num_splits + p.ring_splits;
+    float* mine = p.partials + ((int64_t)(b * p.H + h) * nslot + slot_idx) * PS;
+    if (tid < GP) {
+        mine[tid] = m_run[tid];
+        mine[GP + tid] = l_run[tid];
+    }
+#pragma unroll
+    for (int g = 0; g < GP; ++g)
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) mine[2 * GP + g * D + tid * DPT + i] = acc[g][i];
+    __threadfence();
+    __shared__ int s_last;
+    __syncthreads();
+    if (tid == 0) {
+        const int t = atomicAdd(p.tickets + b * p.H + h, 1);
+        s_last = (t == nslot - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+
+    const float* base = p.partials + (int64_t)(b * p.H + h) * nslot * PS;
+    float* wM = wsm;             // [GP] global max
+    float* wL = wsm + GP;        // [GP] global sum
+    float* w = wsm + 2 * GP;     // [nslot][GP] weight of each partial
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int g = warp; g < GP; g += DEC_THREADS / 32) {
+        float mx = -INFINITY;
+        for (int s = lane; s < nslot; s += 32) mx = fmaxf(mx, __ldcg(base + (int64_t)s * PS + g));
+        mx = tq_warp_max(mx);
+        float sum = 0.f;
+        for (int s = lane; s < nslot; s += 32) {
+            const float ms = __ldcg(base + (int64_t)s * PS + g);
+            const float ls = __ldcg(base + (int64_t)s * PS + GP + g);
+            const float ws = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
+            w[s * GP + g] = ws;
+            sum += ws * ls;
+        }
+        sum = tq_warp_sum(sum);
+        if (lane == 0) {
+            wM[g] = mx;
+            wL[g] = sum;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < p.G * D; i += DEC_THREADS) {
+        const int g = i / D, d = i % D;
+        float o = 0.f;
+        for (int s = 0; s < nslot; ++s) {
+            const float ws = w[s * GP + g];
+            if (ws != 0.f) o = fmaf(ws, __ldcg(base + (int64_t)s * PS + 2 * GP + g * D + d), o);
+        }
+        const float l = wL[g];
+        tq_store_any(p.out, ((int64_t)b * p.Qh + h * p.G + g) * D + d, l > 0.f ? o / l : 0.f, p.q_dtype);
+    }
+    if (tid == 0) p.tickets[b * p.H + h] = 0;  // ready for the next launch
+}
+
+template <int D, int MSE_BITS, int VAL_BITS, int GP>
+__global__ void __launch_bounds__(DEC_THREADS) tq_decode_kernel(const DecodeParams p) {
+    constexpr int DPT = D / DEC_THREADS;
+    const TqLayout L = tq_make_layout(D, MSE_BITS + 1, VAL_BITS);
+    const int BB = L.block_bytes;
+
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* stages = smem;                                                        // [NSTAGE][4*BB]
+    float* qr = reinterpret_cast<float*>(smem + NSTAGE * TILE_BLOCKS * BB);        // [D][GP]
+    float* qs = qr + D * GP;                                                       // [D][GP]
+    float* sp = qs + D * GP;                                                       // [2][GP][64]
+    float* pp = sp + 2 * GP * TILE_TOK;                                            // [64][GP]
+    float* m_run = pp + TILE_TOK * GP;                                             // [GP]
+    float* l_run = m_run + GP;                                                     // [GP]
+    float* alpha = l_run + GP;                                                     // [GP]
+    float* cent = alpha + GP;                                                      // [16]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(cent + TQ_MAX_CENTROIDS);         // [NSTAGE]
+    float* wsm = reinterpret_cast<float*>(bars + NSTAGE);                          // merge scratch
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int b = blockIdx.z, h = blockIdx.y, x = blockIdx.x;
+
+    float acc[GP][DPT];
+#pragma unroll
+    for (int g = 0; g < GP; ++g)
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) acc[g][i] = 0.f;
+    if (tid < GP) {
+        m_run[tid] = -INFINITY;
+        l_run[tid] = 0.f;
+    }
+    if (tid < TQ_MAX_CENTROIDS) cent[tid] = p.cb.centroids[tid];
+
+    if (x < p.num_splits) {
+        // ------------------------- compressed history -------------------------
+        int n = p.seq_lens[b];
+        if (n < p.min_history) n = 0;
+        const int nblk = (n + TQ_BLOCK_TOKENS - 1) / TQ_BLOCK_TOKENS;
+        const int ntile = (nblk + TILE_BLOCKS - 1) / TILE_BLOCKS;
+        const int tps = (ntile + p.num_splits - 1) / p.num_splits;
+        const int tile0 = x * tps;
+        const int tile1 = min(ntile, tile0 + tps);
+        const int32_t* bt = p.block_table + (int64_t)b * p.bt_stride;
+
+        if (tile0 < tile1) {
+            for (int i = tid; i < D * GP; i += DEC_THREADS) {
+                const int j = i / GP, g = i % GP;
+                float a = 0.f, c = 0.f;
+                if (g < p.G) {
+                    const float* src = p.qprep + ((int64_t)(b * p.Qh + h * p.G + g) * 2) * D;
+                    a = src[j];
+                    c = src[D + j];
+                }
+                qr[i] = a;
+                qs[i] = c;
+            }
+            if (tid == 0) {
+                for (int s = 0; s < NSTAGE; ++s) tq_mbar_init(bars + s, 1);
+                tq_mbar_fence_init();
+            }
+            __syncthreads();
+            if (tid == 0) {
+                for (int s = 0; s < NSTAGE - 1 && tile0 + s < tile1; ++s)
+                    issue_tile(stages + s * TILE_BLOCKS * BB, bars + s, p.pool, p.num_blocks, bt,
+                               (tile0 + s) * TILE_BLOCKS, nblk, p.H, h, BB, p.status);
+            }
+            for (int tile = tile0; tile < tile1; ++tile) {
+                const int it = tile - tile0, st = it % NSTAGE;
+                if (tid == 0 && tile + NSTAGE - 1 < tile1) {
+                    const int s2 = (it + NSTAGE - 1) % NSTAGE;
+                    issue_tile(stages + s2 * TILE_BLOCKS * BB, bars + s2, p.pool, p.num_blocks, bt,
+                               (tile + NSTAGE - 1) * TILE_BLOCKS, nblk, p.H, h, BB, p.status);
+                }
+                const bool ok = tq_mbar_wait_bounded(bars + st, (uint32_t)((it / NSTAGE) & 1));
+                if (__syncthreads_or(!ok)) {
+                    if (tid == 0) atomicCAS(p.status, 0, (int)TQ_ERR_TIMEOUT);
+                    break;
+                }
+                const uint8_t* stage = stages + st * TILE_BLOCKS * BB;
+                const int tok_base = tile * TILE_TOK;
+                const int valid = min(TILE_TOK, n - tok_base);
+
+                // scores: 2 threads per token, one per half of the head dimension
+                {
+                    const int tk = tid & (TILE_TOK - 1), half = tid >> 6;
+                    float part[GP];
+                    if (tk < valid) {
+                        token_half_scores<D, MSE_BITS, GP>(stage + (tk >> 4) * BB, L, tk & 15, half, qr, qs, cent,
+                                                           p.qjl_scale, part);
+                    } else {
+#pragma unroll
+                        for (int g = 0; g < GP; ++g) part[g] = 0.f;
+                    }
+#pragma unroll
+                    for (int g = 0; g < GP; ++g) sp[(half * GP + g) * TILE_TOK + tk] = part[g];
+                }
+                __syncthreads();
+                // online softmax, one warp per query head
+                for (int g = warp; g < GP; g += DEC_THREADS / 32) {
+                    float s0 = -INFINITY, s1 = -INFINITY;
+                    if (lane < valid) s0 = (sp[g * TILE_TOK + lane] + sp[(GP + g) * TILE_TOK + lane]) * p.scale;
+                    if (lane + 32 < valid)
+                        s1 = (sp[g * TILE_TOK + lane + 32] + sp[(GP + g) * TILE_TOK + lane + 32]) * p.scale;
+                    const float m_old = m_run[g];
+                    const float m_new = fmaxf(m_old, tq_warp_max(fmaxf(s0, s1)));
+                    const float p0 = (s0 == -INFINITY) ? 0.f : __expf(s0 - m_new);
+                    const float p1 = (s1 == -INFINITY) ? 0.f : __expf(s1 - m_new);
+                    const float a = (m_old == -INFINITY) ? 0.f : __expf(m_old - m_new);
+                    const float sum = tq_warp_sum(p0 + p1);
+                    pp[lane * GP + g] = p0;
+                    pp[(lane + 32) * GP + g] = p1;
+                    if (lane == 0) {
+                        m_run[g] = m_new;
+                        l_run[g] = l_run[g] * a + sum;
+                        alpha[g] = a;
+                    }
+                }
+                __syncthreads();
+                // values: each thread owns DPT channels for all query heads
+                {
+#pragma unroll
+                    for (int g = 0; g < GP; ++g) {
+                        const float a = alpha[g];
+#pragma unroll
+                        for (int i = 0; i < DPT; ++i) acc[g][i] *= a;
+                    }
+                    const int d0 = tid * DPT, grp = d0 >> 5;
+                    for (int t = 0; t < valid; ++t) {
+                        const uint8_t* rec = stage + (t >> 4) * BB;
+                        const int tl = t & 15;
+                        const float sc = __half2float(reinterpret_cast<const __half*>(rec + L.off_vscale)[grp * 16 + tl]);
+                        const float zr = __half2float(reinterpret_cast<const __half*>(rec + L.off_vzero)[grp * 16 + tl]);
+                        float v[DPT];
+                        if (VAL_BITS == 2) {
+                            const uint32_t byte = rec[L.off_vcodes + tq_vcode_native(D, 2, tl, d0 >> 2)];
+#pragma unroll
+                            for (int i = 0; i < DPT; ++i) v[i] = fmaf((float)((byte >> (2 * ((d0 + i) & 3))) & 3u), sc, zr);
+                        } else {
+                            const uint32_t byte = rec[L.off_vcodes + tq_vcode_native(D, 4, tl, d0 >> 1)];
+#pragma unroll
+                            for (int i = 0; i < DPT; ++i) v[i] = fmaf((float)((byte >> (4 * ((d0 + i) & 1))) & 15u), sc, zr);
+                        }
+                        const float* pt = pp + t * GP;
+#pragma unroll
+                        for (int g = 0; g < GP; ++g)
+#pragma unroll
+                            for (int i = 0; i < DPT; ++i) acc[g][i] = fmaf(pt[g], v[i], acc[g][i]);
+                    }
+                }
+                __syncthreads();
+            }
+        }
+        __syncthreads();
+        finish_and_merge<D, GP>(p, b, h, x, acc, m_run, l_run, wsm);
+        return;
+    }
+
+    // ------------------------------ exact ring ------------------------------
+    {
+        const int rs = x - p.num_splits;
+        const int R = p.ring_lens ? p.ring_lens[b] : 0;
+        const int r0 = rs * RING_TOK;
+        const int nr = max(0, min(RING_TOK, R - r0));
+        float* qf = qr;                 // [D][GP] raw query
+        float* sc = sp;                 // [GP][RING_TOK]
+        if (nr > 0) {
+            for (int i = tid; i < D * GP; i += DEC_THREADS) {
+                const int j = i / GP, g = i % GP;
+                qf[i] = g < p.G ? tq_load_any(p.query, ((int64_t)b * p.Qh + h * p.G + g) * D + j, p.q_dtype) : 0.f;
+            }
+            __syncthreads();
+            for (int t = warp; t < nr; t += DEC_THREADS / 32) {
+                const int64_t off = (int64_t)b * p.ring_stride_seq + (int64_t)(r0 + t) * p.ring_stride_token + (int64_t)h * D;
+                float a[GP];
+#pragma unroll
+                for (int g = 0; g < GP; ++g) a[g] = 0.f;
+                for (int j = lane; j < D; j += 32) {
+                    const float kx = tq_load_any(p.ring_k, off + j, p.ring_dtype);
+#pragma unroll
+                    for (int g = 0; g < GP; ++g) a[g] = fmaf(qf[j * GP + g], kx, a[g]);
+                }
+#pragma unroll
+                for (int g = 0; g < GP; ++g) {
+                    const float s = tq_warp_sum(a[g]);
+                    if (lane == 0) sc[g * RING_TOK + t] = s * p.scale;
+                }
+            }
+            __syncthreads();
+            for (int g = warp; g < GP; g += DEC_THREADS / 32) {
+                const float s0 = lane < nr ? sc[g * RING_TOK + lane] : -INFINITY;
+                const float m_new = tq_warp_max(s0);
+                const float p0 = (s0 == -INFINITY) ? 0.f : __expf(s0 - m_new);
+                const float sum = tq_warp_sum(p0);
+                pp[lane * GP + g] = p0;
+                if (lane == 0) {
+                    m_run[g] = m_new;
+                    l_run[g] = sum;
+                }
+            }
+            __syncthreads();
+            const int d0 = tid * DPT;
+            for (int t = 0; t < nr; ++t) {
+                const int64_t off = (int64_t)b * p.ring_stride_seq + (int64_t)(r0 + t) * p.ring_stride_token + (int64_t)h * D + d0;
+                float v[DPT];
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) v[i] = tq_load_any(p.ring_v, off + i, p.ring_dtype);
+                const float* pt = pp + t * GP;
+#pragma unroll
+                for (int g = 0; g < GP; ++g)
+#pragma unroll
+                    for (int i = 0; i < DPT; ++i) acc[g][i] = fmaf(pt[g], v[i], acc[g][i]);
+            }
+        }
+        __syncthreads();
+        finish_and_merge<D, GP>(p, b, h, x, acc, m_run, l_run, wsm);
+    }
+}
+
+// Unscaled logits of up to 8 query vectors per CTA against one 64-token tile.
+template <int D, int MSE_BITS>
+__global__ void __launch_bounds__(DEC_THREADS) tq_scores_kernel(const ScoreParams p, int key_bits, int val_bits) {
+    constexpr int GP = 8;
+    const TqLayout L = tq_make_layout(D, key_bits, val_bits);
+    const int BB = L.block_bytes;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* stage = smem;
+    float* qr = reinterpret_cast<float*>(smem + TILE_BLOCKS * BB);
+    float* qs = qr + D * GP;
+    float* sp = qs + D * GP;  // [2][GP][64]
+    float* cent = sp + 2 * GP * TILE_TOK;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(cent + TQ_MAX_CENTROIDS);
+
+    const int tid = threadIdx.x;
+    const int tile = blockIdx.x, h = blockIdx.y, q0 = blockIdx.z * GP;
+    const int nq = min(GP, p.n_q - q0);
+    const int nblk = (int)((p.n_tokens + TQ_BLOCK_TOKENS - 1) / TQ_BLOCK_TOKENS);
+    if (tid < TQ_MAX_CENTROIDS) cent[tid] = p.cb.centroids[tid];
+    for (int i = tid; i < D * GP; i += DEC_THREADS) {
+        const int j = i / GP, g = i % GP;
+        float a = 0.f, c = 0.f;
+        if (g < nq) {
+            const float* src = p.qprep + ((int64_t)(h * p.n_q + q0 + g) * 2) * D;
+            a = src[j];
+            c = src[D + j];
+        }
+        qr[i] = a;
+        qs[i] = c;
+    }
+    if (tid == 0) {
+        tq_mbar_init(bar, 1);
+        tq_mbar_fence_init();
+    }
+    __syncthreads();
+    if (tid == 0)
+        issue_tile(stage, bar, p.pool, p.num_blocks, p.block_table, tile * TILE_BLOCKS, nblk, p.H, h, BB, p.status);
+    const bool ok = tq_mbar_wait_bounded(bar, 0);
+    if (__syncthreads_or(!ok)) {
+        if (tid == 0) atomicCAS(p.status, 0, (int)TQ_ERR_TIMEOUT);
+        return;
+    }
+    const int valid = (int)min((int64_t)TILE_TOK, p.n_tokens - (int64_t)tile * TILE_TOK);
+    const int tk = tid & (TILE_TOK - 1), half = tid >> 6;
+    float part[GP];
+    if (tk < valid) {
+        token_half_scores<D, MSE_BITS, GP>(stage + (tk >> 4) * BB, L, tk & 15, half, qr, qs, cent, p.qjl_scale, part);
+    } else {
+#pragma unroll
+        for (int g = 0; g < GP; ++g) part[g] = 0.f;
+    }
+#pragma unroll
+    for (int g = 0; g < GP; ++g) sp[(half * GP + g) * TILE_TOK + tk] = part[g];
+    __syncthreads();
+    for (int i = tid; i < nq * TILE_TOK; i += DEC_THREADS) {
+        const int g = i / TILE_TOK, t = i % TILE_TOK;
+        if (t < valid)
+            p.logits[((int64_t)h * p.n_q + q0 + g) * p.n_tokens + (int64_t)tile * TILE_TOK + t] =
+                sp[g * TILE_TOK + t] + sp[(GP + g) * TILE_TOK + t];
+    }
+}
+
+template <int D, int GP>
+size_t decode_smem_bytes(int block_bytes, int nslot) {
+    size_t s = (size_t)NSTAGE * TILE_BLOCKS * block_bytes;
+    s += sizeof(float) * (2 * D * GP + 2 * GP * TILE_TOK + TILE_TOK * GP + 3 * GP + TQ_MAX_CENTROIDS);
+    s += sizeof(uint64_t) * NSTAGE;
+    // merge scratch sized for at least 128 partials so that the launch size
+    // (and with it the kernel's shared-memory attribute) rarely changes
+    s += sizeof(float) * ((size_t)(nslot > 128 ? nslot : 128) * GP + 2 * GP);
+    return s;
+}
+
+template <int D, int MSE_BITS, int VAL_BITS, int GP>
+int launch_decode(const DecodeParams& p, int B, int block_bytes, cudaStream_t st) {
+    const int nslot = p.num_splits + p.ring_splits;
+    const size_t smem = decode_smem_bytes<D, GP>(block_bytes, nslot);
+    auto kern = tq_decode_kernel<D, MSE_BITS, VAL_BITS, GP>;
+    // raised once per kernel (and again only if a larger launch needs it), so
+    // that steady-state calls issue nothing but the launch (graph capture)
+    static size_t smem_set = 0;
+    if (smem > smem_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return TQ_ERR_CUDA;
+        smem_set = smem;
+    }
+    dim3 grid((unsigned)nslot, (unsigned)p.H, (unsigned)B);
+    kern<<<grid, DEC_THREADS, smem, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
+}
+
+template <int D, int MSE_BITS, int VAL_BITS>
+int launch_decode_g(const DecodeParams& p, int B, int block_bytes, cudaStream_t st) {
+    if (p.G <= 4) return launch_decode<D, MSE_BITS, VAL_BITS, 4>(p, B, block_bytes, st);
+    return launch_decode<D, MSE_BITS, VAL_BITS, 8>(p, B, block_bytes, st);
+}
+
+struct WsLayout {
+    size_t off_tickets, off_qprep, off_partials, total;
+};
+
+WsLayout decode_ws_layout(int D, int B, int Qh, int H, int max_slots) {
+    WsLayout w;
+    const int G = Qh / H;
+    const int GP = G <= 4 ? 4 : 8;
+    w.off_tickets = TQ_WS_HEADER_BYTES;
+    w.off_qprep = w.off_tickets + (((size_t)B * H * sizeof(int32_t) + 255) / 256) * 256;
+    w.off_partials = w.off_qprep + (((size_t)B * Qh * 2 * D * sizeof(float) + 255) / 256) * 256;
+    w.total = w.off_partials + (size_t)B * H * max_slots * GP * (D + 2) * sizeof(float);
+    return w;
+}
+
+int ring_splits_for(int max_ring_len) { return (max_ring_len + RING_TOK - 1) / RING_TOK; }
+
+}  // namespace
+
+extern "C" int tq_decode_workspace_bytes(const tq_config* cfg, int32_t batch, int32_t num_q_heads,
+                                         int32_t num_kv_heads, int32_t max_splits, size_t* out) {
+    if (!cfg || !out) return TQ_ERR_NULL;
+    int rc = tq_check_config(cfg);
+    if (rc != TQ_OK) return rc;
+    if (batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || max_splits <= 0) return TQ_ERR_SHAPE;
+    if (num_q_heads % num_kv_heads != 0 || num_q_heads / num_kv_heads > TQ_MAX_GROUP_HEADS) return TQ_ERR_UNSUPPORTED;
+    // ring CTAs need partial slots too: reserve for a ring of up to 256 tokens
+    *out = decode_ws_layout(cfg->head_dim, batch, num_q_heads, num_kv_heads, max_splits + 8).total;
+    return TQ_OK;
+}
+
+extern "C" int tq_scores_workspace_bytes(const tq_config* cfg, int64_t n_vectors, size_t* out) {
+    if (!cfg || !out) return TQ_ERR_NULL;
+    int rc = tq_check_config(cfg);
+    if (rc != TQ_OK) return rc;
+    if (n_vectors <= 0) return TQ_ERR_SHAPE;
+    *out = TQ_WS_HEADER_BYTES + (size_t)n_vectors * 2 * cfg->head_dim * sizeof(float);
+    return TQ_OK;
+}
+
+extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* a, void* stream) {
+    if (!consts || !pool || !a) return TQ_ERR_NULL;
+    if (!pool->base || !a->query || !a->out || !a->workspace || !a->block_table || !a->seq_lens) return TQ_ERR_NULL;
+    if (!consts->pi_t || !consts->s_t) return TQ_ERR_NULL;
+    int rc = tq_check_config(&consts->cfg);
+    if (rc != TQ_OK) return rc;
+    const int D = consts->cfg.head_dim, H = pool->num_kv_heads;
+    if (a->batch <= 0 || a->num_q_heads <= 0 || H <= 0 || a->max_seq_len < 0 || a->block_table_stride < 0)
+        return TQ_ERR_SHAPE;
+    if (a->num_q_heads % H != 0) return TQ_ERR_SHAPE;
+    const int G = a->num_q_heads / H;
+    if (G > TQ_MAX_GROUP_HEADS) return TQ_ERR_UNSUPPORTED;
+    if ((int64_t)a->block_table_stride * TQ_BLOCK_TOKENS < a->max_seq_len) return TQ_ERR_SHAPE;
+    const bool has_ring = a->ring_k != nullptr && a->max_ring_len > 0;
+    if (has_ring && (!a->ring_v || !a->ring_lens)) return TQ_ERR_NULL;
+    if (has_ring && a->max_ring_len > 256) return TQ_ERR_UNSUPPORTED;
+    if (((uintptr_t)pool->base & 15) || ((uintptr_t)a->workspace & 255)) return TQ_ERR_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+
+    const TqLayout L = tq_make_layout(D, consts->cfg.key_bits, consts->cfg.value_bits);
+    const int ntile = (a->max_seq_len + TILE_TOK - 1) / TILE_TOK;
+    int splits = a->num_splits;
+    if (splits <= 0) {
+        // about two CTAs per SM over the whole launch, at least 2 tiles per split
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int want = (2 * sms + a->batch * H - 1) / (a->batch * H);
+        splits = want < 1 ? 1 : want;
+        const int cap = (ntile + 1) / 2;
+        if (splits > cap) splits = cap;
+    }
+    if (splits < 1) splits = 1;
+    if (splits > ntile && ntile > 0) splits = ntile;
+    const int rsplits = has_ring ? ring_splits_for(a->max_ring_len) : 0;
+    const WsLayout w = decode_ws_layout(D, a->batch, a->num_q_heads, H, splits + rsplits);
+    if (w.total > a->workspace_bytes) return TQ_ERR_WORKSPACE;
+
+    uint8_t* ws = (uint8_t*)a->workspace;
+    float* qprep = (float*)(ws + w.off_qprep);
+    if (!a->query_prepared) {
+        const int64_t nvec = (int64_t)a->batch * a->num_q_heads;
+        tq_qprep_kernel<<<(unsigned)((nvec + 3) / 4), D, 4 * D * sizeof(float), st>>>(
+            a->query, a->q_dtype, nvec, D, consts->pi_t, consts->s_t, qprep);
+        if (cudaGetLastError() != cudaSuccess) return TQ_ERR_CUDA;
+    }
+
+    DecodeParams p;
+    p.pool = (const uint8_t*)pool->base;
+    p.num_blocks = pool->num_blocks;
+    p.H = H;
+    p.Qh = a->num_q_heads;
+    p.G = G;
+    p.block_table = a->block_table;
+    p.bt_stride = a->block_table_stride;
+    p.seq_lens = a->seq_lens;
+    p.min_history = a->min_history;
+    p.qprep = qprep;
+    p.query = a->query;
+    p.q_dtype = a->q_dtype;
+    p.ring_k = has_ring ? a->ring_k : nullptr;
+    p.ring_v = has_ring ? a->ring_v : nullptr;
+    p.ring_dtype = a->ring_dtype;
+    p.ring_lens = has_ring ? a->ring_lens : nullptr;
+    p.ring_stride_seq = a->ring_stride_seq;
+    p.ring_stride_token = a->ring_stride_token;
+    p.scale = a->scale;
+    p.qjl_scale = consts->qjl_scale;
+    for (int i = 0; i < TQ_MAX_CENTROIDS; ++i) {
+        p.cb.centroids[i] = consts->centroids[i];
+        p.cb.boundaries[i] = consts->boundaries[i];
+    }
+    p.out = a->out;
+    p.partials = (float*)(ws + w.off_partials);
+    p.tickets = (int32_t*)(ws + w.off_tickets);
+    p.status = (int32_t*)ws;
+    p.num_splits = splits;
+    p.ring_splits = rsplits;
+
+    const int mse_bits = consts->cfg.key_bits - 1, vb = consts->cfg.value_bits;
+#define TQ_DEC(DD, MB, VB) return launch_decode_g<DD, MB, VB>(p, a->batch, L.block_bytes, st)
+    if (D == 128) {
+        if (mse_bits == 2 && vb == 2) TQ_DEC(128, 2, 2);
+        if (mse_bits == 2 && vb == 4) TQ_DEC(128, 2, 4);
+        if (mse_bits == 3 && vb == 2) TQ_DEC(128, 3, 2);
+        TQ_DEC(128, 3, 4);
+    } else {
+        if (mse_bits == 2 && vb == 2) TQ_DEC(256, 2, 2);
+        if (mse_bits == 2 && vb == 4) TQ_DEC(256, 2, 4);
+        if (mse_bits == 3 && vb == 2) TQ_DEC(256, 3, 2);
+        TQ_DEC(256, 3, 4);
+    }
+#undef TQ_DEC
+}
+
+extern "C" int tq_scores(const tq_consts* consts, const tq_pool* pool, const int32_t* block_table, int64_t n_tokens,
+                         const void* query, tq_dtype q_dtype, int32_t n_q, float* logits, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+    if (!consts || !pool || !pool->base || !block_table || !query || !logits || !workspace) return TQ_ERR_NULL;
+    if (!consts->pi_t || !consts->s_t) return TQ_ERR_NULL;
+    int rc = tq_check_config(&consts->cfg);
+    if (rc != TQ_OK) return rc;
+    if (n_tokens < 0 || n_q <= 0 || pool->num_kv_heads <= 0) return TQ_ERR_SHAPE;
+    if (n_tokens == 0) return TQ_OK;
+    const int D = consts->cfg.head_dim, H = pool->num_kv_heads;
+    size_t need = 0;
+    tq_scores_workspace_bytes(&consts->cfg, (int64_t)H * n_q, &need);
+    if (need > workspace_bytes) return TQ_ERR_WORKSPACE;
+    if ((uintptr_t)workspace & 255) return TQ_ERR_ALIGN;
+    cudaStream_t st = (cudaStream_t)stream;
+    float* qprep = (float*)((uint8_t*)workspace + TQ_WS_HEADER_BYTES);
+    const int64_t nvec = (int64_t)H * n_q;
+    tq_qprep_kernel<<<(unsigned)((nvec + 3) / 4), D, 4 * D * sizeof(float), st>>>(query, q_dtype, nvec, D, consts->pi_t,
+                                                                                  consts->s_t, qprep);
+    if (cudaGetLastError() != cudaSuccess) return TQ_ERR_CUDA;
+
+    const TqLayout L = tq_make_layout(D, consts->cfg.key_bits, consts->cfg.value_bits);
+    ScoreParams p;
+    p.pool = (const uint8_t*)pool->base;
+    p.num_blocks = pool->num_blocks;
+    p.H = H;
+    p.block_table = block_table;
+    p.n_tokens = n_tokens;
+    p.qprep = qprep;
+    p.n_q = n_q;
+    p.qjl_scale = consts->qjl_scale;
+    for (int i = 0; i < TQ_MAX_CENTROIDS; ++i) {
+        p.cb.centroids[i] = consts->centroids[i];
+        p.cb.boundaries[i] = consts->boundaries[i];
+    }
+    p.logits = logits;
+    p.status = (int32_t*)workspace;
+    const size_t smem = (size_t)TILE_BLOCKS * L.block_bytes +
+                        sizeof(float) * (2 * D * 8 + 2 * 8 * TILE_TOK + TQ_MAX_CENTROIDS) + sizeof(uint64_t);
+    dim3 grid((unsigned)((n_tokens + TILE_TOK - 1) / TILE_TOK), (unsigned)H, (unsigned)((n_q + 7) / 8));
+    const int mse_bits = consts->cfg.key_bits - 1;
+#define TQ_SC(DD, MB)                                                                                          \
+    do {                                                                                                       \
+        static size_t smem_set = 0;                                                                            \
+        if (smem > smem_set) {                                                                                 \
+            if (cudaFuncSetAttribute(tq_scores_kernel<DD, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                     (int)smem) != cudaSuccess)                                                \
+                return TQ_ERR_CUDA;                                                                            \
+            smem_set = smem;                                                                                   \
+        }                                                                                                      \
+        tq_scores_kernel<DD, MB><<<grid, DEC_THREADS, smem, st>>>(p, consts->cfg.key_bits, consts->cfg.value_bits); \
+    } while (0)
+    if (D == 128 && mse_bits == 2) TQ_SC(128, 2);
+    else if (D == 128) TQ_SC(128, 3);
+    else if (mse_bits == 2) TQ_SC(256, 2);
+    else TQ_SC(256, 3);
+#undef TQ_SC
+    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
+}
