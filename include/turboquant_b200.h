@@ -177,6 +177,7 @@ typedef struct tq_decode_args {
     int32_t num_splits;         /* sequence splits per (sequence, kv head); 0 = choose */
     int32_t query_prepared;     /* nonzero: the workspace already holds this query's rotated /
                                    sketched form from an earlier tq_decode with the same workspace */
+    int32_t kernel;             /* 0: tensor-core kernel where it applies; 1: always the CUDA-core kernel */
 } tq_decode_args;
 
 /* One decode-attention step over compressed history plus the exact ring:

@@ -178,11 +178,11 @@ def sm_count(device) -> int:
 
 
 def choose_splits(batch: int, num_kv_heads: int, max_seq_len: int, sms: int) -> int:
-    """Sequence splits per (sequence, kv head): about two CTAs per SM, at least
-    two 64-token tiles per split."""
-    ntile = (max_seq_len + 63) // 64
-    want = max(1, -(-2 * sms // max(1, batch * num_kv_heads)))
-    return max(1, min(want, (ntile + 1) // 2))
+    """Sequence splits per (sequence, kv head): about three CTAs per SM over the
+    whole launch, at least eight 16-token records per CTA (two per warp)."""
+    nblk = (max_seq_len + TQ_BLOCK_TOKENS - 1) // TQ_BLOCK_TOKENS
+    want = max(1, -(-3 * sms // max(1, batch * num_kv_heads)))
+    return max(1, min(want, nblk // 8))
 
 
 def store(consts: LayerConstants, pool: BlockPool, key: torch.Tensor, value: torch.Tensor, *,
@@ -206,7 +206,7 @@ def decode(consts: LayerConstants, pool: BlockPool, ws: Workspace, query: torch.
            ring_lens: Optional[torch.Tensor] = None, max_ring_len: int = 0,
            ring_stride_seq: int = 0, ring_stride_token: int = 0, scale: Optional[float] = None,
            min_history: int = 16, num_splits: int = 0, out: Optional[torch.Tensor] = None,
-           query_prepared: bool = False) -> torch.Tensor:
+           query_prepared: bool = False, kernel: int = 0) -> torch.Tensor:
     """query (B, Qh, D) -> out (B, Qh, D) in the query dtype."""
     require_cuda(query, "query")
     b, qh, d = query.shape
@@ -234,6 +234,7 @@ def decode(consts: LayerConstants, pool: BlockPool, ws: Workspace, query: torch.
     a.scale = scale
     a.out, a.workspace, a.workspace_bytes, a.num_splits = out.data_ptr(), ws.ptr, ws.nbytes, splits
     a.query_prepared = 1 if query_prepared else 0
+    a.kernel = kernel
     check(lib().tq_decode(C.byref(consts.c), C.byref(pool.c), C.byref(a), stream_ptr(consts.device)), "tq_decode")
     return out
 

@@ -1,0 +1,264 @@
+// Pieces shared by the two decode kernels (CUDA-core and tensor-core): launch
+// parameters, tile loading, the exact-ring part, and the ticketed merge of the
+// per-CTA partial results.
+#pragma once
+#include "tq_common.cuh"
+
+namespace tqdec {
+
+constexpr int DEC_THREADS = 128;
+constexpr int TILE_BLOCKS = 4;
+constexpr int TILE_TOK = TILE_BLOCKS * TQ_BLOCK_TOKENS;  // 64
+constexpr int NSTAGE = 3;
+constexpr int RING_TOK = 32;  // ring tokens per ring CTA
+
+struct DecodeParams {
+    const uint8_t* pool;
+    int64_t num_blocks;
+    int H, Qh, G;
+    const int32_t* block_table;
+    int bt_stride;
+    const int32_t* seq_lens;
+    int min_history;
+    const float* qprep;  // [B][Qh][2][D] rotated / sketched query
+    const void* query;
+    int q_dtype;
+    const void* ring_k;
+    const void* ring_v;
+    int ring_dtype;
+    const int32_t* ring_lens;
+    int64_t ring_stride_seq, ring_stride_token;
+    float scale, qjl_scale;
+    TqCodebook cb;
+    void* out;
+    float* partials;
+    int32_t* tickets;
+    int32_t* status;
+    int num_splits, ring_splits;
+};
+
+struct ScoreParams {
+    const uint8_t* pool;
+    int64_t num_blocks;
+    int H;
+    const int32_t* block_table;
+    int64_t n_tokens;
+    const float* qprep;  // [H][n_q][2][D]
+    int n_q;
+    float qjl_scale;
+    TqCodebook cb;
+    float* logits;  // [H][n_q][n_tokens]
+    int32_t* status;
+};
+
+// Partial logits of one token over dims [dim0, dim0 + D/2) for GP query heads.
+template <int D, int MSE_BITS, int GP>
+__device__ __forceinline__ void token_half_scores(const uint8_t* rec, const TqLayout& L, int tl, int half,
+                                                  const float* __restrict__ qr, const float* __restrict__ qs,
+                                                  const float* __restrict__ cent, float qjl_scale, float (&out)[GP]) {
+    constexpr int WIDTH = MSE_BITS == 2 ? 2 : 4;
+    constexpr int DIMS_PER_CW = 32 / WIDTH;       // dims per 32-bit code word
+    constexpr int CW_PER_SW = 32 / DIMS_PER_CW;   // code words per 32-bit sign word
+    constexpr uint32_t MASK = (1u << WIDTH) - 1u;
+    const uint32_t* cw = reinterpret_cast<const uint32_t*>(rec + L.off_kcodes + tl * L.kcode_row) + half * (D / 2) / DIMS_PER_CW;
+    const uint32_t* sw = reinterpret_cast<const uint32_t*>(rec + L.off_ksigns + tl * L.ksign_row) + half * (D / 64);
+    float am[GP], aq[GP];
+#pragma unroll
+    for (int g = 0; g < GP; ++g) am[g] = aq[g] = 0.f;
+    int j = half * (D / 2);
+#pragma unroll 1
+    for (int s = 0; s < D / 64; ++s) {
+        uint32_t sg = sw[s];
+#pragma unroll
+        for (int c = 0; c < CW_PER_SW; ++c) {
+            uint32_t w = cw[s * CW_PER_SW + c];
+#pragma unroll 4
+            for (int i = 0; i < DIMS_PER_CW; ++i, ++j) {
+                const float cv = cent[w & MASK];
+                w >>= WIDTH;
+                const float sv = (sg & 1u) ? 1.f : -1.f;
+                sg >>= 1;
+                const float* qrj = qr + j * GP;
+                const float* qsj = qs + j * GP;
+#pragma unroll
+                for (int g4 = 0; g4 < GP / 4; ++g4) {
+                    const float4 a = *reinterpret_cast<const float4*>(qrj + 4 * g4);
+                    const float4 b = *reinterpret_cast<const float4*>(qsj + 4 * g4);
+                    am[4 * g4 + 0] = fmaf(a.x, cv, am[4 * g4 + 0]);
+                    am[4 * g4 + 1] = fmaf(a.y, cv, am[4 * g4 + 1]);
+                    am[4 * g4 + 2] = fmaf(a.z, cv, am[4 * g4 + 2]);
+                    am[4 * g4 + 3] = fmaf(a.w, cv, am[4 * g4 + 3]);
+                    aq[4 * g4 + 0] = fmaf(b.x, sv, aq[4 * g4 + 0]);
+                    aq[4 * g4 + 1] = fmaf(b.y, sv, aq[4 * g4 + 1]);
+                    aq[4 * g4 + 2] = fmaf(b.z, sv, aq[4 * g4 + 2]);
+                    aq[4 * g4 + 3] = fmaf(b.w, sv, aq[4 * g4 + 3]);
+                }
+            }
+        }
+    }
+    const float norm = __half2float(reinterpret_cast<const __half*>(rec + L.off_knorm)[tl]);
+    const float rn = __half2float(reinterpret_cast<const __half*>(rec + L.off_krnorm)[tl]) * qjl_scale;
+#pragma unroll
+    for (int g = 0; g < GP; ++g) out[g] = norm * am[g] + rn * aq[g];
+}
+
+// Issue the bulk copies of one tile (up to 4 block records) into a stage.
+static __device__ __forceinline__ void issue_tile(uint8_t* stage, uint64_t* bar, const uint8_t* pool, int64_t num_blocks,
+                                           const int32_t* bt, int first_blk, int nblk_total, int H, int h,
+                                           int block_bytes, int32_t* status) {
+    const int nb = min(TILE_BLOCKS, nblk_total - first_blk);
+    tq_mbar_expect_tx(bar, (uint32_t)(nb * block_bytes));
+    for (int i = 0; i < nb; ++i) {
+        int64_t phys = bt[first_blk + i];
+        if (phys < 0 || phys >= num_blocks) {
+            if (status) atomicCAS(status, 0, (int)TQ_ERR_RANGE);
+            phys = 0;
+        }
+        tq_bulk_g2s(stage + i * block_bytes, pool + (phys * H + h) * (int64_t)block_bytes, (uint32_t)block_bytes, bar);
+    }
+}
+
+// Partial result of one CTA: m[GP] (natural-log domain), l[GP], acc[GP][D].
+template <int D, int GP>
+__device__ __forceinline__ float* partial_ptr(const DecodeParams& p, int b, int h, int slot_idx) {
+    const int nslot = p.num_splits + p.ring_splits;
+    return p.partials + ((int64_t)(b * p.H + h) * nslot + slot_idx) * (GP * (D + 2));
+}
+
+// Each thread owns D/128 consecutive channels of every query head.
+template <int D, int GP>
+__device__ __forceinline__ void write_partial_regs(const DecodeParams& p, int b, int h, int slot_idx,
+                                                   const float (&acc)[GP][D / DEC_THREADS], const float* m_run,
+                                                   const float* l_run) {
+    constexpr int DPT = D / DEC_THREADS;
+    const int tid = threadIdx.x;
+    float* mine = partial_ptr<D, GP>(p, b, h, slot_idx);
+    if (tid < GP) {
+        mine[tid] = m_run[tid];
+        mine[GP + tid] = l_run[tid];
+    }
+#pragma unroll
+    for (int g = 0; g < GP; ++g)
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) mine[2 * GP + g * D + tid * DPT + i] = acc[g][i];
+}
+
+// After a CTA has written its partial: take a ticket; the last CTA of this
+// (sequence, kv head) merges all partials and writes the output.  Nobody waits.
+template <int D, int GP>
+__device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, int h,
+                                                 float* wsm /* [max(nslot,128)*GP + 2*GP] */) {
+    constexpr int PS = GP * (D + 2);
+    const int tid = threadIdx.x;
+    const int nslot = p.num_splits + p.ring_splits;
+    __threadfence();
+    __shared__ int s_last;
+    __syncthreads();
+    if (tid == 0) {
+        const int t = atomicAdd(p.tickets + b * p.H + h, 1);
+        s_last = (t == nslot - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+
+    const float* base = p.partials + (int64_t)(b * p.H + h) * nslot * PS;
+    float* wL = wsm;             // [GP] global sum
+    float* w = wsm + 2 * GP;     // [nslot][GP] weight of each partial
+    const int warp = tid >> 5, lane = tid & 31;
+    for (int g = warp; g < GP; g += DEC_THREADS / 32) {
+        float mx = -INFINITY;
+        for (int s = lane; s < nslot; s += 32) mx = fmaxf(mx, __ldcg(base + (int64_t)s * PS + g));
+        mx = tq_warp_max(mx);
+        float sum = 0.f;
+        for (int s = lane; s < nslot; s += 32) {
+            const float ms = __ldcg(base + (int64_t)s * PS + g);
+            const float ls = __ldcg(base + (int64_t)s * PS + GP + g);
+            const float ws = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
+            w[s * GP + g] = ws;
+            sum += ws * ls;
+        }
+        sum = tq_warp_sum(sum);
+        if (lane == 0) wL[g] = sum;
+    }
+    __syncthreads();
+    for (int i = tid; i < p.G * D; i += DEC_THREADS) {
+        const int g = i / D, d = i % D;
+        float o = 0.f;
+        for (int s = 0; s < nslot; ++s) {
+            const float ws = w[s * GP + g];
+            if (ws != 0.f) o = fmaf(ws, __ldcg(base + (int64_t)s * PS + 2 * GP + g * D + d), o);
+        }
+        const float l = wL[g];
+        tq_store_any(p.out, ((int64_t)b * p.Qh + h * p.G + g) * D + d, l > 0.f ? o / l : 0.f, p.q_dtype);
+    }
+    if (tid == 0) p.tickets[b * p.H + h] = 0;  // ready for the next launch
+}
+
+// Exact attention over this CTA's slice of the ring (up to RING_TOK tokens),
+// fp32 like the reference's matmul path (score.py:154-170).  Leaves the partial
+// in (acc, m_run, l_run).  scratch: qf [D][GP], sc [GP][RING_TOK], pp [RING_TOK][GP].
+template <int D, int GP>
+__device__ __forceinline__ void ring_part(const DecodeParams& p, int b, int h, int rs, float* qf, float* sc,
+                                          float* pp, float* m_run, float* l_run,
+                                          float (&acc)[GP][D / DEC_THREADS]) {
+    constexpr int DPT = D / DEC_THREADS;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int R = p.ring_lens ? p.ring_lens[b] : 0;
+    const int r0 = rs * RING_TOK;
+    const int nr = max(0, min(RING_TOK, R - r0));
+    if (nr <= 0) return;
+    for (int i = tid; i < D * GP; i += DEC_THREADS) {
+        const int j = i / GP, g = i % GP;
+        qf[i] = g < p.G ? tq_load_any(p.query, ((int64_t)b * p.Qh + h * p.G + g) * D + j, p.q_dtype) : 0.f;
+    }
+    __syncthreads();
+    for (int t = warp; t < nr; t += DEC_THREADS / 32) {
+        const int64_t off = (int64_t)b * p.ring_stride_seq + (int64_t)(r0 + t) * p.ring_stride_token + (int64_t)h * D;
+        float a[GP];
+#pragma unroll
+        for (int g = 0; g < GP; ++g) a[g] = 0.f;
+        for (int j = lane; j < D; j += 32) {
+            const float kx = tq_load_any(p.ring_k, off + j, p.ring_dtype);
+#pragma unroll
+            for (int g = 0; g < GP; ++g) a[g] = fmaf(qf[j * GP + g], kx, a[g]);
+        }
+#pragma unroll
+        for (int g = 0; g < GP; ++g) {
+            const float s = tq_warp_sum(a[g]);
+            if (lane == 0) sc[g * RING_TOK + t] = s * p.scale;
+        }
+    }
+    __syncthreads();
+    for (int g = warp; g < GP; g += DEC_THREADS / 32) {
+        const float s0 = lane < nr ? sc[g * RING_TOK + lane] : -INFINITY;
+        const float m_new = tq_warp_max(s0);
+        const float p0 = (s0 == -INFINITY) ? 0.f : __expf(s0 - m_new);
+        const float sum = tq_warp_sum(p0);
+        pp[lane * GP + g] = p0;
+        if (lane == 0) {
+            m_run[g] = m_new;
+            l_run[g] = sum;
+        }
+    }
+    __syncthreads();
+    const int d0 = tid * DPT;
+    for (int t = 0; t < nr; ++t) {
+        const int64_t off = (int64_t)b * p.ring_stride_seq + (int64_t)(r0 + t) * p.ring_stride_token + (int64_t)h * D + d0;
+        float v[DPT];
+#pragma unroll
+        for (int i = 0; i < DPT; ++i) v[i] = tq_load_any(p.ring_v, off + i, p.ring_dtype);
+        const float* pt = pp + t * GP;
+#pragma unroll
+        for (int g = 0; g < GP; ++g)
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) acc[g][i] = fmaf(pt[g], v[i], acc[g][i]);
+    }
+}
+
+// Launcher of the tensor-core kernel (tq_decode_mma.cu); *handled = 0 when the
+// configuration is outside what it covers and the CUDA-core kernel must run.
+int tq_decode_mma_launch(const DecodeParams& p, int D, int mse_bits, int val_bits, int batch, int max_seq_len,
+                         cudaStream_t st, int* handled);
+
+}  // namespace tqdec

@@ -1,0 +1,552 @@
+// Tensor-core decode attention over compressed block records.
+//
+// Decode is HBM-bound only if the arithmetic is almost free: a record of
+// 100-196 bytes carries 3*D*G multiply-adds, far beyond what CUDA cores can do
+// at HBM speed.  So every contraction runs on the tensor cores (mma.sync
+// m16n8k16, fp16 in / fp32 accumulate) with operands expanded from the packed
+// codes IN REGISTERS, one logic instruction per pair of elements:
+//
+//  * A 16-token block record is exactly one MMA row tile.  A warp owns whole
+//    records, streams them through a private 4-stage ring of bulk (TMA) copies
+//    and keeps its own online-softmax state; warps never synchronise in the
+//    main loop.
+//  * A single bit kept in place inside a 16-bit lane IS an fp16 number
+//    (bit b <= 9 is the subnormal 2^(b-24)); a 2/4-bit field is the subnormal
+//    code * 2^(pos-24).  So `word & mask` yields an A-operand register holding
+//    two elements.  The per-position power of two is folded into the B operand
+//    (scores) or into a per-row factor applied once at the end (values).
+//  * Scores: the 2-bit MSE code is used as two bit planes because the code book
+//    is affine in the bits (c = c0 + (c1-c0) b0 + (c2-c0) b1 for a symmetric
+//    4-level book), the QJL signs are a third bit plane.  With G <= 4 query
+//    heads per kv head, columns 0-3 of the B fragment hold the rotated query
+//    and columns 4-7 the sketched query, so one B fragment serves all planes.
+//  * Values: out[d][g] = sum_n code[n][d] * (p[n][g] * scale[n][grp(d)])
+//                        + sum_n p[n][g] * zero[n][grp(d)];
+//    the 16 rows of an MMA tile are 16 channels of one group, the contraction
+//    runs over the 16 tokens, the group scale rides on the probabilities and
+//    the zero-point term is one more small MMA.
+#include "tq_decode_common.cuh"
+
+using namespace tqdec;
+
+namespace {
+
+constexpr int NSTW = 4;  // bulk-copy stages per warp, one block record each
+
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
+    uint32_t y;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(y) : "r"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t hmul2_sat(uint32_t a, uint32_t b) {
+    const __half2 r = __hmin2(__hmul2(*reinterpret_cast<const __half2*>(&a), *reinterpret_cast<const __half2*>(&b)),
+                              __floats2half2_rn(65504.f, 65504.f));
+    return *reinterpret_cast<const uint32_t*>(&r);
+}
+
+// ---- operand geometry shared by the query fragments and the main loop ----------------
+// Thread (gid = lane/4, tig = lane%4).  Score MMA k-step s uses B/A register pair
+// r = 2s, 2s+1; register r covers dims d_lo = (D/4)*tig + 16*(r/8) + r%8 and d_lo + 8:
+// the two 16-bit halves of code word r/8, field j = r%8.
+__host__ __device__ constexpr int code_pos(int j) { return j <= 4 ? j : j - 3; }            // 2-bit field index after the optional >>6
+__host__ __device__ constexpr int sign_bit(int wi, int j) { return j + 8 * (wi & 1); }      // bit in the byte-swapped sign word
+__host__ __device__ constexpr int sign_pos(int b) { return b <= 9 ? b : b - 6; }
+
+template <int D, int VAL_BITS, bool SPLITB>
+__global__ void __launch_bounds__(DEC_THREADS, 3) tq_decode_mma_kernel(const DecodeParams p) {
+    constexpr int GP = SPLITB ? 8 : 4;
+    constexpr int KS = D / 16;    // score k-steps
+    constexpr int NWK = D / 64;   // code words per thread per token
+    constexpr int NMB = D / 16;   // value M-blocks
+    constexpr int NG = D / 32;
+    constexpr int DPT = D / DEC_THREADS;
+    const TqLayout L = tq_make_layout(D, 3, VAL_BITS);
+    const int BB = L.block_bytes;
+
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint8_t* stages = smem;                                              // [4 warps][NSTW][BB]; reused after the loop
+    float* qsm = reinterpret_cast<float*>(smem + 4 * NSTW * BB);         // [2][GP][D] rotated / sketched query
+    float* cst = qsm + 2 * GP * D;                                       // [4][GP]: exponent e_rot, e_sk, sums q_rot, q_sk
+    float* ml = cst + 4 * GP;                                            // [4 warps][2][GP]
+    float* m_run_s = ml + 8 * GP;                                        // [GP] (ring part / combined partial)
+    float* l_run_s = m_run_s + GP;                                       // [GP]
+    int* bt_s = reinterpret_cast<int*>(l_run_s + GP);                    // [256] physical blocks of this CTA
+    uint64_t* bars = reinterpret_cast<uint64_t*>(bt_s + 256);            // [4][NSTW]
+    float* wsm = reinterpret_cast<float*>(bars + 4 * NSTW);              // merge scratch
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int gid = lane >> 2, tig = lane & 3;
+    const int b = blockIdx.z, h = blockIdx.y, x = blockIdx.x;
+
+    if (x >= p.num_splits) {
+        // exact ring tokens: CUDA-core fp32 path shared with the generic kernel
+        float acc[GP][DPT];
+#pragma unroll
+        for (int g = 0; g < GP; ++g)
+#pragma unroll
+            for (int i = 0; i < DPT; ++i) acc[g][i] = 0.f;
+        if (tid < GP) {
+            m_run_s[tid] = -INFINITY;
+            l_run_s[tid] = 0.f;
+        }
+        __syncthreads();
+        float* scratch = reinterpret_cast<float*>(stages);
+        ring_part<D, GP>(p, b, h, x - p.num_splits, scratch, scratch + D * GP, scratch + D * GP + GP * RING_TOK,
+                         m_run_s, l_run_s, acc);
+        __syncthreads();
+        write_partial_regs<D, GP>(p, b, h, x, acc, m_run_s, l_run_s);
+        ticket_and_merge<D, GP>(p, b, h, wsm);
+        return;
+    }
+
+    // ------------------------------ this CTA's share of the history ------------------------------
+    int n = p.seq_lens[b];
+    if (n < p.min_history) n = 0;
+    const int nblk = (n + TQ_BLOCK_TOKENS - 1) / TQ_BLOCK_TOKENS;
+    const int blk0 = (int)((int64_t)x * nblk / p.num_splits);
+    const int blk1 = (int)((int64_t)(x + 1) * nblk / p.num_splits);
+    const int nmine = min(blk1 - blk0, 256);   // host guarantees <= 256 blocks per split
+    const int cnt = nmine > warp ? (nmine - warp + 3) / 4 : 0;   // records of this warp
+
+    // block table slice and barriers first, so the copies overlap the query set-up
+    const int32_t* bt = p.block_table + (int64_t)b * p.bt_stride;
+    for (int i = tid; i < nmine; i += DEC_THREADS) {
+        int phys = bt[blk0 + i];
+        if (phys < 0 || phys >= p.num_blocks) {
+            atomicCAS(p.status, 0, (int)TQ_ERR_RANGE);
+            phys = 0;
+        }
+        bt_s[i] = phys;
+    }
+    if (tid == 0) {
+        for (int s = 0; s < 4 * NSTW; ++s) tq_mbar_init(bars + s, 1);
+        tq_mbar_fence_init();
+    }
+    __syncthreads();
+    uint8_t* my_stage = stages + warp * NSTW * BB;
+    uint64_t* my_bar = bars + warp * NSTW;
+    if (lane == 0) {
+        for (int i = 0; i < NSTW && i < cnt; ++i) {
+            tq_mbar_expect_tx(my_bar + i, (uint32_t)BB);
+            tq_bulk_g2s(my_stage + i * BB, p.pool + ((int64_t)bt_s[warp + 4 * i] * p.H + h) * BB, (uint32_t)BB,
+                        my_bar + i);
+        }
+    }
+
+    // ---- query fragments ----
+    for (int i = tid; i < 2 * GP * D; i += DEC_THREADS) {
+        const int which = i / (GP * D), g = (i / D) % GP, j = i % D;
+        qsm[i] = g < p.G ? p.qprep[((int64_t)(b * p.Qh + h * p.G + g) * 2 + which) * D + j] : 0.f;
+    }
+    __syncthreads();
+    for (int row = warp; row < 2 * GP; row += 4) {   // power-of-two scale per query row
+        float mx = 0.f;
+        for (int j = lane; j < D; j += 32) mx = fmaxf(mx, fabsf(qsm[row * D + j]));
+        mx = tq_warp_max(mx);
+        if (lane == 0) cst[row] = (mx > 0.f && mx < 3.0e38f) ? (float)(14 - ilogbf(mx)) : 0.f;
+    }
+    __syncthreads();
+
+    uint32_t bq[2 * KS];
+    uint32_t bsk[SPLITB ? 2 * KS : 1];
+    {
+        // column of this thread in the B fragment: n = gid
+        const int g_rot = SPLITB ? gid : (gid & 3);
+        const bool is_sk = !SPLITB && gid >= 4;
+        const float* src_a = qsm + ((is_sk ? GP : 0) + g_rot) * D;
+        const int e_a = (int)cst[(is_sk ? GP : 0) + g_rot];
+        const float* src_b = qsm + (GP + g_rot) * D;
+        const int e_b = (int)cst[GP + g_rot];
+        float sum_a = 0.f, sum_b = 0.f;
+#pragma unroll
+        for (int r = 0; r < 2 * KS; ++r) {
+            const int wi = r >> 3, j = r & 7;
+            const int d_lo = (D / 4) * tig + 16 * wi + j, d_hi = d_lo + 8;
+            const int sh_code = 2 * code_pos(j), sh_sign = sign_pos(sign_bit(wi, j));
+            const int sh = is_sk ? sh_sign : sh_code;
+            const __half lo = __float2half_rn(ldexpf(src_a[d_lo], e_a - sh));
+            const __half hi = __float2half_rn(ldexpf(src_a[d_hi], e_a - sh));
+            sum_a += ldexpf(__half2float(lo) + __half2float(hi), sh - e_a);
+            const __half2 v = __halves2half2(lo, hi);
+            bq[r] = *reinterpret_cast<const uint32_t*>(&v);
+            if (SPLITB) {
+                const __half lo2 = __float2half_rn(ldexpf(src_b[d_lo], e_b - sh_sign));
+                const __half hi2 = __float2half_rn(ldexpf(src_b[d_hi], e_b - sh_sign));
+                sum_b += ldexpf(__half2float(lo2) + __half2float(hi2), sh_sign - e_b);
+                const __half2 v2 = __halves2half2(lo2, hi2);
+                bsk[r] = *reinterpret_cast<const uint32_t*>(&v2);
+            }
+        }
+        // sums of the fp16-rounded query over all dims: add the four tig lanes
+        sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
+        sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
+        sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
+        sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+        if (warp == 0 && tig == 0) {
+            if (SPLITB) {
+                cst[2 * GP + gid] = sum_a;
+                cst[3 * GP + gid] = sum_b;
+            } else {
+                cst[(is_sk ? 3 : 2) * GP + g_rot] = sum_a;
+            }
+        }
+    }
+    __syncthreads();
+
+    // per-thread constants of its two score columns g = 2*tig, 2*tig+1
+    // logit*log2e*scale = nk * (k0 + k1*acc1 + kb0*acc0) + rk * (ks*accs - kq)
+    float k0[2], k1[2], kb0[2], ksg[2], kq[2];
+    {
+        const float c0 = p.cb.centroids[0], c1 = p.cb.centroids[1], c2 = p.cb.centroids[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int g = (2 * tig + i) & (GP - 1);
+            const int e_rot = (int)cst[g], e_sk = (int)cst[GP + g];
+            k0[i] = c0 * cst[2 * GP + g];
+            k1[i] = ldexpf(c2 - c0, 23 - e_rot);
+            kb0[i] = ldexpf(c1 - c0, 24 - e_rot);
+            ksg[i] = ldexpf(1.f, 25 - e_sk);
+            kq[i] = cst[3 * GP + g];
+        }
+    }
+    const float sm_scale = p.scale * 1.4426950408889634f;   // softmax in base 2
+    const float qjl = p.qjl_scale;
+    const bool col_ok = SPLITB || tig < 2;                   // this thread's score columns are real heads
+
+    float o[NMB][4];
+#pragma unroll
+    for (int mb = 0; mb < NMB; ++mb)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[mb][c] = 0.f;
+    float zacc[4] = {0.f, 0.f, 0.f, 0.f};
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    const int tokA = 4 * (gid >> 1) + (gid & 1), tokB = tokA + 2;   // tokens of score rows gid, gid+8
+    bool failed = false;
+
+    for (int it = 0; it < cnt; ++it) {
+        const int st = it % NSTW;
+        bool ok = tq_mbar_wait_bounded(my_bar + st, (uint32_t)((it / NSTW) & 1));
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+            failed = true;
+            break;
+        }
+        const uint8_t* rec = my_stage + st * BB;
+        const int blk = blk0 + warp + 4 * it;
+        const int valid = min(TQ_BLOCK_TOKENS, n - blk * TQ_BLOCK_TOKENS);
+
+        // ------------------------------ scores ------------------------------
+        float acc1[4] = {0.f, 0.f, 0.f, 0.f}, acc0[4] = {0.f, 0.f, 0.f, 0.f}, accs[4] = {0.f, 0.f, 0.f, 0.f};
+        {
+            const uint32_t* cwA = reinterpret_cast<const uint32_t*>(rec + L.off_kcodes + tokA * L.kcode_row) + tig * NWK;
+            const uint32_t* cwB = reinterpret_cast<const uint32_t*>(rec + L.off_kcodes + tokB * L.kcode_row) + tig * NWK;
+            const uint32_t* swA = reinterpret_cast<const uint32_t*>(rec + L.off_ksigns + tokA * L.ksign_row) + tig * (NWK / 2);
+            const uint32_t* swB = reinterpret_cast<const uint32_t*>(rec + L.off_ksigns + tokB * L.ksign_row) + tig * (NWK / 2);
+            uint32_t wA[NWK], wB[NWK], sA[NWK / 2], sB[NWK / 2];
+            if (NWK == 4) {
+                const uint4 a = *reinterpret_cast<const uint4*>(cwA), bb = *reinterpret_cast<const uint4*>(cwB);
+                wA[0] = a.x; wA[1] = a.y; wA[NWK - 2] = a.z; wA[NWK - 1] = a.w;
+                wB[0] = bb.x; wB[1] = bb.y; wB[NWK - 2] = bb.z; wB[NWK - 1] = bb.w;
+                const uint2 c = *reinterpret_cast<const uint2*>(swA), d = *reinterpret_cast<const uint2*>(swB);
+                sA[0] = c.x; sA[NWK / 2 - 1] = c.y;
+                sB[0] = d.x; sB[NWK / 2 - 1] = d.y;
+            } else {
+                const uint2 a = *reinterpret_cast<const uint2*>(cwA), bb = *reinterpret_cast<const uint2*>(cwB);
+                wA[0] = a.x; wA[1] = a.y;
+                wB[0] = bb.x; wB[1] = bb.y;
+                sA[0] = swA[0];
+                sB[0] = swB[0];
+            }
+#pragma unroll
+            for (int wi = 0; wi < NWK; ++wi) {
+                const uint32_t a_lo = wA[wi], b_lo = wB[wi];
+                const uint32_t a_hi = a_lo >> 6, b_hi = b_lo >> 6;
+                // sign word with bytes 1 and 2 swapped: halves then pair the same dims as the code word
+                const uint32_t sa_lo = __byte_perm(sA[wi >> 1], 0, 0x3120), sb_lo = __byte_perm(sB[wi >> 1], 0, 0x3120);
+                const uint32_t sa_hi = sa_lo >> 6, sb_hi = sb_lo >> 6;
+#pragma unroll
+                for (int jj = 0; jj < 4; ++jj) {
+                    const int s = wi * 4 + jj;
+                    const int j0 = 2 * jj, j1 = j0 + 1;
+                    const uint32_t m0 = 0x00010001u << (2 * code_pos(j0)), m1 = 0x00010001u << (2 * code_pos(j1));
+                    const uint32_t xa0 = j0 <= 4 ? a_lo : a_hi, xb0 = j0 <= 4 ? b_lo : b_hi;
+                    const uint32_t xa1 = j1 <= 4 ? a_lo : a_hi, xb1 = j1 <= 4 ? b_lo : b_hi;
+                    mma16816(acc0, xa0 & m0, xb0 & m0, xa1 & m1, xb1 & m1, bq[2 * s], bq[2 * s + 1]);
+                    mma16816(acc1, xa0 & (m0 << 1), xb0 & (m0 << 1), xa1 & (m1 << 1), xb1 & (m1 << 1), bq[2 * s],
+                             bq[2 * s + 1]);
+                    const int sb0 = sign_bit(wi, j0), sb1 = sign_bit(wi, j1);
+                    const uint32_t n0 = 0x00010001u << sign_pos(sb0), n1 = 0x00010001u << sign_pos(sb1);
+                    const uint32_t ya0 = sb0 <= 9 ? sa_lo : sa_hi, yb0 = sb0 <= 9 ? sb_lo : sb_hi;
+                    const uint32_t ya1 = sb1 <= 9 ? sa_lo : sa_hi, yb1 = sb1 <= 9 ? sb_lo : sb_hi;
+                    if (SPLITB)
+                        mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, bsk[2 * s], bsk[2 * s + 1]);
+                    else
+                        mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, bq[2 * s], bq[2 * s + 1]);
+                }
+            }
+        }
+        if (!SPLITB) {   // sketched-query columns 4..7 live two lanes to the right
+#pragma unroll
+            for (int c = 0; c < 4; ++c) accs[c] = __shfl_xor_sync(0xffffffffu, accs[c], 2);
+        }
+
+        // ------------------------------ online softmax ------------------------------
+        const __half* nrm = reinterpret_cast<const __half*>(rec + L.off_knorm);
+        const __half* rnm = reinterpret_cast<const __half*>(rec + L.off_krnorm);
+        const float nA = __half2float(nrm[tokA]) * sm_scale, nB = __half2float(nrm[tokB]) * sm_scale;
+        const float rA = __half2float(rnm[tokA]) * (qjl * sm_scale), rB = __half2float(rnm[tokB]) * (qjl * sm_scale);
+        float sA[2], sB[2], pA[2], pB[2];
+        bool rescale = false;
+        float alpha[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            sA[i] = nA * (k0[i] + k1[i] * acc1[i] + kb0[i] * acc0[i]) + rA * (ksg[i] * accs[i] - kq[i]);
+            sB[i] = nB * (k0[i] + k1[i] * acc1[2 + i] + kb0[i] * acc0[2 + i]) + rB * (ksg[i] * accs[2 + i] - kq[i]);
+            if (tokA >= valid) sA[i] = -INFINITY;
+            if (tokB >= valid) sB[i] = -INFINITY;
+            float mx = fmaxf(sA[i], sB[i]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            const float m_new = fmaxf(m_run[i], mx);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            alpha[i] = exp2f(m_run[i] - m_use);
+            pA[i] = exp2f(sA[i] - m_use);
+            pB[i] = exp2f(sB[i] - m_use);
+            l_run[i] = l_run[i] * alpha[i] + pA[i] + pB[i];
+            rescale |= (m_new != m_run[i]);
+            m_run[i] = m_new;
+        }
+        if (__any_sync(0xffffffffu, rescale && col_ok)) {
+#pragma unroll
+            for (int mb = 0; mb < NMB; ++mb) {
+                o[mb][0] *= alpha[0];
+                o[mb][1] *= alpha[1];
+                o[mb][2] *= alpha[0];
+                o[mb][3] *= alpha[1];
+            }
+            zacc[0] *= alpha[0];
+            zacc[1] *= alpha[1];
+            zacc[2] *= alpha[0];
+            zacc[3] *= alpha[1];
+        }
+        // probabilities (x16, clear of fp16 underflow) -> B fragment of the value MMA
+        const uint32_t t0 = movmatrix_trans(col_ok ? pack_half2(pA[0] * 16.f, pA[1] * 16.f) : 0u);
+        const uint32_t t1 = movmatrix_trans(col_ok ? pack_half2(pB[0] * 16.f, pB[1] * 16.f) : 0u);
+
+        // ------------------------------ values ------------------------------
+        {
+            // tokens of this thread's contraction slots: 4*tig .. 4*tig+3
+            uint32_t keep01 = 0xffffffffu, keep23 = 0xffffffffu;
+            if (valid < TQ_BLOCK_TOKENS) {   // never let stale bytes of unused slots in
+                keep01 = (4 * tig < valid ? 0x0000ffffu : 0u) | (4 * tig + 1 < valid ? 0xffff0000u : 0u);
+                keep23 = (4 * tig + 2 < valid ? 0x0000ffffu : 0u) | (4 * tig + 3 < valid ? 0xffff0000u : 0u);
+            }
+            const uint2* vsc = reinterpret_cast<const uint2*>(rec + L.off_vscale) + tig;   // [grp][16 tok] fp16: 4 uint2 per group
+            const uint2* vzr = reinterpret_cast<const uint2*>(rec + L.off_vzero) + tig;
+            // zero-point term: rows = groups
+            {
+                uint2 z = make_uint2(0u, 0u);
+                if (gid < NG) z = vzr[gid * 4];
+                mma16816(zacc, z.x & keep01, 0u, z.y & keep23, 0u, t0, t1);
+            }
+            const uint4* vcw = reinterpret_cast<const uint4*>(rec + L.off_vcodes) + lane;   // [chunk][lane] 16 B
+            if (VAL_BITS == 2) {
+                // word (p, gp): [tokA grp 2gp, tokA grp 2gp+1, tokB grp 2gp, tokB grp 2gp+1]
+                constexpr int NGP = NG / 2;
+                uint32_t w[2 * NGP];
+                if (NGP == 4) {
+                    const uint4 a = vcw[0], c = vcw[32];
+                    w[0] = a.x; w[1] = a.y; w[NGP - 2] = a.z; w[NGP - 1] = a.w;
+                    w[NGP] = c.x; w[NGP + 1] = c.y; w[2 * NGP - 2] = c.z; w[2 * NGP - 1] = c.w;
+                } else {
+                    const uint4 a = vcw[0];
+                    w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w;
+                }
+#pragma unroll
+                for (int gp = 0; gp < NGP; ++gp) {
+                    const uint32_t w0 = w[gp], w1 = w[NGP + gp];
+                    const uint32_t w0h = w0 >> 6, w1h = w1 >> 6;
+#pragma unroll
+                    for (int odd = 0; odd < 2; ++odd) {
+                        const int grp = 2 * gp + odd;
+                        const uint2 sc = vsc[grp * 4];
+                        const uint32_t bp0 = hmul2_sat(t0, sc.x & keep01), bp1 = hmul2_sat(t1, sc.y & keep23);
+#pragma unroll
+                        for (int hb = 0; hb < 2; ++hb) {   // the two M-blocks of the group
+                            const int i_lo = 2 * hb, i_hi = i_lo + 1;
+                            // even group: field i at bits 2i; odd group: i=0 at bits 8-9, i>=1 after >>6 at 2(i+1)
+                            const int p_lo = odd ? (i_lo == 0 ? 4 : i_lo + 1) : i_lo;
+                            const int p_hi = odd ? i_hi + 1 : i_hi;
+                            const bool sh_lo = odd && i_lo != 0, sh_hi = odd;
+                            const uint32_t mk_lo = 0x00030003u << (2 * p_lo), mk_hi = 0x00030003u << (2 * p_hi);
+                            mma16816(o[2 * grp + hb], (sh_lo ? w0h : w0) & mk_lo, (sh_hi ? w0h : w0) & mk_hi,
+                                     (sh_lo ? w1h : w1) & mk_lo, (sh_hi ? w1h : w1) & mk_hi, bp0, bp1);
+                        }
+                    }
+                }
+            } else {
+                // word (p, grp): [tokA byte0, tokA byte1, tokB byte0, tokB byte1]; byte0 = codes 0,1, byte1 = codes 2,3
+                uint32_t w[2 * NG];
+#pragma unroll
+                for (int c = 0; c < 2 * NG / 4; ++c) {
+                    const uint4 a = vcw[32 * c];
+                    w[4 * c] = a.x; w[4 * c + 1] = a.y; w[4 * c + 2] = a.z; w[4 * c + 3] = a.w;
+                }
+#pragma unroll
+                for (int grp = 0; grp < NG; ++grp) {
+                    const uint32_t w0 = w[grp], w1 = w[NG + grp];
+                    const uint32_t w0h = w0 >> 8, w1h = w1 >> 8;
+                    const uint2 sc = vsc[grp * 4];
+                    const uint32_t bp0 = hmul2_sat(t0, sc.x & keep01), bp1 = hmul2_sat(t1, sc.y & keep23);
+                    mma16816(o[2 * grp], w0 & 0x000f000fu, w0 & 0x00f000f0u, w1 & 0x000f000fu, w1 & 0x00f000f0u, bp0, bp1);
+                    mma16816(o[2 * grp + 1], w0h & 0x000f000fu, w0h & 0x00f000f0u, w1h & 0x000f000fu,
+                             w1h & 0x00f000f0u, bp0, bp1);
+                }
+            }
+        }
+
+        __syncwarp();
+        if (lane == 0 && it + NSTW < cnt) {   // refill the stage just consumed
+            tq_mbar_expect_tx(my_bar + st, (uint32_t)BB);
+            tq_bulk_g2s(my_stage + st * BB, p.pool + ((int64_t)bt_s[warp + 4 * (it + NSTW)] * p.H + h) * BB,
+                        (uint32_t)BB, my_bar + st);
+        }
+    }
+    if (failed && lane == 0) atomicCAS(p.status, 0, (int)TQ_ERR_TIMEOUT);
+
+    // ------------------------------ combine the four warps ------------------------------
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {   // row sums over the eight row groups
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 4);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 8);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 16);
+    }
+    // zero-point sums Z[grp][g] sit in lane (grp, tig); fetch the ones of this thread's rows
+    float zrow[NG][2];
+#pragma unroll
+    for (int grp = 0; grp < NG; ++grp) {
+        zrow[grp][0] = __shfl_sync(0xffffffffu, zacc[0], grp * 4 + tig);
+        zrow[grp][1] = __shfl_sync(0xffffffffu, zacc[1], grp * 4 + tig);
+    }
+    __syncthreads();   // every warp is done with its stages: reuse them
+    float* osm = reinterpret_cast<float*>(stages);   // [4 warps][GP][D]
+    if (col_ok) {
+#pragma unroll
+        for (int mb = 0; mb < NMB; ++mb) {
+            const int grp = mb >> 1, hb = mb & 1, odd = grp & 1;
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int i = 2 * hb + half;
+                int sh;   // A value = code * 2^(sh - 24); probabilities carried x16
+                if (VAL_BITS == 2) sh = 2 * (odd ? (i == 0 ? 4 : i + 1) : i);
+                else sh = 4 * (i & 1);
+                const float f = ldexpf(1.f, 24 - sh - 4);
+                const int d = 32 * grp + 4 * gid + i;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int g = 2 * tig + c;
+                    osm[(warp * GP + g) * D + d] = o[mb][2 * half + c] * f + zrow[grp][c] * 0.0625f;
+                }
+            }
+        }
+        if (gid == 0) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                ml[(warp * 2 + 0) * GP + 2 * tig + c] = m_run[c];
+                ml[(warp * 2 + 1) * GP + 2 * tig + c] = l_run[c];
+            }
+        }
+    }
+    __syncthreads();
+    {
+        float* mine = partial_ptr<D, GP>(p, b, h, x);
+        for (int i = tid; i < GP * D; i += DEC_THREADS) {
+            const int g = i / D, d = i % D;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) mx = fmaxf(mx, ml[(w * 2) * GP + g]);
+            float acc = 0.f, lsum = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float mw = ml[(w * 2) * GP + g];
+                if (mw != -INFINITY) {
+                    const float wt = exp2f(mw - mx);
+                    acc = fmaf(wt, osm[(w * GP + g) * D + d], acc);
+                    lsum = fmaf(wt, ml[(w * 2 + 1) * GP + g], lsum);
+                }
+            }
+            mine[2 * GP + g * D + d] = acc;
+            if (d == 0) {
+                mine[g] = mx * 0.6931471805599453f;   // back to the natural-log domain of the merge
+                mine[GP + g] = lsum;
+            }
+        }
+    }
+    ticket_and_merge<D, GP>(p, b, h, wsm);
+}
+
+template <int D, bool SPLITB>
+size_t mma_smem_bytes(int block_bytes, int nslot) {
+    constexpr int GP = SPLITB ? 8 : 4;
+    size_t s = (size_t)4 * NSTW * block_bytes;
+    s += sizeof(float) * (2 * GP * D + 4 * GP + 8 * GP + 2 * GP);
+    s += sizeof(int) * 256 + sizeof(uint64_t) * 4 * NSTW;
+    s += sizeof(float) * ((size_t)(nslot > 128 ? nslot : 128) * GP + 2 * GP);
+    return s;
+}
+
+template <int D, int VAL_BITS, bool SPLITB>
+int launch_mma(const DecodeParams& p, int batch, cudaStream_t st) {
+    const TqLayout L = tq_make_layout(D, 3, VAL_BITS);
+    const int nslot = p.num_splits + p.ring_splits;
+    const size_t smem = mma_smem_bytes<D, SPLITB>(L.block_bytes, nslot);
+    auto kern = tq_decode_mma_kernel<D, VAL_BITS, SPLITB>;
+    static size_t smem_set = 0;
+    if (smem > smem_set) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return TQ_ERR_CUDA;
+        smem_set = smem;
+    }
+    dim3 grid((unsigned)nslot, (unsigned)p.H, (unsigned)batch);
+    kern<<<grid, DEC_THREADS, smem, st>>>(p);
+    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
+}
+
+}  // namespace
+
+namespace tqdec {
+
+int tq_decode_mma_launch(const DecodeParams& p, int D, int mse_bits, int val_bits, int batch, int max_seq_len,
+                         cudaStream_t st, int* handled) {
+    *handled = 0;
+    if (mse_bits != 2) return TQ_OK;                 // 3-bit (nibble) codes: generic kernel
+    if (D == 256 && p.G > 4) return TQ_OK;           // would need two B-fragment sets of 32 registers
+    // the bit-plane form needs a code book that is affine in the two code bits
+    const float* c = p.cb.centroids;
+    if (fabsf(c[3] - c[2] - c[1] + c[0]) > 1e-6f * fabsf(c[3] - c[0])) return TQ_OK;
+    const int nblk = (max_seq_len + TQ_BLOCK_TOKENS - 1) / TQ_BLOCK_TOKENS;
+    if ((nblk + p.num_splits - 1) / p.num_splits + 1 > 256) return TQ_OK;   // block-table slice kept in shared memory
+    *handled = 1;
+    const bool split = p.G > 4;
+    if (D == 128) {
+        if (val_bits == 2) return split ? launch_mma<128, 2, true>(p, batch, st) : launch_mma<128, 2, false>(p, batch, st);
+        return split ? launch_mma<128, 4, true>(p, batch, st) : launch_mma<128, 4, false>(p, batch, st);
+    }
+    if (val_bits == 2) return launch_mma<256, 2, false>(p, batch, st);
+    return launch_mma<256, 4, false>(p, batch, st);
+}
+
+}  // namespace tqdec
