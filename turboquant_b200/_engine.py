@@ -178,11 +178,14 @@ def sm_count(device) -> int:
 
 
 def choose_splits(batch: int, num_kv_heads: int, max_seq_len: int, sms: int) -> int:
-    """Sequence splits per (sequence, kv head): about three CTAs per SM over the
-    whole launch, at least eight 16-token records per CTA (two per warp)."""
+    """Sequence splits per (sequence, kv head).  The decode kernel runs one
+    12-warp CTA per SM: with few (sequence, head) pairs the sequence is cut so
+    that every SM gets one CTA; with many pairs a CTA takes at most 512 records
+    (8192 tokens) so that long and short sequences balance out."""
     nblk = (max_seq_len + TQ_BLOCK_TOKENS - 1) // TQ_BLOCK_TOKENS
-    want = max(1, -(-3 * sms // max(1, batch * num_kv_heads)))
-    return max(1, min(want, nblk // 8))
+    pairs = max(1, batch * num_kv_heads)
+    want = max(sms // pairs, -(-nblk // 512), 1)
+    return max(1, min(want, max(1, nblk // 12)))
 
 
 def store(consts: LayerConstants, pool: BlockPool, key: torch.Tensor, value: torch.Tensor, *,

@@ -224,9 +224,7 @@ __global__ void __launch_bounds__(DEC_THREADS) tq_decode_kernel(const DecodePara
 
     // ------------------------------ exact ring ------------------------------
     __syncthreads();
-    ring_part<D, GP>(p, b, h, x - p.num_splits, qr, sp, pp, m_run, l_run, acc);
-    __syncthreads();
-    write_partial_regs<D, GP>(p, b, h, x, acc, m_run, l_run);
+    ring_part<D, GP>(p, b, h, x, qr, sp, pp, m_run);   // m_run, l_run are adjacent: [2*GP]
     ticket_and_merge<D, GP>(p, b, h, wsm);
 }
 

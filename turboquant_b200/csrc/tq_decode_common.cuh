@@ -145,11 +145,13 @@ __device__ __forceinline__ void write_partial_regs(const DecodeParams& p, int b,
 
 // After a CTA has written its partial: take a ticket; the last CTA of this
 // (sequence, kv head) merges all partials and writes the output.  Nobody waits.
+// Every partial is always fully written with finite numbers, so the merge is
+// branch free: a float4 of one head per thread, slots unrolled.
 template <int D, int GP>
 __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, int h,
                                                  float* wsm /* [max(nslot,128)*GP + 2*GP] */) {
     constexpr int PS = GP * (D + 2);
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, nt = blockDim.x;
     const int nslot = p.num_splits + p.ring_splits;
     __threadfence();
     __shared__ int s_last;
@@ -166,7 +168,7 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
     float* wL = wsm;             // [GP] global sum
     float* w = wsm + 2 * GP;     // [nslot][GP] weight of each partial
     const int warp = tid >> 5, lane = tid & 31;
-    for (int g = warp; g < GP; g += DEC_THREADS / 32) {
+    for (int g = warp; g < GP; g += nt / 32) {
         float mx = -INFINITY;
         for (int s = lane; s < nslot; s += 32) mx = fmaxf(mx, __ldcg(base + (int64_t)s * PS + g));
         mx = tq_warp_max(mx);
@@ -182,78 +184,106 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
         if (lane == 0) wL[g] = sum;
     }
     __syncthreads();
-    for (int i = tid; i < p.G * D; i += DEC_THREADS) {
-        const int g = i / D, d = i % D;
-        float o = 0.f;
-        for (int s = 0; s < nslot; ++s) {
+    for (int i = tid; i < p.G * (D / 4); i += nt) {
+        const int g = i / (D / 4), d = (i % (D / 4)) * 4;
+        const float4* src = reinterpret_cast<const float4*>(base + 2 * GP + g * D + d);   // PS*4 and (2GP+gD+d)*4 are multiples of 16
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        int s = 0;
+        for (; s + 8 <= nslot; s += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) v[u] = __ldcg(src + (int64_t)(s + u) * (PS / 4));
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const float ws = w[(s + u) * GP + g];
+                o.x = fmaf(ws, v[u].x, o.x);
+                o.y = fmaf(ws, v[u].y, o.y);
+                o.z = fmaf(ws, v[u].z, o.z);
+                o.w = fmaf(ws, v[u].w, o.w);
+            }
+        }
+        for (; s < nslot; ++s) {
+            const float4 v = __ldcg(src + (int64_t)s * (PS / 4));
             const float ws = w[s * GP + g];
-            if (ws != 0.f) o = fmaf(ws, __ldcg(base + (int64_t)s * PS + 2 * GP + g * D + d), o);
+            o.x = fmaf(ws, v.x, o.x);
+            o.y = fmaf(ws, v.y, o.y);
+            o.z = fmaf(ws, v.z, o.z);
+            o.w = fmaf(ws, v.w, o.w);
         }
         const float l = wL[g];
-        tq_store_any(p.out, ((int64_t)b * p.Qh + h * p.G + g) * D + d, l > 0.f ? o / l : 0.f, p.q_dtype);
+        const float inv = l > 0.f ? 1.f / l : 0.f;
+        const int64_t dst = ((int64_t)b * p.Qh + h * p.G + g) * D + d;
+        tq_store_any(p.out, dst + 0, o.x * inv, p.q_dtype);
+        tq_store_any(p.out, dst + 1, o.y * inv, p.q_dtype);
+        tq_store_any(p.out, dst + 2, o.z * inv, p.q_dtype);
+        tq_store_any(p.out, dst + 3, o.w * inv, p.q_dtype);
     }
     if (tid == 0) p.tickets[b * p.H + h] = 0;  // ready for the next launch
 }
 
 // Exact attention over this CTA's slice of the ring (up to RING_TOK tokens),
-// fp32 like the reference's matmul path (score.py:154-170).  Leaves the partial
-// in (acc, m_run, l_run).  scratch: qf [D][GP], sc [GP][RING_TOK], pp [RING_TOK][GP].
+// fp32 like the reference's matmul path (score.py:154-170); works for any
+// block size.  Writes the CTA's partial itself.
+// scratch: qf [D][GP], sc [GP][RING_TOK], pp [RING_TOK][GP], ml [2*GP].
 template <int D, int GP>
-__device__ __forceinline__ void ring_part(const DecodeParams& p, int b, int h, int rs, float* qf, float* sc,
-                                          float* pp, float* m_run, float* l_run,
-                                          float (&acc)[GP][D / DEC_THREADS]) {
-    constexpr int DPT = D / DEC_THREADS;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+__device__ __forceinline__ void ring_part(const DecodeParams& p, int b, int h, int slot_idx, float* qf, float* sc,
+                                          float* pp, float* ml) {
+    const int tid = threadIdx.x, nt = blockDim.x, warp = tid >> 5, lane = tid & 31;
+    const int rs = slot_idx - p.num_splits;
     const int R = p.ring_lens ? p.ring_lens[b] : 0;
     const int r0 = rs * RING_TOK;
     const int nr = max(0, min(RING_TOK, R - r0));
-    if (nr <= 0) return;
-    for (int i = tid; i < D * GP; i += DEC_THREADS) {
-        const int j = i / GP, g = i % GP;
-        qf[i] = g < p.G ? tq_load_any(p.query, ((int64_t)b * p.Qh + h * p.G + g) * D + j, p.q_dtype) : 0.f;
+    float* mine = partial_ptr<D, GP>(p, b, h, slot_idx);
+    if (tid < GP) {
+        ml[tid] = -INFINITY;
+        ml[GP + tid] = 0.f;
+    }
+    if (nr > 0) {
+        for (int i = tid; i < D * GP; i += nt) {
+            const int j = i / GP, g = i % GP;
+            qf[i] = g < p.G ? tq_load_any(p.query, ((int64_t)b * p.Qh + h * p.G + g) * D + j, p.q_dtype) : 0.f;
+        }
+        __syncthreads();
+        for (int t = warp; t < nr; t += nt / 32) {
+            const int64_t off = (int64_t)b * p.ring_stride_seq + (int64_t)(r0 + t) * p.ring_stride_token + (int64_t)h * D;
+            float a[GP];
+#pragma unroll
+            for (int g = 0; g < GP; ++g) a[g] = 0.f;
+            for (int j = lane; j < D; j += 32) {
+                const float kx = tq_load_any(p.ring_k, off + j, p.ring_dtype);
+#pragma unroll
+                for (int g = 0; g < GP; ++g) a[g] = fmaf(qf[j * GP + g], kx, a[g]);
+            }
+#pragma unroll
+            for (int g = 0; g < GP; ++g) {
+                const float s = tq_warp_sum(a[g]);
+                if (lane == 0) sc[g * RING_TOK + t] = s * p.scale;
+            }
+        }
+        __syncthreads();
+        for (int g = warp; g < GP; g += nt / 32) {
+            const float s0 = lane < nr ? sc[g * RING_TOK + lane] : -INFINITY;
+            const float m_new = tq_warp_max(s0);
+            const float p0 = (s0 == -INFINITY) ? 0.f : __expf(s0 - m_new);
+            const float sum = tq_warp_sum(p0);
+            pp[lane * GP + g] = p0;
+            if (lane == 0) {
+                ml[g] = m_new;
+                ml[GP + g] = sum;
+            }
+        }
     }
     __syncthreads();
-    for (int t = warp; t < nr; t += DEC_THREADS / 32) {
-        const int64_t off = (int64_t)b * p.ring_stride_seq + (int64_t)(r0 + t) * p.ring_stride_token + (int64_t)h * D;
-        float a[GP];
-#pragma unroll
-        for (int g = 0; g < GP; ++g) a[g] = 0.f;
-        for (int j = lane; j < D; j += 32) {
-            const float kx = tq_load_any(p.ring_k, off + j, p.ring_dtype);
-#pragma unroll
-            for (int g = 0; g < GP; ++g) a[g] = fmaf(qf[j * GP + g], kx, a[g]);
+    for (int i = tid; i < GP * D; i += nt) {
+        const int g = i / D, d = i % D;
+        float acc = 0.f;
+        for (int t = 0; t < nr; ++t) {
+            const int64_t off = (int64_t)b * p.ring_stride_seq + (int64_t)(r0 + t) * p.ring_stride_token + (int64_t)h * D + d;
+            acc = fmaf(pp[t * GP + g], tq_load_any(p.ring_v, off, p.ring_dtype), acc);
         }
-#pragma unroll
-        for (int g = 0; g < GP; ++g) {
-            const float s = tq_warp_sum(a[g]);
-            if (lane == 0) sc[g * RING_TOK + t] = s * p.scale;
-        }
+        mine[2 * GP + i] = acc;
     }
-    __syncthreads();
-    for (int g = warp; g < GP; g += DEC_THREADS / 32) {
-        const float s0 = lane < nr ? sc[g * RING_TOK + lane] : -INFINITY;
-        const float m_new = tq_warp_max(s0);
-        const float p0 = (s0 == -INFINITY) ? 0.f : __expf(s0 - m_new);
-        const float sum = tq_warp_sum(p0);
-        pp[lane * GP + g] = p0;
-        if (lane == 0) {
-            m_run[g] = m_new;
-            l_run[g] = sum;
-        }
-    }
-    __syncthreads();
-    const int d0 = tid * DPT;
-    for (int t = 0; t < nr; ++t) {
-        const int64_t off = (int64_t)b * p.ring_stride_seq + (int64_t)(r0 + t) * p.ring_stride_token + (int64_t)h * D + d0;
-        float v[DPT];
-#pragma unroll
-        for (int i = 0; i < DPT; ++i) v[i] = tq_load_any(p.ring_v, off + i, p.ring_dtype);
-        const float* pt = pp + t * GP;
-#pragma unroll
-        for (int g = 0; g < GP; ++g)
-#pragma unroll
-            for (int i = 0; i < DPT; ++i) acc[g][i] = fmaf(pt[g], v[i], acc[g][i]);
-    }
+    if (tid < 2 * GP) mine[tid] = ml[tid];
 }
 
 // Launcher of the tensor-core kernel (tq_decode_mma.cu); *handled = 0 when the

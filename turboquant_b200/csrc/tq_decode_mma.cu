@@ -31,7 +31,12 @@ using namespace tqdec;
 
 namespace {
 
-constexpr int NSTW = 4;  // bulk-copy stages per warp, one block record each
+constexpr int NSTW = 4;    // bulk-copy stages per warp, one block record each
+constexpr int NW = 12;     // warps per CTA; one CTA per SM
+constexpr int NT = NW * 32;
+constexpr int BT_MAX = 1024;   // block-table entries a CTA keeps in shared memory
+
+__device__ __forceinline__ float pow2i(int e) { return __int_as_float((127 + e) << 23); }   // 2^e, -126 <= e <= 127
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                          uint32_t b0, uint32_t b1) {
@@ -64,26 +69,23 @@ __host__ __device__ constexpr int sign_bit(int wi, int j) { return j + 8 * (wi &
 __host__ __device__ constexpr int sign_pos(int b) { return b <= 9 ? b : b - 6; }
 
 template <int D, int VAL_BITS, bool SPLITB>
-__global__ void __launch_bounds__(DEC_THREADS, 3) tq_decode_mma_kernel(const DecodeParams p) {
+__global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams p) {
     constexpr int GP = SPLITB ? 8 : 4;
     constexpr int KS = D / 16;    // score k-steps
     constexpr int NWK = D / 64;   // code words per thread per token
     constexpr int NMB = D / 16;   // value M-blocks
     constexpr int NG = D / 32;
-    constexpr int DPT = D / DEC_THREADS;
     const TqLayout L = tq_make_layout(D, 3, VAL_BITS);
     const int BB = L.block_bytes;
 
     extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t* stages = smem;                                              // [4 warps][NSTW][BB]; reused after the loop
-    float* qsm = reinterpret_cast<float*>(smem + 4 * NSTW * BB);         // [2][GP][D] rotated / sketched query
+    uint8_t* stages = smem;                                              // [NW warps][NSTW][BB]; reused after the loop
+    float* qsm = reinterpret_cast<float*>(smem + NW * NSTW * BB);        // [2][GP][D] rotated / sketched query
     float* cst = qsm + 2 * GP * D;                                       // [4][GP]: exponent e_rot, e_sk, sums q_rot, q_sk
-    float* ml = cst + 4 * GP;                                            // [4 warps][2][GP]
-    float* m_run_s = ml + 8 * GP;                                        // [GP] (ring part / combined partial)
-    float* l_run_s = m_run_s + GP;                                       // [GP]
-    int* bt_s = reinterpret_cast<int*>(l_run_s + GP);                    // [256] physical blocks of this CTA
-    uint64_t* bars = reinterpret_cast<uint64_t*>(bt_s + 256);            // [4][NSTW]
-    float* wsm = reinterpret_cast<float*>(bars + 4 * NSTW);              // merge scratch
+    float* ml = cst + 4 * GP;                                            // [NW warps][2][GP]
+    int* bt_s = reinterpret_cast<int*>(ml + 2 * NW * GP);                // [BT_MAX] physical blocks of this CTA
+    uint64_t* bars = reinterpret_cast<uint64_t*>(bt_s + BT_MAX);         // [NW][NSTW]
+    float* wsm = reinterpret_cast<float*>(bars + NW * NSTW);             // merge scratch
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tig = lane & 3;
@@ -91,21 +93,8 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) tq_decode_mma_kernel(const Dec
 
     if (x >= p.num_splits) {
         // exact ring tokens: CUDA-core fp32 path shared with the generic kernel
-        float acc[GP][DPT];
-#pragma unroll
-        for (int g = 0; g < GP; ++g)
-#pragma unroll
-            for (int i = 0; i < DPT; ++i) acc[g][i] = 0.f;
-        if (tid < GP) {
-            m_run_s[tid] = -INFINITY;
-            l_run_s[tid] = 0.f;
-        }
-        __syncthreads();
         float* scratch = reinterpret_cast<float*>(stages);
-        ring_part<D, GP>(p, b, h, x - p.num_splits, scratch, scratch + D * GP, scratch + D * GP + GP * RING_TOK,
-                         m_run_s, l_run_s, acc);
-        __syncthreads();
-        write_partial_regs<D, GP>(p, b, h, x, acc, m_run_s, l_run_s);
+        ring_part<D, GP>(p, b, h, x, scratch, scratch + D * GP, scratch + D * GP + GP * RING_TOK, ml);
         ticket_and_merge<D, GP>(p, b, h, wsm);
         return;
     }
@@ -116,12 +105,12 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) tq_decode_mma_kernel(const Dec
     const int nblk = (n + TQ_BLOCK_TOKENS - 1) / TQ_BLOCK_TOKENS;
     const int blk0 = (int)((int64_t)x * nblk / p.num_splits);
     const int blk1 = (int)((int64_t)(x + 1) * nblk / p.num_splits);
-    const int nmine = min(blk1 - blk0, 256);   // host guarantees <= 256 blocks per split
-    const int cnt = nmine > warp ? (nmine - warp + 3) / 4 : 0;   // records of this warp
+    const int nmine = min(blk1 - blk0, BT_MAX);   // the launcher guarantees <= BT_MAX blocks per split
+    const int cnt = nmine > warp ? (nmine - warp + NW - 1) / NW : 0;   // records of this warp
 
     // block table slice and barriers first, so the copies overlap the query set-up
     const int32_t* bt = p.block_table + (int64_t)b * p.bt_stride;
-    for (int i = tid; i < nmine; i += DEC_THREADS) {
+    for (int i = tid; i < nmine; i += NT) {
         int phys = bt[blk0 + i];
         if (phys < 0 || phys >= p.num_blocks) {
             atomicCAS(p.status, 0, (int)TQ_ERR_RANGE);
@@ -130,7 +119,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) tq_decode_mma_kernel(const Dec
         bt_s[i] = phys;
     }
     if (tid == 0) {
-        for (int s = 0; s < 4 * NSTW; ++s) tq_mbar_init(bars + s, 1);
+        for (int s = 0; s < NW * NSTW; ++s) tq_mbar_init(bars + s, 1);
         tq_mbar_fence_init();
     }
     __syncthreads();
@@ -139,22 +128,22 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) tq_decode_mma_kernel(const Dec
     if (lane == 0) {
         for (int i = 0; i < NSTW && i < cnt; ++i) {
             tq_mbar_expect_tx(my_bar + i, (uint32_t)BB);
-            tq_bulk_g2s(my_stage + i * BB, p.pool + ((int64_t)bt_s[warp + 4 * i] * p.H + h) * BB, (uint32_t)BB,
+            tq_bulk_g2s(my_stage + i * BB, p.pool + ((int64_t)bt_s[warp + NW * i] * p.H + h) * BB, (uint32_t)BB,
                         my_bar + i);
         }
     }
 
     // ---- query fragments ----
-    for (int i = tid; i < 2 * GP * D; i += DEC_THREADS) {
+    for (int i = tid; i < 2 * GP * D; i += NT) {
         const int which = i / (GP * D), g = (i / D) % GP, j = i % D;
         qsm[i] = g < p.G ? p.qprep[((int64_t)(b * p.Qh + h * p.G + g) * 2 + which) * D + j] : 0.f;
     }
     __syncthreads();
-    for (int row = warp; row < 2 * GP; row += 4) {   // power-of-two scale per query row
+    for (int row = warp; row < 2 * GP; row += NW) {   // power-of-two scale per query row
         float mx = 0.f;
         for (int j = lane; j < D; j += 32) mx = fmaxf(mx, fabsf(qsm[row * D + j]));
         mx = tq_warp_max(mx);
-        if (lane == 0) cst[row] = (mx > 0.f && mx < 3.0e38f) ? (float)(14 - ilogbf(mx)) : 0.f;
+        if (lane == 0) cst[row] = (mx > 0.f && mx < 3.0e38f) ? (float)max(-100, min(100, 14 - ilogbf(mx))) : 0.f;
     }
     __syncthreads();
 
@@ -168,22 +157,26 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) tq_decode_mma_kernel(const Dec
         const int e_a = (int)cst[(is_sk ? GP : 0) + g_rot];
         const float* src_b = qsm + (GP + g_rot) * D;
         const int e_b = (int)cst[GP + g_rot];
+        const float fa = pow2i(e_a), fa_inv = pow2i(-e_a), fb = pow2i(e_b), fb_inv = pow2i(-e_b);
         float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
         for (int r = 0; r < 2 * KS; ++r) {
             const int wi = r >> 3, j = r & 7;
             const int d_lo = (D / 4) * tig + 16 * wi + j, d_hi = d_lo + 8;
             const int sh_code = 2 * code_pos(j), sh_sign = sign_pos(sign_bit(wi, j));
-            const int sh = is_sk ? sh_sign : sh_code;
-            const __half lo = __float2half_rn(ldexpf(src_a[d_lo], e_a - sh));
-            const __half hi = __float2half_rn(ldexpf(src_a[d_hi], e_a - sh));
-            sum_a += ldexpf(__half2float(lo) + __half2float(hi), sh - e_a);
+            // value stored = q * 2^(e - sh); sh is a compile-time constant after unrolling
+            const float dn_code = 1.f / (float)(1 << sh_code), dn_sign = 1.f / (float)(1 << sh_sign);
+            const float up_code = (float)(1 << sh_code), up_sign = (float)(1 << sh_sign);
+            const float dn = is_sk ? dn_sign : dn_code, up = is_sk ? up_sign : up_code;
+            const __half lo = __float2half_rn(src_a[d_lo] * fa * dn);
+            const __half hi = __float2half_rn(src_a[d_hi] * fa * dn);
+            sum_a += (__half2float(lo) + __half2float(hi)) * up * fa_inv;
             const __half2 v = __halves2half2(lo, hi);
             bq[r] = *reinterpret_cast<const uint32_t*>(&v);
             if (SPLITB) {
-                const __half lo2 = __float2half_rn(ldexpf(src_b[d_lo], e_b - sh_sign));
-                const __half hi2 = __float2half_rn(ldexpf(src_b[d_hi], e_b - sh_sign));
-                sum_b += ldexpf(__half2float(lo2) + __half2float(hi2), sh_sign - e_b);
+                const __half lo2 = __float2half_rn(src_b[d_lo] * fb * dn_sign);
+                const __half hi2 = __float2half_rn(src_b[d_hi] * fb * dn_sign);
+                sum_b += (__half2float(lo2) + __half2float(hi2)) * up_sign * fb_inv;
                 const __half2 v2 = __halves2half2(lo2, hi2);
                 bsk[r] = *reinterpret_cast<const uint32_t*>(&v2);
             }
@@ -214,9 +207,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) tq_decode_mma_kernel(const Dec
             const int g = (2 * tig + i) & (GP - 1);
             const int e_rot = (int)cst[g], e_sk = (int)cst[GP + g];
             k0[i] = c0 * cst[2 * GP + g];
-            k1[i] = ldexpf(c2 - c0, 23 - e_rot);
-            kb0[i] = ldexpf(c1 - c0, 24 - e_rot);
-            ksg[i] = ldexpf(1.f, 25 - e_sk);
+            k1[i] = (c2 - c0) * pow2i(23 - e_rot);
+            kb0[i] = (c1 - c0) * pow2i(24 - e_rot);
+            ksg[i] = pow2i(25 - e_sk);
             kq[i] = cst[3 * GP + g];
         }
     }
@@ -244,7 +237,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) tq_decode_mma_kernel(const Dec
             break;
         }
         const uint8_t* rec = my_stage + st * BB;
-        const int blk = blk0 + warp + 4 * it;
+        const int blk = blk0 + warp + NW * it;
         const int valid = min(TQ_BLOCK_TOKENS, n - blk * TQ_BLOCK_TOKENS);
 
         // ------------------------------ scores ------------------------------
@@ -421,13 +414,13 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) tq_decode_mma_kernel(const Dec
         __syncwarp();
         if (lane == 0 && it + NSTW < cnt) {   // refill the stage just consumed
             tq_mbar_expect_tx(my_bar + st, (uint32_t)BB);
-            tq_bulk_g2s(my_stage + st * BB, p.pool + ((int64_t)bt_s[warp + 4 * (it + NSTW)] * p.H + h) * BB,
+            tq_bulk_g2s(my_stage + st * BB, p.pool + ((int64_t)bt_s[warp + NW * (it + NSTW)] * p.H + h) * BB,
                         (uint32_t)BB, my_bar + st);
         }
     }
     if (failed && lane == 0) atomicCAS(p.status, 0, (int)TQ_ERR_TIMEOUT);
 
-    // ------------------------------ combine the four warps ------------------------------
+    // ------------------------------ combine the warps of the CTA ------------------------------
 #pragma unroll
     for (int i = 0; i < 2; ++i) {   // row sums over the eight row groups
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 4);
@@ -442,7 +435,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) tq_decode_mma_kernel(const Dec
         zrow[grp][1] = __shfl_sync(0xffffffffu, zacc[1], grp * 4 + tig);
     }
     __syncthreads();   // every warp is done with its stages: reuse them
-    float* osm = reinterpret_cast<float*>(stages);   // [4 warps][GP][D]
+    float* osm = reinterpret_cast<float*>(stages);   // [NW warps][GP][D]
     if (col_ok) {
 #pragma unroll
         for (int mb = 0; mb < NMB; ++mb) {
@@ -453,7 +446,7 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) tq_decode_mma_kernel(const Dec
                 int sh;   // A value = code * 2^(sh - 24); probabilities carried x16
                 if (VAL_BITS == 2) sh = 2 * (odd ? (i == 0 ? 4 : i + 1) : i);
                 else sh = 4 * (i & 1);
-                const float f = ldexpf(1.f, 24 - sh - 4);
+                const float f = pow2i(24 - sh - 4);
                 const int d = 32 * grp + 4 * gid + i;
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
@@ -473,14 +466,14 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) tq_decode_mma_kernel(const Dec
     __syncthreads();
     {
         float* mine = partial_ptr<D, GP>(p, b, h, x);
-        for (int i = tid; i < GP * D; i += DEC_THREADS) {
+        for (int i = tid; i < GP * D; i += NT) {
             const int g = i / D, d = i % D;
             float mx = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < 4; ++w) mx = fmaxf(mx, ml[(w * 2) * GP + g]);
+            for (int w = 0; w < NW; ++w) mx = fmaxf(mx, ml[(w * 2) * GP + g]);
             float acc = 0.f, lsum = 0.f;
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
+            for (int w = 0; w < NW; ++w) {
                 const float mw = ml[(w * 2) * GP + g];
                 if (mw != -INFINITY) {
                     const float wt = exp2f(mw - mx);
@@ -501,9 +494,9 @@ __global__ void __launch_bounds__(DEC_THREADS, 3) tq_decode_mma_kernel(const Dec
 template <int D, bool SPLITB>
 size_t mma_smem_bytes(int block_bytes, int nslot) {
     constexpr int GP = SPLITB ? 8 : 4;
-    size_t s = (size_t)4 * NSTW * block_bytes;
-    s += sizeof(float) * (2 * GP * D + 4 * GP + 8 * GP + 2 * GP);
-    s += sizeof(int) * 256 + sizeof(uint64_t) * 4 * NSTW;
+    size_t s = (size_t)NW * NSTW * block_bytes;
+    s += sizeof(float) * (2 * GP * D + 4 * GP + 2 * NW * GP);
+    s += sizeof(int) * BT_MAX + sizeof(uint64_t) * NW * NSTW;
     s += sizeof(float) * ((size_t)(nslot > 128 ? nslot : 128) * GP + 2 * GP);
     return s;
 }
@@ -521,7 +514,7 @@ int launch_mma(const DecodeParams& p, int batch, cudaStream_t st) {
         smem_set = smem;
     }
     dim3 grid((unsigned)nslot, (unsigned)p.H, (unsigned)batch);
-    kern<<<grid, DEC_THREADS, smem, st>>>(p);
+    kern<<<grid, NT, smem, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 
@@ -538,7 +531,7 @@ int tq_decode_mma_launch(const DecodeParams& p, int D, int mse_bits, int val_bit
     const float* c = p.cb.centroids;
     if (fabsf(c[3] - c[2] - c[1] + c[0]) > 1e-6f * fabsf(c[3] - c[0])) return TQ_OK;
     const int nblk = (max_seq_len + TQ_BLOCK_TOKENS - 1) / TQ_BLOCK_TOKENS;
-    if ((nblk + p.num_splits - 1) / p.num_splits + 1 > 256) return TQ_OK;   // block-table slice kept in shared memory
+    if ((nblk + p.num_splits - 1) / p.num_splits + 1 > BT_MAX) return TQ_OK;   // block-table slice kept in shared memory
     *handled = 1;
     const bool split = p.G > 4;
     if (D == 128) {
