@@ -133,7 +133,7 @@ class Runner:
         from turboquant_b200 import _engine as E
         self.E, self.dev = E, dev
         self.layers = [Layer(i, rank, dev) for i in range(WL["layers"])]
-        self.splits = E.choose_splits(1, WL["H"], WL["N"], E.sm_count(dev))
+        self.splits = E.choose_splits(1, WL["H"], WL["N"], E.sm_count(dev), WL["ring"])
         self.launches = 0      # kernels of this library
         self.tokens = 0        # KV tokens attended
         self.bytes = 0         # algorithmic bytes of the decode kernel
@@ -398,7 +398,7 @@ def run_ours(args):
                        "splits_per_kv_head": runner.splits, "steps_replayed_from": "CUDA graphs",
                        "parallelism": f"dp{world} (independent sequences per GPU, no collective on the data path)"},
             "hbm_gbs": dec_bytes / ms / 1e6 * world,
-            "roofline": {"bound": "hbm", "kernel": "tq_decode_kernel", "achieved": achieved, "peak": peak,
+            "roofline": {"bound": "hbm", "kernel": "tq_decode_mma_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                          "frac_of_nominal_8TBs": achieved / 8000.0, "us_per_launch": kern_ms * 1e3,
                          "bytes_per_launch": bytes_per_launch, "traffic": None},

@@ -177,14 +177,15 @@ def sm_count(device) -> int:
     return _SM_COUNT[idx]
 
 
-def choose_splits(batch: int, num_kv_heads: int, max_seq_len: int, sms: int) -> int:
+def choose_splits(batch: int, num_kv_heads: int, max_seq_len: int, sms: int, max_ring_len: int = 0) -> int:
     """Sequence splits per (sequence, kv head).  The decode kernel runs one
     12-warp CTA per SM: with few (sequence, head) pairs the sequence is cut so
     that every SM gets one CTA; with many pairs a CTA takes at most 512 records
     (8192 tokens) so that long and short sequences balance out."""
     nblk = (max_seq_len + TQ_BLOCK_TOKENS - 1) // TQ_BLOCK_TOKENS
     pairs = max(1, batch * num_kv_heads)
-    want = max(sms // pairs, -(-nblk // 512), 1)
+    ring_ctas = (max_ring_len + 31) // 32          # the ring tokens take CTAs of their own: keep it one wave
+    want = max(sms // pairs - ring_ctas, -(-nblk // 512), 1)
     return max(1, min(want, max(1, nblk // 12)))
 
 
@@ -219,7 +220,7 @@ def decode(consts: LayerConstants, pool: BlockPool, ws: Workspace, query: torch.
     if scale is None:
         scale = 1.0 / math.sqrt(d)
     h = pool.num_kv_heads
-    splits = num_splits or choose_splits(b, h, max_seq_len, sm_count(consts.device))
+    splits = num_splits or choose_splits(b, h, max_seq_len, sm_count(consts.device), max_ring_len)
     need = C.c_size_t(0)
     check(lib().tq_decode_workspace_bytes(C.byref(consts.cfg), b, qh, h, splits, C.byref(need)),
           "tq_decode_workspace_bytes")

@@ -19,48 +19,88 @@ using namespace tqdec;
 namespace {
 
 // q_rot = q @ Pi^T and q_sketch = q @ S^T.  One CTA = 32 output columns of one
-// matrix for up to 4 query vectors; 8 warps split the contraction.
-__global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ q, int dt, int64_t nvec, int D,
+// matrix for up to 4 query vectors; 8 warps split the contraction.  Besides the
+// fp32 result it can emit the fp16 MMA fragments of the tensor-core decode
+// kernel directly: every entry is scaled by a power of two derived from the
+// query's norm alone (|q Pi^T|_inf <= |q|_2 and |q S^T|_inf <= 2 sqrt(D) |q|_2
+// for a Gaussian S), so no CTA needs another CTA's columns.
+template <int D>
+__global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ q, int dt, int64_t nvec,
                                                        const float* __restrict__ pi_t,
-                                                       const float* __restrict__ s_t, float* __restrict__ out) {
-    extern __shared__ float qsm[];        // [4][D] queries, then [8][4][32] partial sums
-    float* red = qsm + 4 * D;
+                                                       const float* __restrict__ s_t, float* __restrict__ out,
+                                                       uint32_t* __restrict__ frag, int G, int Qh) {
+    __shared__ float qsm[4 * D];          // queries
+    __shared__ float red[8 * 4 * 32];     // partial sums
+    __shared__ float qn2[4];              // squared norms
     const int64_t v0 = (int64_t)blockIdx.y * 4;
     const int nv = (int)min((int64_t)4, nvec - v0);
-    const int chunks = D / 32;
+    constexpr int chunks = D / 32;
     const int which = blockIdx.x / chunks;            // 0: Pi^T, 1: S^T
-    const int col = (blockIdx.x % chunks) * 32 + (threadIdx.x & 31);
-    const int ks = threadIdx.x >> 5;
+    const int chunk = blockIdx.x % chunks;
+    const int lane = threadIdx.x & 31, ks = threadIdx.x >> 5;
+    const int col = chunk * 32 + lane;
     const float* __restrict__ m = which ? s_t : pi_t;
     for (int i = threadIdx.x; i < 4 * D; i += 256) {
         const int v = i / D;
         qsm[i] = v < nv ? tq_load_any(q, (v0 + v) * D + (i % D), dt) : 0.f;
     }
     __syncthreads();
+    if (ks < 4) {
+        float s2 = 0.f;
+        for (int j = lane; j < D; j += 32) s2 = fmaf(qsm[ks * D + j], qsm[ks * D + j], s2);
+        s2 = tq_warp_sum(s2);
+        if (lane == 0) qn2[ks] = s2;
+    }
     float a[4] = {0.f, 0.f, 0.f, 0.f};
     const int k0 = ks * (D / 8);
-#pragma unroll 8
-    for (int k = k0; k < k0 + D / 8; ++k) {
-        const float mv = __ldg(m + (size_t)k * D + col);
+    float mv[D / 8];
 #pragma unroll
-        for (int v = 0; v < 4; ++v) a[v] = fmaf(qsm[v * D + k], mv, a[v]);
+    for (int k = 0; k < D / 8; ++k) mv[k] = __ldg(m + (size_t)(k0 + k) * D + col);
+#pragma unroll
+    for (int k = 0; k < D / 8; ++k) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) a[v] = fmaf(qsm[v * D + k0 + k], mv[k], a[v]);
     }
 #pragma unroll
-    for (int v = 0; v < 4; ++v) red[(ks * 4 + v) * 32 + (threadIdx.x & 31)] = a[v];
+    for (int v = 0; v < 4; ++v) red[(ks * 4 + v) * 32 + lane] = a[v];
     __syncthreads();
     if (threadIdx.x < 128) {
-        const int v = threadIdx.x >> 5, c = threadIdx.x & 31;
+        const int v = threadIdx.x >> 5;
         float t = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t += red[(i * 4 + v) * 32 + c];
-        if (v < nv) out[((v0 + v) * 2 + which) * D + (blockIdx.x % chunks) * 32 + c] = t;
+        for (int i = 0; i < 8; ++i) t += red[(i * 4 + v) * 32 + lane];
+        if (v < nv) {
+            out[((v0 + v) * 2 + which) * D + col] = t;
+            if (frag != nullptr) {
+                const int64_t vec = v0 + v;
+                const int qh = (int)(vec % Qh), g = qh % G;
+                const int64_t pair = (vec / Qh) * (Qh / G) + qh / G;   // (sequence, kv head)
+                uint32_t* base = frag + pair * qf_words(D, G);
+                const float bound = sqrtf(qn2[v]) * (which ? 2.f * sqrtf((float)D) : 1.f);
+                int e = 0;
+                if (bound > 0.f && bound < 3.0e38f) e = max(-100, min(100, 14 - ilogbf(bound)));
+                if (chunk == 0 && lane == 0) reinterpret_cast<float*>(base)[which * 8 + g] = (float)e;
+                const int tig = col / (D / 4), rem = col % (D / 4);
+                const int wi = rem >> 4, half = (rem >> 3) & 1, jf = rem & 7;
+                const int r = wi * 8 + jf;
+                const int sh = which ? sign_pos(sign_bit(wi, jf)) : 2 * code_pos(jf);
+                const bool split = G > 4;
+                const int gid = split ? g : g + 4 * which;
+                const int set = split ? which : 0;
+                __half* dst = reinterpret_cast<__half*>(base + QF_HDR + ((set * (D / 8) + r) * 32 + gid * 4 + tig));
+                dst[half] = __float2half_rn(t * __int_as_float((127 + e - sh) << 23));
+            }
+        }
     }
 }
 
 int launch_qprep(const void* q, int dt, int64_t nvec, int D, const float* pi_t, const float* s_t, float* out,
-                 cudaStream_t st) {
+                 uint32_t* frag, int G, int Qh, cudaStream_t st) {
     dim3 grid((unsigned)(2 * D / 32), (unsigned)((nvec + 3) / 4));
-    tq_qprep_kernel<<<grid, 256, (4 * D + 8 * 4 * 32) * sizeof(float), st>>>(q, dt, nvec, D, pi_t, s_t, out);
+    if (D == 128)
+        tq_qprep_kernel<128><<<grid, 256, 0, st>>>(q, dt, nvec, pi_t, s_t, out, frag, G, Qh);
+    else
+        tq_qprep_kernel<256><<<grid, 256, 0, st>>>(q, dt, nvec, pi_t, s_t, out, frag, G, Qh);
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 
@@ -326,7 +366,7 @@ int launch_decode_g(const DecodeParams& p, int B, int block_bytes, cudaStream_t 
 }
 
 struct WsLayout {
-    size_t off_tickets, off_qprep, off_partials, total;
+    size_t off_tickets, off_qprep, off_qfrag, off_partials, total;
 };
 
 WsLayout decode_ws_layout(int D, int B, int Qh, int H, int max_slots) {
@@ -335,7 +375,8 @@ WsLayout decode_ws_layout(int D, int B, int Qh, int H, int max_slots) {
     const int GP = G <= 4 ? 4 : 8;
     w.off_tickets = TQ_WS_HEADER_BYTES;
     w.off_qprep = w.off_tickets + (((size_t)B * H * sizeof(int32_t) + 255) / 256) * 256;
-    w.off_partials = w.off_qprep + (((size_t)B * Qh * 2 * D * sizeof(float) + 255) / 256) * 256;
+    w.off_qfrag = w.off_qprep + (((size_t)B * Qh * 2 * D * sizeof(float) + 255) / 256) * 256;
+    w.off_partials = w.off_qfrag + (((size_t)B * H * qf_words(D, G) * sizeof(uint32_t) + 255) / 256) * 256;
     w.total = w.off_partials + (size_t)B * H * max_slots * GP * (D + 2) * sizeof(float);
     return w;
 }
@@ -404,9 +445,11 @@ extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_
 
     uint8_t* ws = (uint8_t*)a->workspace;
     float* qprep = (float*)(ws + w.off_qprep);
+    uint32_t* qfrag = (uint32_t*)(ws + w.off_qfrag);
     if (!a->query_prepared) {
         const int64_t nvec = (int64_t)a->batch * a->num_q_heads;
-        if (launch_qprep(a->query, a->q_dtype, nvec, D, consts->pi_t, consts->s_t, qprep, st) != TQ_OK)
+        if (launch_qprep(a->query, a->q_dtype, nvec, D, consts->pi_t, consts->s_t, qprep, qfrag, G, a->num_q_heads,
+                         st) != TQ_OK)
             return TQ_ERR_CUDA;
     }
 
@@ -421,6 +464,7 @@ extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_
     p.seq_lens = a->seq_lens;
     p.min_history = a->min_history;
     p.qprep = qprep;
+    p.qfrag = qfrag;
     p.query = a->query;
     p.q_dtype = a->q_dtype;
     p.ring_k = has_ring ? a->ring_k : nullptr;
@@ -480,7 +524,8 @@ extern "C" int tq_scores(const tq_consts* consts, const tq_pool* pool, const int
     cudaStream_t st = (cudaStream_t)stream;
     float* qprep = (float*)((uint8_t*)workspace + TQ_WS_HEADER_BYTES);
     const int64_t nvec = (int64_t)H * n_q;
-    if (launch_qprep(query, q_dtype, nvec, D, consts->pi_t, consts->s_t, qprep, st) != TQ_OK) return TQ_ERR_CUDA;
+    if (launch_qprep(query, q_dtype, nvec, D, consts->pi_t, consts->s_t, qprep, nullptr, 1, 1, st) != TQ_OK)
+        return TQ_ERR_CUDA;
 
     const TqLayout L = tq_make_layout(D, consts->cfg.key_bits, consts->cfg.value_bits);
     ScoreParams p;

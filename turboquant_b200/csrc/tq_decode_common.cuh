@@ -21,6 +21,7 @@ struct DecodeParams {
     const int32_t* seq_lens;
     int min_history;
     const float* qprep;  // [B][Qh][2][D] rotated / sketched query
+    const uint32_t* qfrag;   // per (sequence, kv head): the same query as fp16 MMA fragments (see QF_*)
     const void* query;
     int q_dtype;
     const void* ring_k;
@@ -36,6 +37,23 @@ struct DecodeParams {
     int32_t* status;
     int num_splits, ring_splits;
 };
+
+// ---- operand geometry of the tensor-core kernel, shared with the query preparation ----
+// Thread (gid = lane/4, tig = lane%4).  Score MMA k-step s uses B/A register pair
+// r = 2s, 2s+1; register r covers dims d_lo = (D/4)*tig + 16*(r/8) + r%8 (low half)
+// and d_lo + 8 (high half): the two 16-bit halves of code word r/8, field j = r%8.
+__host__ __device__ constexpr int code_pos(int j) { return j <= 4 ? j : j - 3; }            // 2-bit field index after the optional >>6
+__host__ __device__ constexpr int sign_bit(int wi, int j) { return j + 8 * (wi & 1); }      // bit in the byte-swapped sign word
+__host__ __device__ constexpr int sign_pos(int b) { return b <= 9 ? b : b - 6; }
+
+// Query fragments of one (sequence, kv head): QF_HDR floats (exponent of the
+// rotated query per head [8], of the sketched query per head [8]) followed by
+// `sets` x (D/8) registers x 32 lanes of packed fp16 pairs.  With G <= 4 there
+// is one set: B-fragment columns 0-3 hold the rotated query of heads 0-3
+// scaled by 2^(e - 2*code_pos), columns 4-7 the sketched query scaled by
+// 2^(e - sign_pos); with G > 4 set 0 is the rotated, set 1 the sketched query.
+constexpr int QF_HDR = 16;
+__host__ __device__ constexpr int qf_words(int D, int G) { return QF_HDR + (G > 4 ? 2 : 1) * (D / 8) * 32; }
 
 struct ScoreParams {
     const uint8_t* pool;

@@ -60,14 +60,6 @@ __device__ __forceinline__ uint32_t hmul2_sat(uint32_t a, uint32_t b) {
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-// ---- operand geometry shared by the query fragments and the main loop ----------------
-// Thread (gid = lane/4, tig = lane%4).  Score MMA k-step s uses B/A register pair
-// r = 2s, 2s+1; register r covers dims d_lo = (D/4)*tig + 16*(r/8) + r%8 and d_lo + 8:
-// the two 16-bit halves of code word r/8, field j = r%8.
-__host__ __device__ constexpr int code_pos(int j) { return j <= 4 ? j : j - 3; }            // 2-bit field index after the optional >>6
-__host__ __device__ constexpr int sign_bit(int wi, int j) { return j + 8 * (wi & 1); }      // bit in the byte-swapped sign word
-__host__ __device__ constexpr int sign_pos(int b) { return b <= 9 ? b : b - 6; }
-
 template <int D, int VAL_BITS, bool SPLITB>
 __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams p) {
     constexpr int GP = SPLITB ? 8 : 4;
@@ -80,9 +72,7 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
 
     extern __shared__ __align__(128) uint8_t smem[];
     uint8_t* stages = smem;                                              // [NW warps][NSTW][BB]; reused after the loop
-    float* qsm = reinterpret_cast<float*>(smem + NW * NSTW * BB);        // [2][GP][D] rotated / sketched query
-    float* cst = qsm + 2 * GP * D;                                       // [4][GP]: exponent e_rot, e_sk, sums q_rot, q_sk
-    float* ml = cst + 4 * GP;                                            // [NW warps][2][GP]
+    float* ml = reinterpret_cast<float*>(smem + NW * NSTW * BB);         // [NW warps][2][GP]
     int* bt_s = reinterpret_cast<int*>(ml + 2 * NW * GP);                // [BT_MAX] physical blocks of this CTA
     uint64_t* bars = reinterpret_cast<uint64_t*>(bt_s + BT_MAX);         // [NW][NSTW]
     float* wsm = reinterpret_cast<float*>(bars + NW * NSTW);             // merge scratch
@@ -133,84 +123,57 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
         }
     }
 
-    // ---- query fragments ----
-    for (int i = tid; i < 2 * GP * D; i += NT) {
-        const int which = i / (GP * D), g = (i / D) % GP, j = i % D;
-        qsm[i] = g < p.G ? p.qprep[((int64_t)(b * p.Qh + h * p.G + g) * 2 + which) * D + j] : 0.f;
-    }
-    __syncthreads();
-    for (int row = warp; row < 2 * GP; row += NW) {   // power-of-two scale per query row
-        float mx = 0.f;
-        for (int j = lane; j < D; j += 32) mx = fmaxf(mx, fabsf(qsm[row * D + j]));
-        mx = tq_warp_max(mx);
-        if (lane == 0) cst[row] = (mx > 0.f && mx < 3.0e38f) ? (float)max(-100, min(100, 14 - ilogbf(mx))) : 0.f;
-    }
-    __syncthreads();
-
+    // ---- query fragments, prepared once per (sequence, kv head) by the query-prep kernel ----
     uint32_t bq[2 * KS];
     uint32_t bsk[SPLITB ? 2 * KS : 1];
+    float k0[2], k1[2], kb0[2], ksg[2], kq[2];
     {
-        // column of this thread in the B fragment: n = gid
-        const int g_rot = SPLITB ? gid : (gid & 3);
+        const uint32_t* qf = p.qfrag + (int64_t)(b * p.H + h) * qf_words(D, p.G);
+        const float* hdr = reinterpret_cast<const float*>(qf);
         const bool is_sk = !SPLITB && gid >= 4;
-        const float* src_a = qsm + ((is_sk ? GP : 0) + g_rot) * D;
-        const int e_a = (int)cst[(is_sk ? GP : 0) + g_rot];
-        const float* src_b = qsm + (GP + g_rot) * D;
-        const int e_b = (int)cst[GP + g_rot];
-        const float fa = pow2i(e_a), fa_inv = pow2i(-e_a), fb = pow2i(e_b), fb_inv = pow2i(-e_b);
+        const int g_col = SPLITB ? gid : (gid & 3);             // head of this thread's B-fragment column
+        const bool col_live = g_col < p.G;
+        const int e_a = (int)hdr[(is_sk ? 8 : 0) + g_col], e_b = (int)hdr[8 + g_col];
+#pragma unroll
+        for (int r = 0; r < 2 * KS; ++r) {
+            bq[r] = col_live ? qf[QF_HDR + r * 32 + lane] : 0u;
+            if (SPLITB) bsk[r] = col_live ? qf[QF_HDR + (2 * KS + r) * 32 + lane] : 0u;
+        }
+        // sums of the fp16-rounded query over all dims (the constant terms of the bit-plane form)
         float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll
         for (int r = 0; r < 2 * KS; ++r) {
             const int wi = r >> 3, j = r & 7;
-            const int d_lo = (D / 4) * tig + 16 * wi + j, d_hi = d_lo + 8;
-            const int sh_code = 2 * code_pos(j), sh_sign = sign_pos(sign_bit(wi, j));
-            // value stored = q * 2^(e - sh); sh is a compile-time constant after unrolling
-            const float dn_code = 1.f / (float)(1 << sh_code), dn_sign = 1.f / (float)(1 << sh_sign);
-            const float up_code = (float)(1 << sh_code), up_sign = (float)(1 << sh_sign);
-            const float dn = is_sk ? dn_sign : dn_code, up = is_sk ? up_sign : up_code;
-            const __half lo = __float2half_rn(src_a[d_lo] * fa * dn);
-            const __half hi = __float2half_rn(src_a[d_hi] * fa * dn);
-            sum_a += (__half2float(lo) + __half2float(hi)) * up * fa_inv;
-            const __half2 v = __halves2half2(lo, hi);
-            bq[r] = *reinterpret_cast<const uint32_t*>(&v);
+            const float up_code = (float)(1 << (2 * code_pos(j))), up_sign = (float)(1 << sign_pos(sign_bit(wi, j)));
+            const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&bq[r]));
+            sum_a = fmaf(v.x + v.y, is_sk ? up_sign : up_code, sum_a);
             if (SPLITB) {
-                const __half lo2 = __float2half_rn(src_b[d_lo] * fb * dn_sign);
-                const __half hi2 = __float2half_rn(src_b[d_hi] * fb * dn_sign);
-                sum_b += (__half2float(lo2) + __half2float(hi2)) * up_sign * fb_inv;
-                const __half2 v2 = __halves2half2(lo2, hi2);
-                bsk[r] = *reinterpret_cast<const uint32_t*>(&v2);
+                const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&bsk[r]));
+                sum_b = fmaf(v2.x + v2.y, up_sign, sum_b);
             }
         }
-        // sums of the fp16-rounded query over all dims: add the four tig lanes
+        sum_a *= pow2i(-e_a);
+        sum_b *= pow2i(-e_b);
         sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
         sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
         sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
         sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
-        if (warp == 0 && tig == 0) {
-            if (SPLITB) {
-                cst[2 * GP + gid] = sum_a;
-                cst[3 * GP + gid] = sum_b;
-            } else {
-                cst[(is_sk ? 3 : 2) * GP + g_rot] = sum_a;
-            }
-        }
-    }
-    __syncthreads();
-
-    // per-thread constants of its two score columns g = 2*tig, 2*tig+1
-    // logit*log2e*scale = nk * (k0 + k1*acc1 + kb0*acc0) + rk * (ks*accs - kq)
-    float k0[2], k1[2], kb0[2], ksg[2], kq[2];
-    {
+        // constants of this thread's two score columns g = 2*tig, 2*tig+1:
+        // logit*log2e*scale = nk * (k0 + k1*acc1 + kb0*acc0) + rk * (ks*accs - kq)
         const float c0 = p.cb.centroids[0], c1 = p.cb.centroids[1], c2 = p.cb.centroids[2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int g = (2 * tig + i) & (GP - 1);
-            const int e_rot = (int)cst[g], e_sk = (int)cst[GP + g];
-            k0[i] = c0 * cst[2 * GP + g];
+            // column g's sums sit in the lanes with gid == g (rotated) and, merged layout, gid == g + 4 (sketched)
+            const float s_rot = __shfl_sync(0xffffffffu, sum_a, g * 4);
+            const float s_sk = SPLITB ? __shfl_sync(0xffffffffu, sum_b, g * 4)
+                                      : __shfl_sync(0xffffffffu, sum_a, ((g + 4) & 7) * 4);
+            const int e_rot = (int)hdr[g], e_sk = (int)hdr[8 + g];
+            k0[i] = c0 * s_rot;
             k1[i] = (c2 - c0) * pow2i(23 - e_rot);
             kb0[i] = (c1 - c0) * pow2i(24 - e_rot);
             ksg[i] = pow2i(25 - e_sk);
-            kq[i] = cst[3 * GP + g];
+            kq[i] = s_sk;
         }
     }
     const float sm_scale = p.scale * 1.4426950408889634f;   // softmax in base 2
@@ -495,7 +458,7 @@ template <int D, bool SPLITB>
 size_t mma_smem_bytes(int block_bytes, int nslot) {
     constexpr int GP = SPLITB ? 8 : 4;
     size_t s = (size_t)NW * NSTW * block_bytes;
-    s += sizeof(float) * (2 * GP * D + 4 * GP + 2 * NW * GP);
+    s += sizeof(float) * (2 * NW * GP);
     s += sizeof(int) * BT_MAX + sizeof(uint64_t) * NW * NSTW;
     s += sizeof(float) * ((size_t)(nslot > 128 ? nslot : 128) * GP + 2 * GP);
     return s;
