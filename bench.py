@@ -218,6 +218,47 @@ def measure_store(dev):
             "gbs": nbytes / ms / 1e6, "token_heads_per_s": t * h / ms * 1e3}
 
 
+def measure_decode_large(dev, n_seq: int = 256, n_tok: int = 8192):
+    """Batched decode of one layer of BASELINE config 4 (Llama-3-70B-shaped): 256 sequences x
+    8192 compressed tokens, 8 kv heads, 64 query heads, head_dim 128, 3-bit keys / 2-bit values.
+    1.68 GB of compressed records per launch: fixed launch costs are amortised, which shows
+    what the kernel itself streams."""
+    from turboquant_b200 import _engine as E
+    d, h, qh = 128, 8, 64
+    c = E.LayerConstants(d, 3, 2, dev, seed=42)
+    nblk = n_tok // 16
+    pool = E.BlockPool(c, h, n_seq * nblk)
+    bt = torch.arange(n_seq * nblk, dtype=torch.int32, device=dev).view(n_seq, nblk)
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    ch = torch.exp(0.5 * torch.randn(d, generator=g, device=dev))
+    for s in range(n_seq):
+        k = (torch.randn(n_tok, h, d, generator=g, device=dev) * ch).to(torch.bfloat16)
+        v = torch.randn(n_tok, h, d, generator=g, device=dev).to(torch.bfloat16)
+        E.store(c, pool, k, v, stride_token=h * d, stride_head=d, n_tokens=n_tok, n_heads=h, block_table=bt[s],
+                start_pos=0)
+    q = torch.randn(n_seq, qh, d, generator=g, device=dev).to(torch.bfloat16)
+    lens = torch.full((n_seq,), n_tok, dtype=torch.int32, device=dev)
+    ws = E.Workspace(dev)
+    out = torch.empty_like(q)
+    for _ in range(3):
+        E.decode(c, pool, ws, q, bt, lens, n_tok, out=out)
+    torch.cuda.synchronize()
+    reps = 10
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        E.decode(c, pool, ws, q, bt, lens, n_tok, out=out, query_prepared=True)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    nbytes = n_seq * n_tok * h * c.bytes_per_token
+    peak, kind = _peaks()
+    return {"workload": f"config4 layer: {n_seq} seqs x {n_tok} tok, Hkv=8 Hq=64 D=128 key3b/val2b",
+            "ms_per_launch": ms, "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak, "peak_kind": f"of {kind}",
+            "kv_tokens_per_s": n_seq * n_tok / ms * 1e3, "device_status": ws.status()}
+
+
 def cpu_baseline(steps: int, warmup: int, n_hist: int):
     """The oracle (a torch-CPU restatement of the reference's path) on the host cores."""
     from oracle import tq_oracle as O
@@ -386,6 +427,7 @@ def run_ours(args):
     clocks = sampler.stop()
 
     store = measure_store(dev) if rank == 0 else None
+    large = measure_decode_large(dev) if (rank == 0 and not args.no_large) else None
     base = cpu_baseline(3, 1, w["N"]) if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
 
     if rank == 0:
@@ -407,6 +449,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": (2 * w["H"] + w["Qh"]) * w["D"] * 2,
                     "d2h_bytes_per_step": w["Qh"] * w["D"] * 2},
             "gpu_launches": launches, "device_status": status, "clocks": clocks, "store": store,
+            "decode_large": large,
         }
         if base is not None:
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -423,9 +466,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-large", action="store_true", help="skip the batched 1.7 GB decode measurement")
+    ap.add_argument("--only-large", action="store_true", help="run only the batched decode measurement (profiling)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.impl == "reference":
+    if args.only_large:
+        torch.cuda.set_device(0)
+        print(json.dumps(measure_decode_large(torch.device("cuda", 0))), flush=True)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -427,30 +427,47 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
         }
     }
     __syncthreads();
+    // weight of every warp's partial, once per (warp, head)
+    float* wt = wsm;            // [NW][GP]
+    float* mxl = wsm + NW * GP; // [2][GP]: max (log2 domain), sum
+    if (tid < GP) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) mx = fmaxf(mx, ml[(w * 2) * GP + tid]);
+        float lsum = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const float mw = ml[(w * 2) * GP + tid];
+            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mx);
+            wt[w * GP + tid] = f;
+            lsum = fmaf(f, ml[(w * 2 + 1) * GP + tid], lsum);
+        }
+        mxl[tid] = mx;
+        mxl[GP + tid] = lsum;
+    }
+    __syncthreads();
     {
         float* mine = partial_ptr<D, GP>(p, b, h, x);
-        for (int i = tid; i < GP * D; i += NT) {
-            const int g = i / D, d = i % D;
-            float mx = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < NW; ++w) mx = fmaxf(mx, ml[(w * 2) * GP + g]);
-            float acc = 0.f, lsum = 0.f;
+        for (int i = tid; i < GP * (D / 4); i += NT) {
+            const int g = i / (D / 4), d = (i % (D / 4)) * 4;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int w = 0; w < NW; ++w) {
-                const float mw = ml[(w * 2) * GP + g];
-                if (mw != -INFINITY) {
-                    const float wt = exp2f(mw - mx);
-                    acc = fmaf(wt, osm[(w * GP + g) * D + d], acc);
-                    lsum = fmaf(wt, ml[(w * 2 + 1) * GP + g], lsum);
-                }
+                const float f = wt[w * GP + g];
+                const float4 v = *reinterpret_cast<const float4*>(osm + (w * GP + g) * D + d);
+                acc.x = fmaf(f, v.x, acc.x);
+                acc.y = fmaf(f, v.y, acc.y);
+                acc.z = fmaf(f, v.z, acc.z);
+                acc.w = fmaf(f, v.w, acc.w);
             }
-            mine[2 * GP + g * D + d] = acc;
-            if (d == 0) {
-                mine[g] = mx * 0.6931471805599453f;   // back to the natural-log domain of the merge
-                mine[GP + g] = lsum;
-            }
+            *reinterpret_cast<float4*>(mine + 2 * GP + g * D + d) = acc;
+        }
+        if (tid < GP) {
+            mine[tid] = mxl[tid] * 0.6931471805599453f;   // back to the natural-log domain of the merge
+            mine[GP + tid] = mxl[GP + tid];
         }
     }
+    __syncthreads();   // wsm is reused by the merge
     ticket_and_merge<D, GP>(p, b, h, wsm);
 }
 
