@@ -186,6 +186,25 @@ typedef struct tq_decode_args {
  * (triton_kernels.py:209-356,505-607). */
 int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* args, void* stream);
 
+/* tq_decode without caller-provided scratch: `workspace` / `workspace_bytes` of
+ * the arguments are ignored and a fixed array inside the library, resident on
+ * every GPU that loads it, is used instead.  No counterpart in the reference:
+ * it exists for hosts that cannot allocate device memory at the point of the
+ * call (a plugin inside an engine that has already claimed the whole GPU for
+ * its KV pool, or code running while that engine's allocator is locked).
+ * Limits and rules:
+ *   - the launch must fit tq_decode_static_scratch_bytes() (8 MiB); a larger
+ *     batch x heads x splits is refused with TQ_ERR_WORKSPACE (lower num_splits
+ *     or use tq_decode);
+ *   - the first call on a device looks up the array's device address: make it
+ *     with that device current and before any stream capture;
+ *   - all calls on a device share the one array: calls that overlap on the GPU
+ *     (different streams) race - serialise them;
+ *   - `query_prepared` is ignored (the query is always prepared again).
+ * It calls no cudaMalloc / cudaFree or any other allocating routine. */
+int tq_decode_static(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* args, void* stream);
+size_t tq_decode_static_scratch_bytes(void);
+
 /* Unscaled logits <q, k_hat> of every query vector against the first n_tokens
  * of one sequence: query (H, n_q, D) -> logits (H, n_q, n_tokens) fp32.
  * Replaces TurboQuantProd.attention_score (quantizer.py:274-302) and the two

@@ -210,8 +210,13 @@ def decode(consts: LayerConstants, pool: BlockPool, ws: Workspace, query: torch.
            ring_lens: Optional[torch.Tensor] = None, max_ring_len: int = 0,
            ring_stride_seq: int = 0, ring_stride_token: int = 0, scale: Optional[float] = None,
            min_history: int = 16, num_splits: int = 0, out: Optional[torch.Tensor] = None,
-           query_prepared: bool = False, kernel: int = 0) -> torch.Tensor:
-    """query (B, Qh, D) -> out (B, Qh, D) in the query dtype."""
+           query_prepared: bool = False, kernel: int = 0, static_scratch: bool = False) -> torch.Tensor:
+    """query (B, Qh, D) -> out (B, Qh, D) in the query dtype.
+
+    static_scratch=True routes through tq_decode_static: no workspace tensor is
+    touched, the library's built-in scratch array is used (for callers that
+    must not allocate); `ws` may then be None.
+    """
     require_cuda(query, "query")
     b, qh, d = query.shape
     query = query.contiguous()
@@ -221,10 +226,11 @@ def decode(consts: LayerConstants, pool: BlockPool, ws: Workspace, query: torch.
         scale = 1.0 / math.sqrt(d)
     h = pool.num_kv_heads
     splits = num_splits or choose_splits(b, h, max_seq_len, sm_count(consts.device), max_ring_len)
-    need = C.c_size_t(0)
-    check(lib().tq_decode_workspace_bytes(C.byref(consts.cfg), b, qh, h, splits, C.byref(need)),
-          "tq_decode_workspace_bytes")
-    ws.ensure(need.value)
+    if not static_scratch:
+        need = C.c_size_t(0)
+        check(lib().tq_decode_workspace_bytes(C.byref(consts.cfg), b, qh, h, splits, C.byref(need)),
+              "tq_decode_workspace_bytes")
+        ws.ensure(need.value)
     a = _lib.tq_decode_args()
     a.query, a.q_dtype, a.batch, a.num_q_heads = query.data_ptr(), dtype_code(query.dtype), b, qh
     a.block_table = block_table.data_ptr()
@@ -236,9 +242,14 @@ def decode(consts: LayerConstants, pool: BlockPool, ws: Workspace, query: torch.
         a.ring_lens, a.max_ring_len = ring_lens.data_ptr(), max_ring_len
         a.ring_stride_seq, a.ring_stride_token = ring_stride_seq, ring_stride_token
     a.scale = scale
-    a.out, a.workspace, a.workspace_bytes, a.num_splits = out.data_ptr(), ws.ptr, ws.nbytes, splits
+    a.out, a.num_splits = out.data_ptr(), splits
     a.query_prepared = 1 if query_prepared else 0
     a.kernel = kernel
+    if static_scratch:
+        check(lib().tq_decode_static(C.byref(consts.c), C.byref(pool.c), C.byref(a), stream_ptr(consts.device)),
+              f"tq_decode_static (built-in scratch of {lib().tq_decode_static_scratch_bytes()} bytes)")
+        return out
+    a.workspace, a.workspace_bytes = ws.ptr, ws.nbytes
     check(lib().tq_decode(C.byref(consts.c), C.byref(pool.c), C.byref(a), stream_ptr(consts.device)), "tq_decode")
     return out
 

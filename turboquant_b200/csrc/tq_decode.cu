@@ -565,3 +565,49 @@ extern "C" int tq_scores(const tq_consts* consts, const tq_pool* pool, const int
 #undef TQ_SC
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
+
+// ---------------------------------------------------------------------------
+// Decode for callers that cannot hand over scratch memory
+// ---------------------------------------------------------------------------
+// Some hosts of this library never get to call cudaMalloc themselves: a plugin
+// running inside an engine that has claimed all device memory for its own KV
+// pool up front, or code entered while the engine's allocator is locked (for
+// instance between the engine's warm-up and its CUDA-graph replay).  For them
+// the scratch of tq_decode lives in this fixed array inside the library image.
+// Every GPU that loads the library carries these bytes until the process ends,
+// which is why the size is kept modest.
+#define TQ_STATIC_SCRATCH_BYTES (8u << 20)
+static __device__ __align__(256) unsigned char g_tq_static_scratch[TQ_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_ptr[kMaxDevices];   // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" size_t tq_decode_static_scratch_bytes(void) { return (size_t)TQ_STATIC_SCRATCH_BYTES; }
+
+extern "C" int tq_decode_static(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* a, void* stream) {
+    if (!consts || !pool || !a) return TQ_ERR_NULL;
+    if (a->batch <= 0 || pool->num_kv_heads <= 0) return TQ_ERR_SHAPE;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TQ_ERR_CUDA;
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        // In host code the array's name is only a handle; the kernels need the
+        // address the symbol has on THIS device.  Looked up once per device, on
+        // the first call made with that device current.
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_tq_static_scratch) != cudaSuccess || ptr == nullptr) return TQ_ERR_CUDA;
+        g_static_scratch_ptr[dev] = ptr;
+    }
+    void* scratch = g_static_scratch_ptr[dev];
+    // The array keeps whatever the previous call left: the status word and the
+    // per-(sequence, head) tickets must start at zero.
+    const size_t head = TQ_WS_HEADER_BYTES + (((size_t)a->batch * pool->num_kv_heads * sizeof(int32_t) + 255) / 256) * 256;
+    if (head > TQ_STATIC_SCRATCH_BYTES) return TQ_ERR_WORKSPACE;
+    if (cudaMemsetAsync(scratch, 0, head, (cudaStream_t)stream) != cudaSuccess) return TQ_ERR_CUDA;
+    tq_decode_args b = *a;
+    b.workspace = scratch;
+    b.workspace_bytes = TQ_STATIC_SCRATCH_BYTES;
+    b.query_prepared = 0;   // the prepared query of an earlier call may have been overwritten by another caller
+    return tq_decode(consts, pool, &b, stream);   // answers TQ_ERR_WORKSPACE when the launch needs more than the array
+}
