@@ -152,6 +152,11 @@ int tq_store(const tq_consts* consts, const void* key, const void* value, tq_dty
              const int64_t* slot_mapping, const int32_t* block_table, int64_t start_pos,
              const tq_pool* pool, void* stream);
 
+/* Status word of the tensor-core store kernel: 0, or TQ_ERR_TIMEOUT / TQ_ERR_RANGE
+ * if one of its bounded waits ran out or a block index was out of range.
+ * Synchronises the device. */
+int tq_store_read_status(int32_t* out);
+
 /* ---- read path ------------------------------------------------------------ */
 
 typedef struct tq_decode_args {

@@ -428,3 +428,36 @@ def test_tensor_core_kernel_matches_cuda_core_kernel(d, h, qh, vb, n, dev):
             assert ws.status() == 0
             assert _cos(a, b) >= 0.99995, (splits, ring, _cos(a, b))
             torch.testing.assert_close(a, b, rtol=3e-2, atol=3e-3)
+
+
+@pytest.mark.parametrize("kb,vb,h,n", [(3, 2, 8, 8192), (4, 4, 4, 3000), (3, 4, 2, 129), (4, 2, 1, 16), (3, 2, 3, 2047)])
+def test_tensor_core_store_matches_fp32_store_and_oracle(kb, vb, h, n, dev):
+    """tcgen05 store kernel (head_dim 128, bf16, block-aligned start) against the fp32 store
+    kernel and the oracle: values bit exact, codes / sign bits within the tie budget."""
+    from turboquant_b200 import _engine as E
+    d = 128
+    k, v = O.synth_kv(n, h, d, seed=77 + n, dtype=torch.bfloat16)
+    v[3 % n, 0, :32] = 0.25            # constant group
+    k[5 % n, h - 1, :] = 0             # zero key
+    kd, vd = k.to(dev), v.to(dev)
+    planes = {}
+    for tc in (True, False):
+        c = E.LayerConstants(d, kb, vb, dev, seed=49, tensor_core_store=tc)
+        pool = E.BlockPool(c, h, E.blocks_for(n) + 3)
+        bt = torch.randperm(pool.num_blocks, generator=torch.Generator().manual_seed(n)).int().to(dev)
+        E.store(c, pool, kd, vd, stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h, block_table=bt, start_pos=0)
+        assert E.store_status() == 0
+        planes[tc] = E.pool_to_planes(c, pool, bt, n)
+    a, b = planes[True], planes[False]
+    assert torch.equal(a.v_data, b.v_data) and torch.equal(a.v_scales, b.v_scales) and torch.equal(a.v_zeros, b.v_zeros)
+    assert _frac(a.norms, b.norms) <= TIE_BUDGET
+    assert _frac(a.mse_indices, b.mse_indices) <= TIE_BUDGET
+    assert _frac(a.qjl_signs, b.qjl_signs) <= TIE_BUDGET
+    torch.testing.assert_close(a.residual_norms.float(), b.residual_norms.float(), rtol=2e-3, atol=1e-4)
+    ost = O.OracleStore(d, h, kb, vb, c.centroids_cpu, c.boundaries_cpu, pi=c.Pi.cpu(), s=c.S.cpu())
+    ost.append_chunk(k, v)
+    of = ost.get_flat_cache()
+    assert _frac(a.mse_indices.cpu(), torch.from_numpy(of.mse_indices)) <= TIE_BUDGET
+    assert _frac(a.qjl_signs.cpu(), torch.from_numpy(of.qjl_signs)) <= TIE_BUDGET
+    assert torch.equal(a.v_data.cpu(), torch.from_numpy(of.v_data))
+    assert _frac(a.norms.cpu(), of.norms.to(torch.float16)) <= TIE_BUDGET

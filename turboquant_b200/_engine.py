@@ -63,7 +63,8 @@ class LayerConstants:
 
     def __init__(self, head_dim: int, key_bits: int, value_bits: int, device, seed: int = 42,
                  group_size: int = 32, Pi: Optional[torch.Tensor] = None, S: Optional[torch.Tensor] = None,
-                 centroids: Optional[torch.Tensor] = None, boundaries: Optional[torch.Tensor] = None):
+                 centroids: Optional[torch.Tensor] = None, boundaries: Optional[torch.Tensor] = None,
+                 tensor_core_store: bool = True):
         self.head_dim, self.key_bits, self.value_bits = head_dim, key_bits, value_bits
         self.group_size = group_size
         self.device = torch.device(device)
@@ -101,10 +102,11 @@ class LayerConstants:
         for i in range(n_cent - 1):
             c.boundaries[i] = float(interior[i])
         c.qjl_scale = self.qjl_scale
+        # without the split operands tq_store always runs its fp32 kernel
         for i in range(3):
-            c.pi_limbs[i] = self.pi_limbs[i].data_ptr()
+            c.pi_limbs[i] = self.pi_limbs[i].data_ptr() if tensor_core_store else None
         for i in range(2):
-            c.m_limbs[i] = self.m_limbs[i].data_ptr()
+            c.m_limbs[i] = self.m_limbs[i].data_ptr() if tensor_core_store else None
         self.c = c
 
     @property
@@ -351,3 +353,10 @@ def pack_stage(consts: LayerConstants, y: torch.Tensor, projected: torch.Tensor)
     check(lib().tq_pack_stage(C.byref(consts.c), y2.data_ptr(), p2.data_ptr(), n, codes.data_ptr(),
                               signs.data_ptr(), stream_ptr(consts.device)), "tq_pack_stage")
     return codes.reshape(*y.shape[:-1], -1), signs.reshape(*y.shape[:-1], -1)
+
+
+def store_status() -> int:
+    """Status word of the tensor-core store kernel (0 = fine); synchronises the device."""
+    out = C.c_int32(0)
+    check(lib().tq_store_read_status(C.byref(out)), "tq_store_read_status")
+    return out.value
