@@ -1,6 +1,7 @@
 // Store path on the 5th-generation tensor cores (tcgen05 + TMEM), head_dim 128,
-// bf16 input.  One persistent CTA per SM; a tile is 128 tokens of one kv head,
-// thread t owns token row t from load to packed output:
+// bf16 input.  One persistent 512-thread CTA per SM; a tile is 128 tokens of one
+// kv head; four threads share a token row, each owning 32 channels from load to
+// packed output:
 //
 //   load row -> norm, normalise (bf16, as torch does) -> operand tiles in shared memory
 //   MMA 1 : Y = x_unit * Pi^T   (Pi as two bf16 limbs: exact-enough fp32 rotation)
@@ -24,7 +25,7 @@ namespace {
 
 constexpr int TC_D = 128;
 constexpr int TC_TOK = 128;
-constexpr int TC_THREADS = 128;
+constexpr int TC_THREADS = 512;
 constexpr int TILE_BYTES = TC_TOK * TC_D * 2;   // one bf16 operand tile
 constexpr int LBO = 128;                        // bytes between core matrices along K
 constexpr int SBO = (TC_D / 8) * 128;           // bytes between 8-row groups
@@ -108,56 +109,50 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& q, float (&f)[8]) {
 
 namespace {
 
-// Per-group (32 channels) asymmetric quantisation of one value row in bf16
-// arithmetic (kv_cache.py:64-90); codes go to the record image in the decode
-// kernel's byte order, scales / zero points group-major.
+// Asymmetric min/max quantisation of ONE 32-channel group of one value row in
+// bf16 arithmetic (kv_cache.py:64-90); codes go to the record image in the
+// decode kernel's byte order, scale / zero point group-major.
 template <int VAL_BITS>
-__device__ __forceinline__ void quantize_value_row(const __nv_bfloat16* __restrict__ vrow, bool valid, uint8_t* rec,
-                                                   const TqLayout& L, int tl) {
+__device__ __forceinline__ void quantize_value_group(const __nv_bfloat16* __restrict__ vrow, bool valid, uint8_t* rec,
+                                                     const TqLayout& L, int tl, int grp) {
     const float n_levels = (float)((1 << VAL_BITS) - 1);
     const float min_scale = bf16r(1e-10f);
-#pragma unroll 1
-    for (int grp = 0; grp < TC_D / 32; ++grp) {
-        float v[32];
+    float v[32];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            uint4 q = make_uint4(0u, 0u, 0u, 0u);
-            if (valid) q = __ldg(reinterpret_cast<const uint4*>(vrow + grp * 32 + c * 8));
-            float f[8];
-            unpack_bf16x8(q, f);
+    for (int c = 0; c < 4; ++c) {
+        uint4 q = make_uint4(0u, 0u, 0u, 0u);
+        if (valid) q = __ldg(reinterpret_cast<const uint4*>(vrow + grp * 32 + c * 8));
+        float f[8];
+        unpack_bf16x8(q, f);
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[c * 8 + i] = f[i];
+        for (int i = 0; i < 8; ++i) v[c * 8 + i] = f[i];
+    }
+    float vmin = v[0], vmax = v[0];
+#pragma unroll
+    for (int i = 1; i < 32; ++i) {
+        vmin = fminf(vmin, v[i]);
+        vmax = fmaxf(vmax, v[i]);
+    }
+    float scale = bf16r(__fdiv_rn(bf16r(vmax - vmin), n_levels));
+    scale = fmaxf(scale, min_scale);
+    reinterpret_cast<__half*>(rec + L.off_vscale)[grp * TQ_BLOCK_TOKENS + tl] = __float2half_rn(scale);
+    reinterpret_cast<__half*>(rec + L.off_vzero)[grp * TQ_BLOCK_TOKENS + tl] = __float2half_rn(vmin);
+    constexpr int PER_BYTE = 8 / VAL_BITS;
+#pragma unroll
+    for (int bt = 0; bt < 32 / PER_BYTE; ++bt) {
+        uint32_t byte = 0;
+#pragma unroll
+        for (int e = 0; e < PER_BYTE; ++e) {
+            const float r = rintf(bf16r(__fdiv_rn(bf16r(v[bt * PER_BYTE + e] - vmin), scale)));
+            byte |= (uint32_t)fminf(fmaxf(r, 0.f), n_levels) << (e * VAL_BITS);
         }
-        float vmin = v[0], vmax = v[0];
-#pragma unroll
-        for (int i = 1; i < 32; ++i) {
-            vmin = fminf(vmin, v[i]);
-            vmax = fmaxf(vmax, v[i]);
-        }
-        float scale = bf16r(__fdiv_rn(bf16r(vmax - vmin), n_levels));
-        scale = fmaxf(scale, min_scale);
-        reinterpret_cast<__half*>(rec + L.off_vscale)[grp * TQ_BLOCK_TOKENS + tl] = __float2half_rn(scale);
-        reinterpret_cast<__half*>(rec + L.off_vzero)[grp * TQ_BLOCK_TOKENS + tl] = __float2half_rn(vmin);
-        uint32_t code[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-            const float r = rintf(bf16r(__fdiv_rn(bf16r(v[i] - vmin), scale)));
-            code[i] = (uint32_t)fminf(fmaxf(r, 0.f), n_levels);
-        }
-        if (VAL_BITS == 2) {
-#pragma unroll
-            for (int bt = 0; bt < 8; ++bt)
-                rec[L.off_vcodes + tq_vcode_native(TC_D, 2, tl, grp * 8 + bt)] =
-                    (uint8_t)(code[4 * bt] | (code[4 * bt + 1] << 2) | (code[4 * bt + 2] << 4) | (code[4 * bt + 3] << 6));
-        } else {
-#pragma unroll
-            for (int bt = 0; bt < 16; ++bt)
-                rec[L.off_vcodes + tq_vcode_native(TC_D, 4, tl, grp * 16 + bt)] =
-                    (uint8_t)(code[2 * bt] | (code[2 * bt + 1] << 4));
-        }
+        rec[L.off_vcodes + tq_vcode_native(TC_D, VAL_BITS, tl, grp * (32 / PER_BYTE) + bt)] = (uint8_t)byte;
     }
 }
 
+// 512 threads: thread (row = tid % 128, q = tid / 128) owns channels [32q, 32q+32) of
+// token row `row` - one TMEM chunk, one value group.  Warp w reads TMEM lanes of
+// quarter w % 4 = row / 32, as the hardware requires.
 template <int MSE_BITS, int VAL_BITS>
 __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcParams p) {
     const TqLayout L = tq_make_layout(TC_D, MSE_BITS + 1, VAL_BITS);
@@ -169,10 +164,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
     uint8_t* sA0 = smem + 4 * TILE_BYTES;             // x_unit, later r_hi
     uint8_t* sA1 = sA0 + TILE_BYTES;                  // e, later r_lo
     uint8_t* sRec = sA1 + TILE_BYTES;                 // image of the tile's 8 block records
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sRec + 8 * REC_MAX);
+    float* s_part = reinterpret_cast<float*>(sRec + 8 * REC_MAX);   // [4][128] partial sums of squares
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_part + 4 * TC_TOK);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
 
     const int tid = threadIdx.x, warp = tid >> 5;
+    const int row = tid & (TC_TOK - 1), q = tid >> 7;
 
     // constant operands, once per CTA, into the core-matrix layout
 #pragma unroll 1
@@ -199,12 +196,12 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmem_y = tmem, tmem_e = tmem + 128, tmem_p = tmem + 256;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;   // this warp's quarter of the 128 TMEM lanes
+    const uint32_t lane_base = (uint32_t)(row & ~31) << 16;   // this warp's quarter of the 128 TMEM lanes
     const uint32_t aA0 = tq_smem_u32(sA0), aA1 = tq_smem_u32(sA1), aB = tq_smem_u32(sB);
 
     uint32_t ph0 = 0, ph1 = 0;
     bool failed = false;
-    const int row = tid, blk_l = row >> 4, tl = row & 15;
+    const int blk_l = row >> 4, tl = row & 15;
     uint8_t* rec = sRec + blk_l * BB;
 
 #pragma unroll 1
@@ -217,33 +214,36 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
         // ---------------- key row: norm, normalise, operand tiles ----------------
         float nd;
         {
-            const __nv_bfloat16* krow = p.key + tok * p.stride_token + (int64_t)h * p.stride_head;
-            uint4 xr[16];
-#pragma unroll
-            for (int c = 0; c < 16; ++c)
-                xr[c] = valid ? __ldg(reinterpret_cast<const uint4*>(krow + c * 8)) : make_uint4(0u, 0u, 0u, 0u);
+            const __nv_bfloat16* kseg = p.key + tok * p.stride_token + (int64_t)h * p.stride_head + q * 32;
+            float x[32];
             float ss = 0.f;
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
+            for (int c = 0; c < 4; ++c) {
+                const uint4 xr = valid ? __ldg(reinterpret_cast<const uint4*>(kseg + c * 8)) : make_uint4(0u, 0u, 0u, 0u);
                 float f[8];
-                unpack_bf16x8(xr[c], f);
+                unpack_bf16x8(xr, f);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
+                for (int i = 0; i < 8; ++i) {
+                    x[c * 8 + i] = f[i];
+                    ss = fmaf(f[i], f[i], ss);
+                }
             }
+            s_part[q * TC_TOK + row] = ss;
+            __syncthreads();
+            ss = (s_part[row] + s_part[TC_TOK + row]) + (s_part[2 * TC_TOK + row] + s_part[3 * TC_TOK + row]);
             nd = bf16r(__fsqrt_rn(ss));              // quantizer.py:136, in the input dtype
             const float den = bf16r(nd + 1e-10f);    // quantizer.py:138
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                float f[8], u[8], e[8];
-                unpack_bf16x8(xr[c], f);
+            for (int c = 0; c < 4; ++c) {
+                float u[8], e[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    u[i] = bf16r(__fdiv_rn(f[i], den));
-                    e[i] = fmaf(-nd, u[i], f[i]);    // exact: what the bf16 normalisation lost
+                    u[i] = bf16r(__fdiv_rn(x[c * 8 + i], den));
+                    e[i] = fmaf(-nd, u[i], x[c * 8 + i]);    // exact: what the bf16 normalisation lost
                 }
-                *reinterpret_cast<uint4*>(sA0 + core_off(row, c)) =
+                *reinterpret_cast<uint4*>(sA0 + core_off(row, q * 4 + c)) =
                     make_uint4(pack_bf16(u[0], u[1]), pack_bf16(u[2], u[3]), pack_bf16(u[4], u[5]), pack_bf16(u[6], u[7]));
-                *reinterpret_cast<uint4*>(sA1 + core_off(row, c)) =
+                *reinterpret_cast<uint4*>(sA1 + core_off(row, q * 4 + c)) =
                     make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
             }
         }
@@ -264,8 +264,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
             umma_commit(bars + 0);
         }
 
-        // ---------------- values, while the tensor core works ----------------
-        quantize_value_row<VAL_BITS>(p.value + tok * p.stride_token + (int64_t)h * p.stride_head, valid, rec, L, tl);
+        // ---------------- values (group q of the row), while the tensor core works ----------------
+        quantize_value_group<VAL_BITS>(p.value + tok * p.stride_token + (int64_t)h * p.stride_head, valid, rec, L, tl, q);
 
         {
             const bool ok = tq_mbar_wait_bounded(bars + 0, ph0);
@@ -277,45 +277,32 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
         }
         tc_fence_after();
 
-        // ---------------- codes and rotated-space residual ----------------
-        float rn2 = 0.f;
-#pragma unroll 1
-        for (int ch = 0; ch < 4; ++ch) {
+        // ---------------- codes and rotated-space residual of channels [32q, 32q+32) ----------------
+        {
             float y[32], er[32];
-            tmem_ld32(tmem_y + lane_base + ch * 32, y);
-            tmem_ld32(tmem_e + lane_base + ch * 32, er);
-            uint32_t codes[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-                uint32_t k = 0;
-#pragma unroll
-                for (int bnd = 0; bnd < N_CENT - 1; ++bnd) k += (p.cb.boundaries[bnd] < y[j]) ? 1u : 0u;
-                if (y[j] != y[j]) k = N_CENT - 1;
-                codes[j] = k;
-                const float r = fmaf(nd, y[j] - p.cb.centroids[k], er[j]);
-                rn2 = fmaf(r, r, rn2);
-                y[j] = r;
-            }
-            // packed codes of these 32 channels (quantizer.py:50-68)
+            tmem_ld32(tmem_y + lane_base + q * 32, y);
+            tmem_ld32(tmem_e + lane_base + q * 32, er);
             uint32_t* kc = reinterpret_cast<uint32_t*>(rec + L.off_kcodes + tl * L.kcode_row);
-            if (MSE_BITS == 2) {
-                uint32_t w0 = 0, w1 = 0;
+            constexpr int WIDTH = MSE_BITS == 2 ? 2 : 4, PER_WORD = 32 / WIDTH;
+            float rn2 = 0.f;
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    w0 |= codes[j] << (2 * j);
-                    w1 |= codes[16 + j] << (2 * j);
+            for (int w = 0; w < 32 / PER_WORD; ++w) {
+                uint32_t word = 0;
+#pragma unroll
+                for (int jj = 0; jj < PER_WORD; ++jj) {
+                    const int j = w * PER_WORD + jj;
+                    uint32_t k = 0;
+#pragma unroll
+                    for (int bnd = 0; bnd < N_CENT - 1; ++bnd) k += (p.cb.boundaries[bnd] < y[j]) ? 1u : 0u;
+                    if (y[j] != y[j]) k = N_CENT - 1;
+                    word |= k << (WIDTH * jj);       // quantizer.py:50-68
+                    const float r = fmaf(nd, y[j] - p.cb.centroids[k], er[j]);
+                    rn2 = fmaf(r, r, rn2);
+                    y[j] = r;
                 }
-                kc[ch * 2] = w0;
-                kc[ch * 2 + 1] = w1;
-            } else {
-#pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    uint32_t x = 0;
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) x |= codes[w * 8 + j] << (4 * j);
-                    kc[ch * 4 + w] = x;
-                }
+                kc[q * (32 / PER_WORD) + w] = word;
             }
+            s_part[q * TC_TOK + row] = rn2;
             // residual as bf16 hi + lo limbs -> operand tiles of the QJL product
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
@@ -327,13 +314,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
                     hi[i] = pack_bf16(ah, bh);
                     lo[i] = pack_bf16(a - ah, b - bh);
                 }
-                *reinterpret_cast<uint4*>(sA0 + core_off(row, ch * 4 + c)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4*>(sA1 + core_off(row, ch * 4 + c)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                *reinterpret_cast<uint4*>(sA0 + core_off(row, q * 4 + c)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                *reinterpret_cast<uint4*>(sA1 + core_off(row, q * 4 + c)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
             }
         }
-        reinterpret_cast<__half*>(rec + L.off_knorm)[tl] = __float2half_rn(nd);
-        reinterpret_cast<__half*>(rec + L.off_krnorm)[tl] = __float2half_rn(__fsqrt_rn(rn2));
-
         tq_fence_proxy_async();
         tc_fence_before();
         __syncthreads();
@@ -350,6 +334,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
                 umma(tmem_p, smem_desc(aA1 + ks * 2 * LBO), smem_desc(aB + 2 * TILE_BYTES + ks * 2 * LBO), 1);
             umma_commit(bars + 1);
         }
+        if (q == 0) {   // norms of the row (partials were published before the barrier above)
+            const float rn2 = (s_part[row] + s_part[TC_TOK + row]) + (s_part[2 * TC_TOK + row] + s_part[3 * TC_TOK + row]);
+            reinterpret_cast<__half*>(rec + L.off_knorm)[tl] = __float2half_rn(nd);
+            reinterpret_cast<__half*>(rec + L.off_krnorm)[tl] = __float2half_rn(__fsqrt_rn(rn2));
+        }
         {
             const bool ok = tq_mbar_wait_bounded(bars + 1, ph1);
             ph1 ^= 1;
@@ -360,18 +349,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
         }
         tc_fence_after();
 
-        // ---------------- sign bits (quantizer.py:214-222) ----------------
+        // ---------------- sign bits of channels [32q, 32q+32) (quantizer.py:214-222) ----------------
         {
-            uint32_t* sgn = reinterpret_cast<uint32_t*>(rec + L.off_ksigns + tl * L.ksign_row);
-#pragma unroll 1
-            for (int ch = 0; ch < 4; ++ch) {
-                float pr[32];
-                tmem_ld32(tmem_p + lane_base + ch * 32, pr);
-                uint32_t w = 0;
+            float pr[32];
+            tmem_ld32(tmem_p + lane_base + q * 32, pr);
+            uint32_t w = 0;
 #pragma unroll
-                for (int j = 0; j < 32; ++j) w |= (pr[j] > 0.f ? 1u : 0u) << j;
-                sgn[ch] = w;
-            }
+            for (int j = 0; j < 32; ++j) w |= (pr[j] > 0.f ? 1u : 0u) << j;
+            reinterpret_cast<uint32_t*>(rec + L.off_ksigns + tl * L.ksign_row)[q] = w;
         }
         tq_fence_proxy_async();
         tc_fence_before();
@@ -449,7 +434,7 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
             cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
             sms = 148;
     }
-    const size_t smem = (size_t)6 * TILE_BYTES + 8 * REC_MAX + 2 * sizeof(uint64_t) + 16;
+    const size_t smem = (size_t)6 * TILE_BYTES + 8 * REC_MAX + 4 * TC_TOK * sizeof(float) + 2 * sizeof(uint64_t) + 16;
     const unsigned grid = (unsigned)(p.n_tiles < sms ? p.n_tiles : sms);
     const int mse_bits = cfg.key_bits - 1;
 #define TQ_TC(MB, VB)                                                                                            \
