@@ -468,9 +468,13 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-large", action="store_true", help="skip the batched 1.7 GB decode measurement")
     ap.add_argument("--only-large", action="store_true", help="run only the batched decode measurement (profiling)")
+    ap.add_argument("--only-store", action="store_true", help="run only the store-path measurement (profiling)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
-    if args.only_large:
+    if args.only_store:
+        torch.cuda.set_device(0)
+        print(json.dumps(measure_store(torch.device("cuda", 0))), flush=True)
+    elif args.only_large:
         torch.cuda.set_device(0)
         print(json.dumps(measure_decode_large(torch.device("cuda", 0))), flush=True)
     elif args.impl == "reference":

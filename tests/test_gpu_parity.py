@@ -259,7 +259,8 @@ def test_paged_equals_flat_and_split_invariance(dev):
     """Random block tables and slot mappings; split count must not change the result."""
     from turboquant_b200 import _engine as E
     d, h, qh, n_seq = 128, 4, 16, 5
-    c = E.LayerConstants(d, 3, 2, dev, seed=42)
+    # one store kernel for both layouts (slot mappings always take the fp32 kernel), so bytes must be equal
+    c = E.LayerConstants(d, 3, 2, dev, seed=42, tensor_core_store=False)
     g = torch.Generator().manual_seed(3)
     lens = torch.randint(100, 900, (n_seq,), generator=g)
     nblk = [(int(x) + 15) // 16 for x in lens]

@@ -96,6 +96,22 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
 }
+// a / b for a caller that rounds the result to bf16 next: the product with the
+// reciprocal is within 2 ulp of the quotient, which can change the bf16 rounding
+// only next to a rounding tie (low half-word 0x8000); only there the exact
+// division runs.  Bit-identical to rounding __fdiv_rn(a, b), at a tenth of the cost.
+__device__ __forceinline__ float div_then_bf16(float a, float b, float rb) {
+    float q = a * rb;
+    if (((__float_as_uint(q) + 0x8004u) & 0xFFFFu) < 9u) q = __fdiv_rn(a, b);
+    return q;
+}
+// round two floats to bf16 with one conversion; returns the packed pair and the rounded values
+__device__ __forceinline__ uint32_t round_pair(float a, float b, float& ra, float& rb) {
+    const uint32_t pk = pack_bf16(a, b);
+    ra = __uint_as_float(pk << 16);
+    rb = __uint_as_float(pk & 0xffff0000u);
+    return pk;
+}
 __device__ __forceinline__ void unpack_bf16x8(const uint4& q, float (&f)[8]) {
     const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
@@ -110,20 +126,19 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& q, float (&f)[8]) {
 namespace {
 
 // Asymmetric min/max quantisation of ONE 32-channel group of one value row in
-// bf16 arithmetic (kv_cache.py:64-90); codes go to the record image in the
-// decode kernel's byte order, scale / zero point group-major.
+// bf16 arithmetic (kv_cache.py:64-90), from the four preloaded 16-byte pieces;
+// codes go to the record image in the decode kernel's byte order, scale / zero
+// point group-major.
 template <int VAL_BITS>
-__device__ __forceinline__ void quantize_value_group(const __nv_bfloat16* __restrict__ vrow, bool valid, uint8_t* rec,
-                                                     const TqLayout& L, int tl, int grp) {
-    const float n_levels = (float)((1 << VAL_BITS) - 1);
+__device__ __forceinline__ void quantize_value_group(const uint4 (&raw)[4], uint8_t* rec, const TqLayout& L, int tl,
+                                                     int grp) {
+    constexpr uint32_t N_LEVELS = (1u << VAL_BITS) - 1u;
     const float min_scale = bf16r(1e-10f);
     float v[32];
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-        uint4 q = make_uint4(0u, 0u, 0u, 0u);
-        if (valid) q = __ldg(reinterpret_cast<const uint4*>(vrow + grp * 32 + c * 8));
         float f[8];
-        unpack_bf16x8(q, f);
+        unpack_bf16x8(raw[c], f);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[c * 8 + i] = f[i];
     }
@@ -133,8 +148,9 @@ __device__ __forceinline__ void quantize_value_group(const __nv_bfloat16* __rest
         vmin = fminf(vmin, v[i]);
         vmax = fmaxf(vmax, v[i]);
     }
-    float scale = bf16r(__fdiv_rn(bf16r(vmax - vmin), n_levels));
+    float scale = bf16r(__fdiv_rn(bf16r(vmax - vmin), (float)N_LEVELS));
     scale = fmaxf(scale, min_scale);
+    const float rscale = __frcp_rn(scale);
     reinterpret_cast<__half*>(rec + L.off_vscale)[grp * TQ_BLOCK_TOKENS + tl] = __float2half_rn(scale);
     reinterpret_cast<__half*>(rec + L.off_vzero)[grp * TQ_BLOCK_TOKENS + tl] = __float2half_rn(vmin);
     constexpr int PER_BYTE = 8 / VAL_BITS;
@@ -142,9 +158,13 @@ __device__ __forceinline__ void quantize_value_group(const __nv_bfloat16* __rest
     for (int bt = 0; bt < 32 / PER_BYTE; ++bt) {
         uint32_t byte = 0;
 #pragma unroll
-        for (int e = 0; e < PER_BYTE; ++e) {
-            const float r = rintf(bf16r(__fdiv_rn(bf16r(v[bt * PER_BYTE + e] - vmin), scale)));
-            byte |= (uint32_t)fminf(fmaxf(r, 0.f), n_levels) << (e * VAL_BITS);
+        for (int e = 0; e < PER_BYTE; e += 2) {
+            float d0, d1, t0, t1;
+            round_pair(v[bt * PER_BYTE + e] - vmin, v[bt * PER_BYTE + e + 1] - vmin, d0, d1);   // (v - zero) in bf16
+            round_pair(div_then_bf16(d0, scale, rscale), div_then_bf16(d1, scale, rscale), t0, t1);   // / scale in bf16
+            // round half to even, clamp to [0, levels]; t >= 0 because zero = min
+            byte |= min(__float2uint_rn(t0), N_LEVELS) << (e * VAL_BITS);
+            byte |= min(__float2uint_rn(t1), N_LEVELS) << ((e + 1) * VAL_BITS);
         }
         rec[L.off_vcodes + tq_vcode_native(TC_D, VAL_BITS, tl, grp * (32 / PER_BYTE) + bt)] = (uint8_t)byte;
     }
@@ -204,6 +224,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
     const int blk_l = row >> 4, tl = row & 15;
     uint8_t* rec = sRec + blk_l * BB;
 
+    // this thread's 32 key channels of the NEXT tile, fetched while the current tile finishes
+    uint4 knext[4];
+    auto fetch_keys = [&](int64_t tile_idx) {
+        const int hh = (int)(tile_idx % p.H);
+        const int64_t tk = (tile_idx / p.H) * TC_TOK + row;
+        const bool ok = tile_idx < p.n_tiles && tk < p.n_tokens;
+        const __nv_bfloat16* src = p.key + tk * p.stride_token + (int64_t)hh * p.stride_head + q * 32;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            knext[c] = ok ? __ldg(reinterpret_cast<const uint4*>(src + c * 8)) : make_uint4(0u, 0u, 0u, 0u);
+    };
+    fetch_keys(blockIdx.x);
+
 #pragma unroll 1
     for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
         const int h = (int)(tile % p.H);
@@ -211,40 +244,46 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
         const int64_t tok = t0 + row;
         const bool valid = tok < p.n_tokens;
 
+        // value channels of this tile: in flight while the keys are normalised
+        uint4 vraw[4];
+        {
+            const __nv_bfloat16* vseg = p.value + tok * p.stride_token + (int64_t)h * p.stride_head + q * 32;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                vraw[c] = valid ? __ldg(reinterpret_cast<const uint4*>(vseg + c * 8)) : make_uint4(0u, 0u, 0u, 0u);
+        }
+
         // ---------------- key row: norm, normalise, operand tiles ----------------
         float nd;
         {
-            const __nv_bfloat16* kseg = p.key + tok * p.stride_token + (int64_t)h * p.stride_head + q * 32;
-            float x[32];
             float ss = 0.f;
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                const uint4 xr = valid ? __ldg(reinterpret_cast<const uint4*>(kseg + c * 8)) : make_uint4(0u, 0u, 0u, 0u);
                 float f[8];
-                unpack_bf16x8(xr, f);
+                unpack_bf16x8(knext[c], f);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    x[c * 8 + i] = f[i];
-                    ss = fmaf(f[i], f[i], ss);
-                }
+                for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
             }
             s_part[q * TC_TOK + row] = ss;
             __syncthreads();
             ss = (s_part[row] + s_part[TC_TOK + row]) + (s_part[2 * TC_TOK + row] + s_part[3 * TC_TOK + row]);
             nd = bf16r(__fsqrt_rn(ss));              // quantizer.py:136, in the input dtype
             const float den = bf16r(nd + 1e-10f);    // quantizer.py:138
+            const float rden = __frcp_rn(den);
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
-                float u[8], e[8];
+                float f[8];
+                unpack_bf16x8(knext[c], f);
+                uint32_t up[4], ep[4];
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    u[i] = bf16r(__fdiv_rn(x[c * 8 + i], den));
-                    e[i] = fmaf(-nd, u[i], x[c * 8 + i]);    // exact: what the bf16 normalisation lost
+                for (int i = 0; i < 4; ++i) {
+                    float u0, u1;
+                    up[i] = round_pair(div_then_bf16(f[2 * i], den, rden), div_then_bf16(f[2 * i + 1], den, rden), u0, u1);
+                    // what the bf16 normalisation lost, exact in fp32
+                    ep[i] = pack_bf16(fmaf(-nd, u0, f[2 * i]), fmaf(-nd, u1, f[2 * i + 1]));
                 }
-                *reinterpret_cast<uint4*>(sA0 + core_off(row, q * 4 + c)) =
-                    make_uint4(pack_bf16(u[0], u[1]), pack_bf16(u[2], u[3]), pack_bf16(u[4], u[5]), pack_bf16(u[6], u[7]));
-                *reinterpret_cast<uint4*>(sA1 + core_off(row, q * 4 + c)) =
-                    make_uint4(pack_bf16(e[0], e[1]), pack_bf16(e[2], e[3]), pack_bf16(e[4], e[5]), pack_bf16(e[6], e[7]));
+                *reinterpret_cast<uint4*>(sA0 + core_off(row, q * 4 + c)) = make_uint4(up[0], up[1], up[2], up[3]);
+                *reinterpret_cast<uint4*>(sA1 + core_off(row, q * 4 + c)) = make_uint4(ep[0], ep[1], ep[2], ep[3]);
             }
         }
         tq_fence_proxy_async();
@@ -265,7 +304,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
         }
 
         // ---------------- values (group q of the row), while the tensor core works ----------------
-        quantize_value_group<VAL_BITS>(p.value + tok * p.stride_token + (int64_t)h * p.stride_head, valid, rec, L, tl, q);
+        quantize_value_group<VAL_BITS>(vraw, rec, L, tl, q);
 
         {
             const bool ok = tq_mbar_wait_bounded(bars + 0, ph0);
@@ -310,8 +349,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const float a = y[c * 8 + 2 * i], b = y[c * 8 + 2 * i + 1];
-                    const float ah = bf16r(a), bh = bf16r(b);
-                    hi[i] = pack_bf16(ah, bh);
+                    float ah, bh;
+                    hi[i] = round_pair(a, b, ah, bh);
                     lo[i] = pack_bf16(a - ah, b - bh);
                 }
                 *reinterpret_cast<uint4*>(sA0 + core_off(row, q * 4 + c)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
@@ -334,6 +373,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
                 umma(tmem_p, smem_desc(aA1 + ks * 2 * LBO), smem_desc(aB + 2 * TILE_BYTES + ks * 2 * LBO), 1);
             umma_commit(bars + 1);
         }
+        fetch_keys(tile + gridDim.x);
         if (q == 0) {   // norms of the row (partials were published before the barrier above)
             const float rn2 = (s_part[row] + s_part[TC_TOK + row]) + (s_part[2 * TC_TOK + row] + s_part[3 * TC_TOK + row]);
             reinterpret_cast<__half*>(rec + L.off_knorm)[tl] = __float2half_rn(nd);
