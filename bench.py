@@ -138,12 +138,15 @@ class Runner:
         self.tokens = 0        # KV tokens attended
         self.bytes = 0         # algorithmic bytes of the decode kernel
 
-    def decode(self, L: Layer, q, prepared=False):
+    def decode(self, L: Layer, q, prepared=False, append=None):
         E, w = self.E, WL
+        kw = {}
+        if append is not None:       # the new token is written into the ring by the decode call itself
+            kw = dict(append_k=append[0], append_v=append[1])
         E.decode(L.store.consts, L.store.pool, L.store.workspace, q, L.store.block_table.unsqueeze(0),
                  L.store.seq_len_device, L.store.num_tokens, ring_k=L.ring_k, ring_v=L.ring_v, ring_lens=L.ring_len,
                  max_ring_len=L.ring_pos, ring_stride_seq=0, ring_stride_token=w["H"] * w["D"],
-                 num_splits=self.splits, out=L.out, query_prepared=prepared)
+                 num_splits=self.splits, out=L.out, query_prepared=prepared, **kw)
         self.launches += 1 if prepared else 2
         self.tokens += L.store.num_tokens + L.ring_pos
         self.bytes += self.decode_bytes(L)
@@ -162,11 +165,9 @@ class Runner:
             L.store.append_chunk(L.ring_k, L.ring_v)
             self.launches += 1
             L.ring_pos = 0
-        L.ring_k[L.ring_pos].copy_(L.new_k[i])
-        L.ring_v[L.ring_pos].copy_(L.new_v[i])
-        L.ring_pos += 1
-        L.ring_len.fill_(L.ring_pos)
-        self.decode(L, L.query[i])
+            L.ring_len.zero_()
+        L.ring_pos += 1                                  # device side: ring_len += 1 inside the decode call
+        self.decode(L, L.query[i], append=(L.new_k[i:i + 1], L.new_v[i:i + 1]))
         L.steps += 1
 
     def capture(self, first: int, count: int, chunk: int = 256):

@@ -183,6 +183,14 @@ typedef struct tq_decode_args {
     int32_t query_prepared;     /* nonzero: the workspace already holds this query's rotated /
                                    sketched form from an earlier tq_decode with the same workspace */
     int32_t kernel;             /* 0: tensor-core kernel where it applies; 1: always the CUDA-core kernel */
+    /* Optional: append one new exact token per sequence to the ring before attending (the
+     * reference's KVCaptureEngine.ingest_decode, capture.py:219-228, fused into this call).
+     * append_k / append_v: (batch, num_kv_heads, D) in ring_dtype, 16-byte aligned; the token of
+     * sequence b lands at ring position ring_lens[b], which is then incremented on the device.
+     * max_ring_len must already count the new token; ring_capacity is the ring's row count. */
+    const void* append_k;
+    const void* append_v;
+    int32_t ring_capacity;
 } tq_decode_args;
 
 /* One decode-attention step over compressed history plus the exact ring:

@@ -478,3 +478,75 @@ def test_tensor_core_store_matches_fp32_store_and_oracle(kb, vb, h, n, dev):
     assert _bit_frac(a.qjl_signs.cpu(), torch.from_numpy(of.qjl_signs)) <= TIE_BUDGET
     assert torch.equal(a.v_data.cpu(), torch.from_numpy(of.v_data))
     assert _frac(a.norms.cpu(), of.norms.to(torch.float16)) <= TIE_BUDGET
+
+
+def test_fused_ring_append(dev):
+    """tq_decode with append_k/append_v: the new token is written into the ring on the device
+    (position ring_lens[b], then incremented) and attended in the same call."""
+    from turboquant_b200 import _engine as E
+    d, h, qh, n, cap = 256, 4, 16, 1000, 64
+    c = E.LayerConstants(d, 3, 2, dev, seed=42)
+    k, v = O.synth_kv(n + cap, h, d, seed=9, dtype=torch.bfloat16)
+    pool = E.BlockPool(c, h, E.blocks_for(n))
+    bt = E.identity_block_table(pool.num_blocks, dev)
+    E.store(c, pool, k[:n].to(dev), v[:n].to(dev), stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h,
+            block_table=bt, start_pos=0)
+    lens = torch.tensor([n], dtype=torch.int32, device=dev)
+    ring_a = (torch.zeros(cap, h, d, dtype=torch.bfloat16, device=dev), torch.zeros(cap, h, d, dtype=torch.bfloat16, device=dev))
+    ring_b = (torch.zeros_like(ring_a[0]), torch.zeros_like(ring_a[1]))
+    len_a = torch.zeros(1, dtype=torch.int32, device=dev)
+    len_b = torch.zeros(1, dtype=torch.int32, device=dev)
+    ws_a, ws_b = E.Workspace(dev), E.Workspace(dev)
+    for step in range(5):
+        q = O.synth_query(1, qh, d, seed=20 + step, dtype=torch.bfloat16).to(dev)
+        nk, nv = k[n + step:n + step + 1].to(dev).contiguous(), v[n + step:n + step + 1].to(dev).contiguous()
+        # a: fused append
+        out_a = E.decode(c, pool, ws_a, q, bt.unsqueeze(0), lens, n, ring_k=ring_a[0], ring_v=ring_a[1],
+                         ring_lens=len_a, max_ring_len=step + 1, ring_stride_seq=0, ring_stride_token=h * d,
+                         append_k=nk, append_v=nv)
+        # b: ring written by the host code, as KVCaptureEngine does
+        ring_b[0][step].copy_(nk[0]); ring_b[1][step].copy_(nv[0]); len_b.fill_(step + 1)
+        out_b = E.decode(c, pool, ws_b, q, bt.unsqueeze(0), lens, n, ring_k=ring_b[0], ring_v=ring_b[1],
+                         ring_lens=len_b, max_ring_len=step + 1, ring_stride_seq=0, ring_stride_token=h * d)
+        assert int(len_a.item()) == step + 1
+        assert torch.equal(ring_a[0], ring_b[0]) and torch.equal(ring_a[1], ring_b[1])
+        assert torch.equal(out_a, out_b)
+
+
+def test_vllm_adapter_hybrid_decode(dev):
+    """The adapter end to end with a fake attention impl: prefill is captured (compressed history +
+    ring), the decode step is answered from the compressed store and matches the oracle."""
+    import types
+    from tests.test_vllm_adapter_cpu import FakeImpl
+    from turboquant_b200.integration import vllm as adapter
+    d, h, qh, cap = 128, 2, 8, 32
+    impl = FakeImpl(num_kv_heads=h, head_size=d, num_heads=qh)
+    impl.scale = 1.0 / math.sqrt(d)
+    ctx = {"layers.0.attn": types.SimpleNamespace(impl=impl, num_heads=qh)}
+    runner = types.SimpleNamespace(compilation_config=types.SimpleNamespace(static_forward_context=ctx), device=dev,
+                                   kv_caches=[])
+    states = adapter.install_hooks(runner, key_bits=3, value_bits=2, ring_capacity=cap, initial_layers_count=0,
+                                   mode=adapter.MODE_HYBRID)
+    st = states["layers.0.attn"]
+    k, v = O.synth_kv(201, h, d, seed=3, dtype=torch.bfloat16)
+    q = O.synth_query(1, qh, d, seed=4, dtype=torch.bfloat16)
+    try:
+        impl.do_kv_cache_update(None, k[:200].to(dev), v[:200].to(dev), None, torch.zeros(200, dtype=torch.long))
+        pre = impl.forward(None, torch.zeros(200, qh, d, device=dev), k[:200].to(dev), v[:200].to(dev), None,
+                           types.SimpleNamespace(num_actual_tokens=200, max_query_len=200))
+        assert pre == "flash-output"                              # prefill stays with the engine
+        impl.do_kv_cache_update(None, k[200:].to(dev), v[200:].to(dev), None, torch.zeros(1, dtype=torch.long))
+        assert (st.store.num_tokens, st.engine.ring.size) == (200, 1)   # ring was full: drained, then the new token
+        out_buf = torch.zeros(1, qh * d, dtype=torch.bfloat16, device=dev)
+        ret = impl.forward(None, q.to(dev).reshape(1, qh * d), k[200:].to(dev), v[200:].to(dev), None,
+                           types.SimpleNamespace(num_actual_tokens=1, max_query_len=1), output=out_buf)
+        assert ret is out_buf
+        c = st.store.consts
+        ost = O.OracleStore(d, h, 3, 2, c.centroids_cpu, c.boundaries_cpu, pi=c.Pi.cpu(), s=c.S.cpu())
+        ost.append_chunk(k[:168], v[:168])
+        ost.append_chunk(k[168:200], v[168:200])
+        ref = O.hybrid_attention(q, ost.get_flat_cache(), k[200:], v[200:], h, c.Pi.cpu(), c.S.cpu(), c.centroids_cpu)
+        assert _cos(out_buf.view(1, qh, d).cpu(), ref) >= COS_MIN
+        assert adapter.get_stats(runner)["total_compressed_tokens"] == 200
+    finally:
+        adapter.set_mode(adapter.MODE_OFF)

@@ -212,7 +212,8 @@ def decode(consts: LayerConstants, pool: BlockPool, ws: Workspace, query: torch.
            ring_lens: Optional[torch.Tensor] = None, max_ring_len: int = 0,
            ring_stride_seq: int = 0, ring_stride_token: int = 0, scale: Optional[float] = None,
            min_history: int = 16, num_splits: int = 0, out: Optional[torch.Tensor] = None,
-           query_prepared: bool = False, kernel: int = 0, static_scratch: bool = False) -> torch.Tensor:
+           query_prepared: bool = False, kernel: int = 0, static_scratch: bool = False,
+           append_k: Optional[torch.Tensor] = None, append_v: Optional[torch.Tensor] = None) -> torch.Tensor:
     """query (B, Qh, D) -> out (B, Qh, D) in the query dtype.
 
     static_scratch=True routes through tq_decode_static: no workspace tensor is
@@ -247,6 +248,9 @@ def decode(consts: LayerConstants, pool: BlockPool, ws: Workspace, query: torch.
     a.out, a.num_splits = out.data_ptr(), splits
     a.query_prepared = 1 if query_prepared else 0
     a.kernel = kernel
+    if append_k is not None:      # (B, H, D) new exact token per sequence, appended on the device before attending
+        a.append_k, a.append_v = append_k.data_ptr(), append_v.data_ptr()
+        a.ring_capacity = ring_k.shape[-3]
     if static_scratch:
         check(lib().tq_decode_static(C.byref(consts.c), C.byref(pool.c), C.byref(a), stream_ptr(consts.device)),
               f"tq_decode_static (built-in scratch of {lib().tq_decode_static_scratch_bytes()} bytes)")

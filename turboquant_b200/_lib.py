@@ -57,7 +57,8 @@ class tq_decode_args(C.Structure):
                 ("ring_v", C.c_void_p), ("ring_dtype", C.c_int32), ("ring_lens", C.c_void_p),
                 ("max_ring_len", C.c_int32), ("ring_stride_seq", C.c_int64), ("ring_stride_token", C.c_int64),
                 ("scale", C.c_float), ("out", C.c_void_p), ("workspace", C.c_void_p),
-                ("workspace_bytes", C.c_size_t), ("num_splits", C.c_int32), ("query_prepared", C.c_int32), ("kernel", C.c_int32)]
+                ("workspace_bytes", C.c_size_t), ("num_splits", C.c_int32), ("query_prepared", C.c_int32), ("kernel", C.c_int32), ("append_k", C.c_void_p), ("append_v", C.c_void_p),
+                ("ring_capacity", C.c_int32)]
 
 
 # name -> (restype, argtypes); every symbol include/turboquant_b200.h declares

@@ -24,11 +24,41 @@ namespace {
 // kernel directly: every entry is scaled by a power of two derived from the
 // query's norm alone (|q Pi^T|_inf <= |q|_2 and |q S^T|_inf <= 2 sqrt(D) |q|_2
 // for a Gaussian S), so no CTA needs another CTA's columns.
+// Optional extra job of the query-prep launch: append one new exact token per
+// sequence to the ring (capture.py:219-228 does this with tensor slicing).
+struct RingAppend {
+    const void* new_k;     // (B, H, D) in the ring's dtype; nullptr = nothing to append
+    const void* new_v;
+    void* ring_k;
+    void* ring_v;
+    int32_t* ring_lens;    // position of the new token; incremented
+    int elem_bytes, B, H, capacity;
+    int64_t stride_seq, stride_token;   // in elements
+};
+
 template <int D>
 __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ q, int dt, int64_t nvec,
                                                        const float* __restrict__ pi_t,
                                                        const float* __restrict__ s_t, float* __restrict__ out,
-                                                       uint32_t* __restrict__ frag, int G, int Qh) {
+                                                       uint32_t* __restrict__ frag, int G, int Qh,
+                                                       const RingAppend ap) {
+    // the decode kernel may start its set-up now; it waits for this grid before it reads our output
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (ap.new_k != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
+        const int row_bytes = D * ap.elem_bytes, chunks_per_row = row_bytes / 16;
+        for (int i = threadIdx.x; i < ap.B * ap.H * chunks_per_row; i += 256) {
+            const int c = i % chunks_per_row, h = (i / chunks_per_row) % ap.H, b = i / (chunks_per_row * ap.H);
+            const int pos = ap.ring_lens[b];
+            if (pos < 0 || pos >= ap.capacity) continue;
+            const int64_t dst = ((int64_t)b * ap.stride_seq + (int64_t)pos * ap.stride_token + (int64_t)h * D) * ap.elem_bytes;
+            const int64_t src = ((int64_t)(b * ap.H + h) * D) * ap.elem_bytes;
+            *reinterpret_cast<uint4*>((char*)ap.ring_k + dst + c * 16) = *reinterpret_cast<const uint4*>((const char*)ap.new_k + src + c * 16);
+            *reinterpret_cast<uint4*>((char*)ap.ring_v + dst + c * 16) = *reinterpret_cast<const uint4*>((const char*)ap.new_v + src + c * 16);
+        }
+        __syncthreads();
+        for (int b = threadIdx.x; b < ap.B; b += 256)
+            if (ap.ring_lens[b] >= 0 && ap.ring_lens[b] < ap.capacity) ap.ring_lens[b] += 1;
+    }
     __shared__ float qsm[4 * D];          // queries
     __shared__ float red[8 * 4 * 32];     // partial sums
     __shared__ float qn2[4];              // squared norms
@@ -95,12 +125,12 @@ __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ 
 }
 
 int launch_qprep(const void* q, int dt, int64_t nvec, int D, const float* pi_t, const float* s_t, float* out,
-                 uint32_t* frag, int G, int Qh, cudaStream_t st) {
+                 uint32_t* frag, int G, int Qh, const RingAppend& ap, cudaStream_t st) {
     dim3 grid((unsigned)(2 * D / 32), (unsigned)((nvec + 3) / 4));
     if (D == 128)
-        tq_qprep_kernel<128><<<grid, 256, 0, st>>>(q, dt, nvec, pi_t, s_t, out, frag, G, Qh);
+        tq_qprep_kernel<128><<<grid, 256, 0, st>>>(q, dt, nvec, pi_t, s_t, out, frag, G, Qh, ap);
     else
-        tq_qprep_kernel<256><<<grid, 256, 0, st>>>(q, dt, nvec, pi_t, s_t, out, frag, G, Qh);
+        tq_qprep_kernel<256><<<grid, 256, 0, st>>>(q, dt, nvec, pi_t, s_t, out, frag, G, Qh, ap);
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 
@@ -446,10 +476,30 @@ extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_
     uint8_t* ws = (uint8_t*)a->workspace;
     float* qprep = (float*)(ws + w.off_qprep);
     uint32_t* qfrag = (uint32_t*)(ws + w.off_qfrag);
+    RingAppend ap = {};
+    if (a->append_k != nullptr) {
+        if (!has_ring || !a->append_v || a->query_prepared) return TQ_ERR_NULL;
+        if (a->ring_capacity < a->max_ring_len) return TQ_ERR_SHAPE;
+        const int eb = (int)tq_dtype_size(a->ring_dtype);
+        if (((uintptr_t)a->append_k | (uintptr_t)a->append_v | (uintptr_t)a->ring_k | (uintptr_t)a->ring_v) & 15)
+            return TQ_ERR_ALIGN;
+        if ((a->ring_stride_seq * eb) % 16 || (a->ring_stride_token * eb) % 16) return TQ_ERR_ALIGN;
+        ap.new_k = a->append_k;
+        ap.new_v = a->append_v;
+        ap.ring_k = const_cast<void*>(a->ring_k);
+        ap.ring_v = const_cast<void*>(a->ring_v);
+        ap.ring_lens = const_cast<int32_t*>(a->ring_lens);
+        ap.elem_bytes = eb;
+        ap.B = a->batch;
+        ap.H = H;
+        ap.capacity = a->ring_capacity;
+        ap.stride_seq = a->ring_stride_seq;
+        ap.stride_token = a->ring_stride_token;
+    }
     if (!a->query_prepared) {
         const int64_t nvec = (int64_t)a->batch * a->num_q_heads;
         if (launch_qprep(a->query, a->q_dtype, nvec, D, consts->pi_t, consts->s_t, qprep, qfrag, G, a->num_q_heads,
-                         st) != TQ_OK)
+                         ap, st) != TQ_OK)
             return TQ_ERR_CUDA;
     }
 
@@ -524,7 +574,7 @@ extern "C" int tq_scores(const tq_consts* consts, const tq_pool* pool, const int
     cudaStream_t st = (cudaStream_t)stream;
     float* qprep = (float*)((uint8_t*)workspace + TQ_WS_HEADER_BYTES);
     const int64_t nvec = (int64_t)H * n_q;
-    if (launch_qprep(query, q_dtype, nvec, D, consts->pi_t, consts->s_t, qprep, nullptr, 1, 1, st) != TQ_OK)
+    if (launch_qprep(query, q_dtype, nvec, D, consts->pi_t, consts->s_t, qprep, nullptr, 1, 1, RingAppend{}, st) != TQ_OK)
         return TQ_ERR_CUDA;
 
     const TqLayout L = tq_make_layout(D, consts->cfg.key_bits, consts->cfg.value_bits);

@@ -82,7 +82,9 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
     const int b = blockIdx.z, h = blockIdx.y, x = blockIdx.x;
 
     if (x >= p.num_splits) {
-        // exact ring tokens: CUDA-core fp32 path shared with the generic kernel
+        // exact ring tokens: CUDA-core fp32 path shared with the generic kernel.  The ring and its
+        // length may have been written by the query-prep grid this launch overlaps with.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         float* scratch = reinterpret_cast<float*>(stages);
         ring_part<D, GP>(p, b, h, x, scratch, scratch + D * GP, scratch + D * GP + GP * RING_TOK, ml);
         ticket_and_merge<D, GP>(p, b, h, wsm);
@@ -124,6 +126,8 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
     }
 
     // ---- query fragments, prepared once per (sequence, kv head) by the query-prep kernel ----
+    // (launched with programmatic stream serialisation: everything above overlapped that kernel)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     uint32_t bq[2 * KS];
     uint32_t bsk[SPLITB ? 2 * KS : 1];
     float k0[2], k1[2], kb0[2], ksg[2], kq[2];
@@ -493,9 +497,17 @@ int launch_mma(const DecodeParams& p, int batch, cudaStream_t st) {
             return TQ_ERR_CUDA;
         smem_set = smem;
     }
-    dim3 grid((unsigned)nslot, (unsigned)p.H, (unsigned)batch);
-    kern<<<grid, NT, smem, st>>>(p);
-    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)nslot, (unsigned)p.H, (unsigned)batch);
+    cfg.blockDim = dim3(NT);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // start while the previous kernel drains
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kern, p) == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 
 }  // namespace
