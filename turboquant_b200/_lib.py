@@ -100,11 +100,12 @@ def lib() -> C.CDLL:
     """The loaded library; raises if it has not been built."""
     global _lib
     if _lib is None:
-        if not os.path.exists(LIB_PATH):
+        path = os.environ.get("TQ_B200_LIB", LIB_PATH)   # a differently built library, for A/B measurements
+        if not os.path.exists(path):
             raise RuntimeError(
-                f"{LIB_PATH} is missing: build it with `python -m turboquant_b200.build` "
+                f"{path} is missing: build it with `python -m turboquant_b200.build` "
                 "(there is no CPU or PyTorch fallback for this path)")
-        handle = C.CDLL(LIB_PATH)
+        handle = C.CDLL(path)
         for name, (restype, argtypes) in SIGNATURES.items():
             fn = getattr(handle, name)
             fn.restype = restype

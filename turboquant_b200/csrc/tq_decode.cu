@@ -141,8 +141,9 @@ __global__ void __launch_bounds__(DEC_THREADS) tq_decode_kernel(const DecodePara
     const int BB = L.block_bytes;
 
     extern __shared__ __align__(128) uint8_t smem[];
-    uint8_t* stages = smem;                                                        // [NSTAGE][4*BB]
-    float* qr = reinterpret_cast<float*>(smem + NSTAGE * TILE_BLOCKS * BB);        // [D][GP]
+    uint8_t* stages = smem;                                                        // [NSTAGE][4*BB]; ring CTAs: K/V rows
+    const int stage_bytes = max(NSTAGE * TILE_BLOCKS * BB, 2 * RING_TOK * D * 4);  // same rule as the launcher
+    float* qr = reinterpret_cast<float*>(smem + stage_bytes);                      // [D][GP]
     float* qs = qr + D * GP;                                                       // [D][GP]
     float* sp = qs + D * GP;                                                       // [2][GP][64]
     float* pp = sp + 2 * GP * TILE_TOK;                                            // [64][GP]
@@ -294,7 +295,8 @@ __global__ void __launch_bounds__(DEC_THREADS) tq_decode_kernel(const DecodePara
 
     // ------------------------------ exact ring ------------------------------
     __syncthreads();
-    ring_part<D, GP>(p, b, h, x, qr, sp, pp, m_run);   // m_run, l_run are adjacent: [2*GP]
+    // m_run, l_run are adjacent: [2*GP]; the stage region (sized for it by the launcher) holds the ring rows
+    ring_part<D, GP>(p, b, h, x, qr, sp, pp, m_run, stages, stages + RING_TOK * D * 4);
     ticket_and_merge<D, GP>(p, b, h, wsm);
 }
 
@@ -363,6 +365,7 @@ __global__ void __launch_bounds__(DEC_THREADS) tq_scores_kernel(const ScoreParam
 template <int D, int GP>
 size_t decode_smem_bytes(int block_bytes, int nslot) {
     size_t s = (size_t)NSTAGE * TILE_BLOCKS * block_bytes;
+    if (s < (size_t)2 * RING_TOK * D * 4) s = (size_t)2 * RING_TOK * D * 4;   // ring CTAs stage their K/V rows here
     s += sizeof(float) * (2 * D * GP + 2 * GP * TILE_TOK + TILE_TOK * GP + 3 * GP + TQ_MAX_CENTROIDS);
     s += sizeof(uint64_t) * NSTAGE;
     // merge scratch sized for at least 128 partials so that the launch size

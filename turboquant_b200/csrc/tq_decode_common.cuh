@@ -241,11 +241,14 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
 
 // Exact attention over this CTA's slice of the ring (up to RING_TOK tokens),
 // fp32 like the reference's matmul path (score.py:154-170); works for any
-// block size.  Writes the CTA's partial itself.
-// scratch: qf [D][GP], sc [GP][RING_TOK], pp [RING_TOK][GP], ml [2*GP].
+// block size.  The slice's key and value rows are first staged in shared
+// memory with 16-byte loads that are all in flight at once; everything after
+// that runs out of shared memory.  Writes the CTA's partial itself.
+// scratch: qf [D][GP], sc [GP][RING_TOK], pp [RING_TOK][GP] floats, ml [2*GP],
+//          kst / vst: RING_TOK * D * element size bytes each, 16-byte aligned.
 template <int D, int GP>
 __device__ __forceinline__ void ring_part(const DecodeParams& p, int b, int h, int slot_idx, float* qf, float* sc,
-                                          float* pp, float* ml) {
+                                          float* pp, float* ml, uint8_t* kst, uint8_t* vst) {
     const int tid = threadIdx.x, nt = blockDim.x, warp = tid >> 5, lane = tid & 31;
     const int rs = slot_idx - p.num_splits;
     const int R = p.ring_lens ? p.ring_lens[b] : 0;
@@ -257,18 +260,26 @@ __device__ __forceinline__ void ring_part(const DecodeParams& p, int b, int h, i
         ml[GP + tid] = 0.f;
     }
     if (nr > 0) {
+        const int eb = p.ring_dtype == TQ_F32 ? 4 : 2;
+        const int row_chunks = D * eb / 16;
+        for (int i = tid; i < nr * row_chunks; i += nt) {
+            const int t = i / row_chunks, c = i % row_chunks;
+            const int64_t off = ((int64_t)b * p.ring_stride_seq + (int64_t)(r0 + t) * p.ring_stride_token +
+                                 (int64_t)h * D) * eb + c * 16;
+            reinterpret_cast<uint4*>(kst)[i] = *reinterpret_cast<const uint4*>((const char*)p.ring_k + off);
+            reinterpret_cast<uint4*>(vst)[i] = *reinterpret_cast<const uint4*>((const char*)p.ring_v + off);
+        }
         for (int i = tid; i < D * GP; i += nt) {
             const int j = i / GP, g = i % GP;
             qf[i] = g < p.G ? tq_load_any(p.query, ((int64_t)b * p.Qh + h * p.G + g) * D + j, p.q_dtype) : 0.f;
         }
         __syncthreads();
         for (int t = warp; t < nr; t += nt / 32) {
-            const int64_t off = (int64_t)b * p.ring_stride_seq + (int64_t)(r0 + t) * p.ring_stride_token + (int64_t)h * D;
             float a[GP];
 #pragma unroll
             for (int g = 0; g < GP; ++g) a[g] = 0.f;
             for (int j = lane; j < D; j += 32) {
-                const float kx = tq_load_any(p.ring_k, off + j, p.ring_dtype);
+                const float kx = tq_load_any(kst, t * D + j, p.ring_dtype);
 #pragma unroll
                 for (int g = 0; g < GP; ++g) a[g] = fmaf(qf[j * GP + g], kx, a[g]);
             }
@@ -295,10 +306,7 @@ __device__ __forceinline__ void ring_part(const DecodeParams& p, int b, int h, i
     for (int i = tid; i < GP * D; i += nt) {
         const int g = i / D, d = i % D;
         float acc = 0.f;
-        for (int t = 0; t < nr; ++t) {
-            const int64_t off = (int64_t)b * p.ring_stride_seq + (int64_t)(r0 + t) * p.ring_stride_token + (int64_t)h * D + d;
-            acc = fmaf(pp[t * GP + g], tq_load_any(p.ring_v, off, p.ring_dtype), acc);
-        }
+        for (int t = 0; t < nr; ++t) acc = fmaf(pp[t * GP + g], tq_load_any(vst, t * D + d, p.ring_dtype), acc);
         mine[2 * GP + i] = acc;
     }
     if (tid < 2 * GP) mine[tid] = ml[tid];

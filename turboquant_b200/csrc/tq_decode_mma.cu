@@ -86,7 +86,9 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
         // length may have been written by the query-prep grid this launch overlaps with.
         asm volatile("griddepcontrol.wait;" ::: "memory");
         float* scratch = reinterpret_cast<float*>(stages);
-        ring_part<D, GP>(p, b, h, x, scratch, scratch + D * GP, scratch + D * GP + GP * RING_TOK, ml);
+        uint8_t* kst = reinterpret_cast<uint8_t*>(scratch + D * GP + 2 * GP * RING_TOK);   // 16-byte aligned
+        ring_part<D, GP>(p, b, h, x, scratch, scratch + D * GP, scratch + D * GP + GP * RING_TOK, ml, kst,
+                         kst + RING_TOK * D * 4);
         ticket_and_merge<D, GP>(p, b, h, wsm);
         return;
     }
