@@ -36,6 +36,25 @@ constexpr int NW = 12;     // warps per CTA; one CTA per SM
 constexpr int NT = NW * 32;
 constexpr int BT_MAX = 1024;   // block-table entries a CTA keeps in shared memory
 
+#ifdef TQ_TRACE
+// Debug build only: per-CTA phase time stamps (ns) for latency analysis.
+__device__ unsigned long long g_tq_trace[4096 * 8];
+__device__ __forceinline__ unsigned long long tq_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TQ_STAMP(i)                                                                                       \
+    do {                                                                                                  \
+        if (threadIdx.x == 0) {                                                                           \
+            const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);               \
+            if (cta < 4096) g_tq_trace[cta * 8 + (i)] = tq_now();                                         \
+        }                                                                                                 \
+    } while (0)
+#else
+#define TQ_STAMP(i)
+#endif
+
 __device__ __forceinline__ float pow2i(int e) { return __int_as_float((127 + e) << 23); }   // 2^e, -126 <= e <= 127
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -80,6 +99,7 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tig = lane & 3;
     const int b = blockIdx.z, h = blockIdx.y, x = blockIdx.x;
+    TQ_STAMP(0);
 
     if (x >= p.num_splits) {
         // exact ring tokens: CUDA-core fp32 path shared with the generic kernel.  The ring and its
@@ -89,7 +109,9 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
         uint8_t* kst = reinterpret_cast<uint8_t*>(scratch + D * GP + 2 * GP * RING_TOK);   // 16-byte aligned
         ring_part<D, GP>(p, b, h, x, scratch, scratch + D * GP, scratch + D * GP + GP * RING_TOK, ml, kst,
                          kst + RING_TOK * D * 4);
+        TQ_STAMP(5);
         ticket_and_merge<D, GP>(p, b, h, wsm);
+        TQ_STAMP(6);
         return;
     }
 
@@ -129,7 +151,9 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
 
     // ---- query fragments, prepared once per (sequence, kv head) by the query-prep kernel ----
     // (launched with programmatic stream serialisation: everything above overlapped that kernel)
+    TQ_STAMP(1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    TQ_STAMP(2);
     uint32_t bq[2 * KS];
     uint32_t bsk[SPLITB ? 2 * KS : 1];
     float k0[2], k1[2], kb0[2], ksg[2], kq[2];
@@ -196,6 +220,7 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
 
     const int tokA = 4 * (gid >> 1) + (gid & 1), tokB = tokA + 2;   // tokens of score rows gid, gid+8
     bool failed = false;
+    TQ_STAMP(3);
 
     for (int it = 0; it < cnt; ++it) {
         const int st = it % NSTW;
@@ -388,6 +413,7 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
         }
     }
     if (failed && lane == 0) atomicCAS(p.status, 0, (int)TQ_ERR_TIMEOUT);
+    if (warp == 0) TQ_STAMP(4);
 
     // ------------------------------ combine the warps of the CTA ------------------------------
 #pragma unroll
@@ -474,7 +500,9 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
         }
     }
     __syncthreads();   // wsm is reused by the merge
+    TQ_STAMP(5);
     ticket_and_merge<D, GP>(p, b, h, wsm);
+    TQ_STAMP(6);
 }
 
 template <int D, bool SPLITB>
@@ -513,6 +541,12 @@ int launch_mma(const DecodeParams& p, int batch, cudaStream_t st) {
 }
 
 }  // namespace
+
+#ifdef TQ_TRACE
+extern "C" int tq_debug_read_trace(unsigned long long* out, int n) {
+    return cudaMemcpyFromSymbol(out, g_tq_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -5;
+}
+#endif
 
 namespace tqdec {
 
