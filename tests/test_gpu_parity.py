@@ -418,13 +418,14 @@ def test_errors_are_loud(dev):
         CompressedKVStore(64, 2, device=dev)
 
 
-@pytest.mark.parametrize("d,h,qh,vb,n", [(256, 4, 16, 2, 5000), (128, 8, 32, 2, 3000), (128, 8, 32, 4, 2000),
-                                         (128, 4, 32, 2, 2500), (256, 2, 6, 4, 1111), (128, 2, 14, 4, 999)])
-def test_tensor_core_kernel_matches_cuda_core_kernel(d, h, qh, vb, n, dev):
+@pytest.mark.parametrize("d,h,qh,vb,n,kb", [(256, 4, 16, 2, 5000, 3), (128, 8, 32, 2, 3000, 3), (128, 8, 32, 4, 2000, 3),
+                                            (128, 4, 32, 2, 2500, 3), (256, 2, 6, 4, 1111, 3), (128, 2, 14, 4, 999, 3),
+                                            (128, 8, 32, 4, 2100, 4), (128, 2, 16, 2, 777, 4), (128, 4, 4, 4, 1500, 4)])
+def test_tensor_core_kernel_matches_cuda_core_kernel(d, h, qh, vb, n, kb, dev):
     """The two decode kernels on the same pool, same splits: the tensor-core one
     (fp16 operands) against the fp32 CUDA-core one, with and without a ring."""
     from turboquant_b200 import _engine as E
-    c = E.LayerConstants(d, 3, vb, dev, seed=49)
+    c = E.LayerConstants(d, kb, vb, dev, seed=49)
     k, v = O.synth_kv(n + 70, h, d, seed=31 + n, dtype=torch.bfloat16)
     pool = E.BlockPool(c, h, E.blocks_for(n))
     bt = E.identity_block_table(pool.num_blocks, dev)

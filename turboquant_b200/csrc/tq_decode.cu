@@ -40,7 +40,7 @@ template <int D>
 __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ q, int dt, int64_t nvec,
                                                        const float* __restrict__ pi_t,
                                                        const float* __restrict__ s_t, float* __restrict__ out,
-                                                       uint32_t* __restrict__ frag, int G, int Qh,
+                                                       uint32_t* __restrict__ frag, int G, int Qh, int mse_bits,
                                                        const RingAppend ap) {
     // the decode kernel may start its set-up now; it waits for this grid before it reads our output
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -105,16 +105,22 @@ __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ 
                 const int64_t vec = v0 + v;
                 const int qh = (int)(vec % Qh), g = qh % G;
                 const int64_t pair = (vec / Qh) * (Qh / G) + qh / G;   // (sequence, kv head)
-                uint32_t* base = frag + pair * qf_words(D, G);
+                const bool split = G > 4 || mse_bits == 3;   // separate rotated / sketched fragment sets
+                uint32_t* base = frag + pair * qf_words(D, split ? 8 : 4);
                 const float bound = sqrtf(qn2[v]) * (which ? 2.f * sqrtf((float)D) : 1.f);
                 int e = 0;
                 if (bound > 0.f && bound < 3.0e38f) e = max(-100, min(100, 14 - ilogbf(bound)));
                 if (chunk == 0 && lane == 0) reinterpret_cast<float*>(base)[which * 8 + g] = (float)e;
                 const int tig = col / (D / 4), rem = col % (D / 4);
-                const int wi = rem >> 4, half = (rem >> 3) & 1, jf = rem & 7;
-                const int r = wi * 8 + jf;
-                const int sh = which ? sign_pos(sign_bit(wi, jf)) : 2 * code_pos(jf);
-                const bool split = G > 4;
+                int wi = rem >> 4, half = (rem >> 3) & 1, jf = rem & 7;
+                int r = wi * 8 + jf;
+                int sh = which ? sign_pos(sign_bit(wi, jf)) : 2 * code_pos(jf);
+                if (mse_bits == 3 && which == 0) {
+                    // nibble codes: registers pair adjacent dims, k-step = 4 dims, true centroid values (no scaling)
+                    r = rem >> 1;
+                    half = rem & 1;
+                    sh = 0;
+                }
                 const int gid = split ? g : g + 4 * which;
                 const int set = split ? which : 0;
                 __half* dst = reinterpret_cast<__half*>(base + QF_HDR + ((set * (D / 8) + r) * 32 + gid * 4 + tig));
@@ -125,12 +131,12 @@ __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ 
 }
 
 int launch_qprep(const void* q, int dt, int64_t nvec, int D, const float* pi_t, const float* s_t, float* out,
-                 uint32_t* frag, int G, int Qh, const RingAppend& ap, cudaStream_t st) {
+                 uint32_t* frag, int G, int Qh, int mse_bits, const RingAppend& ap, cudaStream_t st) {
     dim3 grid((unsigned)(2 * D / 32), (unsigned)((nvec + 3) / 4));
     if (D == 128)
-        tq_qprep_kernel<128><<<grid, 256, 0, st>>>(q, dt, nvec, pi_t, s_t, out, frag, G, Qh, ap);
+        tq_qprep_kernel<128><<<grid, 256, 0, st>>>(q, dt, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
     else
-        tq_qprep_kernel<256><<<grid, 256, 0, st>>>(q, dt, nvec, pi_t, s_t, out, frag, G, Qh, ap);
+        tq_qprep_kernel<256><<<grid, 256, 0, st>>>(q, dt, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 
@@ -409,7 +415,7 @@ WsLayout decode_ws_layout(int D, int B, int Qh, int H, int max_slots) {
     w.off_tickets = TQ_WS_HEADER_BYTES;
     w.off_qprep = w.off_tickets + (((size_t)B * H * sizeof(int32_t) + 255) / 256) * 256;
     w.off_qfrag = w.off_qprep + (((size_t)B * Qh * 2 * D * sizeof(float) + 255) / 256) * 256;
-    w.off_partials = w.off_qfrag + (((size_t)B * H * qf_words(D, G) * sizeof(uint32_t) + 255) / 256) * 256;
+    w.off_partials = w.off_qfrag + (((size_t)B * H * qf_words(D, 8) * sizeof(uint32_t) + 255) / 256) * 256;
     w.total = w.off_partials + (size_t)B * H * max_slots * GP * (D + 2) * sizeof(float);
     return w;
 }
@@ -502,7 +508,7 @@ extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_
     if (!a->query_prepared) {
         const int64_t nvec = (int64_t)a->batch * a->num_q_heads;
         if (launch_qprep(a->query, a->q_dtype, nvec, D, consts->pi_t, consts->s_t, qprep, qfrag, G, a->num_q_heads,
-                         ap, st) != TQ_OK)
+                         consts->cfg.key_bits - 1, ap, st) != TQ_OK)
             return TQ_ERR_CUDA;
     }
 
@@ -577,7 +583,7 @@ extern "C" int tq_scores(const tq_consts* consts, const tq_pool* pool, const int
     cudaStream_t st = (cudaStream_t)stream;
     float* qprep = (float*)((uint8_t*)workspace + TQ_WS_HEADER_BYTES);
     const int64_t nvec = (int64_t)H * n_q;
-    if (launch_qprep(query, q_dtype, nvec, D, consts->pi_t, consts->s_t, qprep, nullptr, 1, 1, RingAppend{}, st) != TQ_OK)
+    if (launch_qprep(query, q_dtype, nvec, D, consts->pi_t, consts->s_t, qprep, nullptr, 1, 1, 2, RingAppend{}, st) != TQ_OK)
         return TQ_ERR_CUDA;
 
     const TqLayout L = tq_make_layout(D, consts->cfg.key_bits, consts->cfg.value_bits);

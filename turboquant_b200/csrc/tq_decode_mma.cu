@@ -79,14 +79,19 @@ __device__ __forceinline__ uint32_t hmul2_sat(uint32_t a, uint32_t b) {
     return *reinterpret_cast<const uint32_t*>(&r);
 }
 
-template <int D, int VAL_BITS, bool SPLITB>
+// MSE_BITS == 2: bit-plane scores as described above.  MSE_BITS == 3 (codes in nibbles, 8 centroids): the
+// nibbles are byte-table selectors - two PRMTs look up the low and high bytes of four fp16 centroids, two more
+// interleave them into two A registers - so the A operand holds true centroid values, one plane, and the
+// rotated query needs no per-position scaling; it always uses separate rotated / sketched fragment sets.
+template <int D, int MSE_BITS, int VAL_BITS, bool SPLITB>
 __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams p) {
+    static_assert(MSE_BITS == 2 || SPLITB, "3-bit codes use separate rotated / sketched fragment sets");
     constexpr int GP = SPLITB ? 8 : 4;
     constexpr int KS = D / 16;    // score k-steps
-    constexpr int NWK = D / 64;   // code words per thread per token
+    constexpr int NWK = D / 64;   // 32-bit words of 2-bit codes per thread per token; twice the sign words
     constexpr int NMB = D / 16;   // value M-blocks
     constexpr int NG = D / 32;
-    const TqLayout L = tq_make_layout(D, 3, VAL_BITS);
+    const TqLayout L = tq_make_layout(D, MSE_BITS + 1, VAL_BITS);
     const int BB = L.block_bytes;
 
     extern __shared__ __align__(128) uint8_t smem[];
@@ -158,7 +163,7 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
     uint32_t bsk[SPLITB ? 2 * KS : 1];
     float k0[2], k1[2], kb0[2], ksg[2], kq[2];
     {
-        const uint32_t* qf = p.qfrag + (int64_t)(b * p.H + h) * qf_words(D, p.G);
+        const uint32_t* qf = p.qfrag + (int64_t)(b * p.H + h) * qf_words(D, SPLITB ? 8 : 4);
         const float* hdr = reinterpret_cast<const float*>(qf);
         const bool is_sk = !SPLITB && gid >= 4;
         const int g_col = SPLITB ? gid : (gid & 3);             // head of this thread's B-fragment column
@@ -176,7 +181,7 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
             const int wi = r >> 3, j = r & 7;
             const float up_code = (float)(1 << (2 * code_pos(j))), up_sign = (float)(1 << sign_pos(sign_bit(wi, j)));
             const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&bq[r]));
-            sum_a = fmaf(v.x + v.y, is_sk ? up_sign : up_code, sum_a);
+            if (MSE_BITS == 2) sum_a = fmaf(v.x + v.y, is_sk ? up_sign : up_code, sum_a);
             if (SPLITB) {
                 const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&bsk[r]));
                 sum_b = fmaf(v2.x + v2.y, up_sign, sum_b);
@@ -199,9 +204,15 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
             const float s_sk = SPLITB ? __shfl_sync(0xffffffffu, sum_b, g * 4)
                                       : __shfl_sync(0xffffffffu, sum_a, ((g + 4) & 7) * 4);
             const int e_rot = (int)hdr[g], e_sk = (int)hdr[8 + g];
-            k0[i] = c0 * s_rot;
-            k1[i] = (c2 - c0) * pow2i(23 - e_rot);
-            kb0[i] = (c1 - c0) * pow2i(24 - e_rot);
+            if (MSE_BITS == 2) {
+                k0[i] = c0 * s_rot;
+                k1[i] = (c2 - c0) * pow2i(23 - e_rot);
+                kb0[i] = (c1 - c0) * pow2i(24 - e_rot);
+            } else {   // acc0 = sum centroid * (q * 2^e): undo the scale, no constant term, no second plane
+                k0[i] = 0.f;
+                k1[i] = 0.f;
+                kb0[i] = pow2i(-e_rot);
+            }
             ksg[i] = pow2i(25 - e_sk);
             kq[i] = s_sk;
         }
@@ -219,6 +230,19 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
     const int tokA = 4 * (gid >> 1) + (gid & 1), tokB = tokA + 2;   // tokens of score rows gid, gid+8
+    // 3-bit codes: low / high bytes of the eight fp16 centroids, selectable by PRMT
+    uint32_t t_lo0 = 0, t_lo1 = 0, t_hi0 = 0, t_hi1 = 0;
+    if (MSE_BITS == 3) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t a = __half_as_ushort(__float2half_rn(p.cb.centroids[i]));
+            const uint32_t c = __half_as_ushort(__float2half_rn(p.cb.centroids[4 + i]));
+            t_lo0 |= (a & 0xffu) << (8 * i);
+            t_hi0 |= (a >> 8) << (8 * i);
+            t_lo1 |= (c & 0xffu) << (8 * i);
+            t_hi1 |= (c >> 8) << (8 * i);
+        }
+    }
     bool failed = false;
     TQ_STAMP(3);
 
@@ -236,7 +260,7 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
 
         // ------------------------------ scores ------------------------------
         float acc1[4] = {0.f, 0.f, 0.f, 0.f}, acc0[4] = {0.f, 0.f, 0.f, 0.f}, accs[4] = {0.f, 0.f, 0.f, 0.f};
-        {
+        if (MSE_BITS == 2) {
             const uint32_t* cwA = reinterpret_cast<const uint32_t*>(rec + L.off_kcodes + tokA * L.kcode_row) + tig * NWK;
             const uint32_t* cwB = reinterpret_cast<const uint32_t*>(rec + L.off_kcodes + tokB * L.kcode_row) + tig * NWK;
             const uint32_t* swA = reinterpret_cast<const uint32_t*>(rec + L.off_ksigns + tokA * L.ksign_row) + tig * (NWK / 2);
@@ -281,6 +305,50 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
                         mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, bsk[2 * s], bsk[2 * s + 1]);
                     else
                         mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, bq[2 * s], bq[2 * s + 1]);
+                }
+            }
+        }
+        if (MSE_BITS == 3) {
+            constexpr int NWC = D / 32;    // words of nibble codes per thread per token (8 codes each)
+            constexpr int NWS = D / 128;   // sign words per thread per token
+            const uint4* cwA = reinterpret_cast<const uint4*>(rec + L.off_kcodes + tokA * L.kcode_row) + tig * (NWC / 4);
+            const uint4* cwB = reinterpret_cast<const uint4*>(rec + L.off_kcodes + tokB * L.kcode_row) + tig * (NWC / 4);
+            const uint32_t* swA = reinterpret_cast<const uint32_t*>(rec + L.off_ksigns + tokA * L.ksign_row) + tig * NWS;
+            const uint32_t* swB = reinterpret_cast<const uint32_t*>(rec + L.off_ksigns + tokB * L.ksign_row) + tig * NWS;
+#pragma unroll
+            for (int q4 = 0; q4 < NWC / 4; ++q4) {
+                const uint4 a4 = cwA[q4], b4 = cwB[q4];
+                const uint32_t wa[4] = {a4.x, a4.y, a4.z, a4.w}, wb[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+                for (int wi = 0; wi < 4; ++wi) {
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        // k-step s covers dims 8*(4*q4+wi) + 4*hf + {0,1 | 2,3} of this thread's slice
+                        const int s = (q4 * 4 + wi) * 2 + hf;
+                        const uint32_t sa = hf ? wa[wi] >> 16 : wa[wi], sb = hf ? wb[wi] >> 16 : wb[wi];
+                        const uint32_t la = __byte_perm(t_lo0, t_lo1, sa), ha = __byte_perm(t_hi0, t_hi1, sa);
+                        const uint32_t lb = __byte_perm(t_lo0, t_lo1, sb), hb = __byte_perm(t_hi0, t_hi1, sb);
+                        mma16816(acc0, __byte_perm(la, ha, 0x5140), __byte_perm(lb, hb, 0x5140),
+                                 __byte_perm(la, ha, 0x7362), __byte_perm(lb, hb, 0x7362), bq[2 * s], bq[2 * s + 1]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int sw = 0; sw < NWS; ++sw) {
+                const uint32_t sa_lo = __byte_perm(swA[sw], 0, 0x3120), sb_lo = __byte_perm(swB[sw], 0, 0x3120);
+                const uint32_t sa_hi = sa_lo >> 6, sb_hi = sb_lo >> 6;
+#pragma unroll
+                for (int wi = 2 * sw; wi < 2 * sw + 2; ++wi) {
+#pragma unroll
+                    for (int jj = 0; jj < 4; ++jj) {
+                        const int s = wi * 4 + jj;
+                        const int sb0 = sign_bit(wi, 2 * jj), sb1 = sign_bit(wi, 2 * jj + 1);
+                        const uint32_t n0 = 0x00010001u << sign_pos(sb0), n1 = 0x00010001u << sign_pos(sb1);
+                        const uint32_t ya0 = sb0 <= 9 ? sa_lo : sa_hi, yb0 = sb0 <= 9 ? sb_lo : sb_hi;
+                        const uint32_t ya1 = sb1 <= 9 ? sa_lo : sa_hi, yb1 = sb1 <= 9 ? sb_lo : sb_hi;
+                        mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, bsk[SPLITB ? 2 * s : 0],
+                                 bsk[SPLITB ? 2 * s + 1 : 0]);
+                    }
                 }
             }
         }
@@ -515,12 +583,12 @@ size_t mma_smem_bytes(int block_bytes, int nslot) {
     return s;
 }
 
-template <int D, int VAL_BITS, bool SPLITB>
+template <int D, int MSE_BITS, int VAL_BITS, bool SPLITB>
 int launch_mma(const DecodeParams& p, int batch, cudaStream_t st) {
-    const TqLayout L = tq_make_layout(D, 3, VAL_BITS);
+    const TqLayout L = tq_make_layout(D, MSE_BITS + 1, VAL_BITS);
     const int nslot = p.num_splits + p.ring_splits;
     const size_t smem = mma_smem_bytes<D, SPLITB>(L.block_bytes, nslot);
-    auto kern = tq_decode_mma_kernel<D, VAL_BITS, SPLITB>;
+    auto kern = tq_decode_mma_kernel<D, MSE_BITS, VAL_BITS, SPLITB>;
     static size_t smem_set = 0;
     if (smem > smem_set) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
@@ -553,21 +621,27 @@ namespace tqdec {
 int tq_decode_mma_launch(const DecodeParams& p, int D, int mse_bits, int val_bits, int batch, int max_seq_len,
                          cudaStream_t st, int* handled) {
     *handled = 0;
-    if (mse_bits != 2) return TQ_OK;                 // 3-bit (nibble) codes: generic kernel
+    const int nblk = (max_seq_len + TQ_BLOCK_TOKENS - 1) / TQ_BLOCK_TOKENS;
+    if ((nblk + p.num_splits - 1) / p.num_splits + 1 > BT_MAX) return TQ_OK;   // block-table slice kept in shared memory
+    if (mse_bits == 3) {
+        if (D != 128) return TQ_OK;                  // two fragment sets of 32 registers do not fit at 256
+        *handled = 1;
+        return val_bits == 2 ? launch_mma<128, 3, 2, true>(p, batch, st) : launch_mma<128, 3, 4, true>(p, batch, st);
+    }
+    if (mse_bits != 2) return TQ_OK;
     if (D == 256 && p.G > 4) return TQ_OK;           // would need two B-fragment sets of 32 registers
     // the bit-plane form needs a code book that is affine in the two code bits
     const float* c = p.cb.centroids;
     if (fabsf(c[3] - c[2] - c[1] + c[0]) > 1e-6f * fabsf(c[3] - c[0])) return TQ_OK;
-    const int nblk = (max_seq_len + TQ_BLOCK_TOKENS - 1) / TQ_BLOCK_TOKENS;
-    if ((nblk + p.num_splits - 1) / p.num_splits + 1 > BT_MAX) return TQ_OK;   // block-table slice kept in shared memory
     *handled = 1;
     const bool split = p.G > 4;
     if (D == 128) {
-        if (val_bits == 2) return split ? launch_mma<128, 2, true>(p, batch, st) : launch_mma<128, 2, false>(p, batch, st);
-        return split ? launch_mma<128, 4, true>(p, batch, st) : launch_mma<128, 4, false>(p, batch, st);
+        if (val_bits == 2)
+            return split ? launch_mma<128, 2, 2, true>(p, batch, st) : launch_mma<128, 2, 2, false>(p, batch, st);
+        return split ? launch_mma<128, 2, 4, true>(p, batch, st) : launch_mma<128, 2, 4, false>(p, batch, st);
     }
-    if (val_bits == 2) return launch_mma<256, 2, false>(p, batch, st);
-    return launch_mma<256, 4, false>(p, batch, st);
+    if (val_bits == 2) return launch_mma<256, 2, 2, false>(p, batch, st);
+    return launch_mma<256, 2, 4, false>(p, batch, st);
 }
 
 }  // namespace tqdec
