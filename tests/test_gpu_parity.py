@@ -514,6 +514,40 @@ def test_fused_ring_append(dev):
         assert torch.equal(out_a, out_b)
 
 
+def test_engine_decode_step_equals_two_calls(dev):
+    """KVCaptureEngine.decode_step == ingest_decode + compute_hybrid_attention, across ring
+    overflows (the ring is compressed when the token after a full ring arrives)."""
+    from turboquant_b200 import CompressedKVStore, KVCaptureEngine, compute_hybrid_attention
+    d, h, qh, cap, n0, steps = 128, 2, 8, 16, 100, 40
+    k, v = O.synth_kv(n0 + steps, h, d, seed=13, dtype=torch.bfloat16)
+    engs = []
+    for _ in range(2):
+        st = CompressedKVStore(d, h, device=dev, capacity_tokens=64)
+        e = KVCaptureEngine(st, ring_capacity=cap, device=dev)
+        e.ingest_prefill(k[:n0].to(dev), v[:n0].to(dev), n0)
+        engs.append(e)
+    a, b = engs
+    for s in range(steps):
+        q = O.synth_query(1, qh, d, seed=50 + s, dtype=torch.bfloat16).to(dev)
+        nk, nv = k[n0 + s:n0 + s + 1].to(dev), v[n0 + s:n0 + s + 1].to(dev)
+        out_a = a.decode_step(q, nk, nv, qh)
+        b.ingest_decode(nk, nv, 1)
+        out_b = compute_hybrid_attention(q, b.store, *b.ring.peek(), qh)
+        assert (a.total_compressed_tokens, a.total_buffered_tokens) == (b.total_compressed_tokens, b.total_buffered_tokens)
+        assert torch.equal(out_a, out_b), s
+        ka, kb_ = a.ring.peek()[0], b.ring.peek()[0]
+        assert torch.equal(ka, kb_)
+    assert a.store.num_chunks == b.store.num_chunks and a.ring.total_written == b.ring.total_written
+    assert a.store.workspace.status() == 0
+    # mixing the fused step with host-side ring writes keeps the device length in step
+    a.ingest_decode(k[:1].to(dev), v[:1].to(dev), 1)
+    b.ingest_decode(k[:1].to(dev), v[:1].to(dev), 1)
+    q = O.synth_query(1, qh, d, seed=99, dtype=torch.bfloat16).to(dev)
+    out_a = a.decode_step(q, k[1:2].to(dev), v[1:2].to(dev), qh)
+    b.ingest_decode(k[1:2].to(dev), v[1:2].to(dev), 1)
+    assert torch.equal(out_a, compute_hybrid_attention(q, b.store, *b.ring.peek(), qh))
+
+
 def test_vllm_adapter_hybrid_decode(dev):
     """The adapter end to end with a fake attention impl: prefill is captured (compressed history +
     ring), the decode step is answered from the compressed store and matches the oracle."""

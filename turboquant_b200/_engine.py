@@ -155,6 +155,17 @@ class Workspace:
         if self.buf.numel() < nbytes:
             self.buf = torch.zeros(nbytes, dtype=torch.uint8, device=self.device)
 
+    def ensure_decode(self, consts: "LayerConstants", b: int, qh: int, h: int, splits: int) -> None:
+        """Size the buffer for one tq_decode shape; the library is asked once per shape."""
+        key = (consts.head_dim, consts.key_bits, consts.value_bits, b, qh, h, splits)
+        need = _DECODE_WS_BYTES.get(key)
+        if need is None:
+            n = C.c_size_t(0)
+            check(lib().tq_decode_workspace_bytes(C.byref(consts.cfg), b, qh, h, splits, C.byref(n)),
+                  "tq_decode_workspace_bytes")
+            need = _DECODE_WS_BYTES[key] = n.value
+        self.ensure(need)
+
     @property
     def ptr(self) -> int:
         return self.buf.data_ptr()
@@ -170,6 +181,20 @@ class Workspace:
 
 
 _SM_COUNT: dict[int, int] = {}
+_DECODE_WS_BYTES: dict[tuple, int] = {}
+_CONST_I32: dict[tuple, torch.Tensor] = {}
+
+
+def const_i32(device, value: int, n: int = 1) -> torch.Tensor:
+    """A cached read-only int32 device tensor of `n` copies of `value` (sequence
+    and ring lengths handed to the kernels; small values only are cached)."""
+    if not 0 <= value <= 4096 or n > 64:
+        return torch.full((n,), value, dtype=torch.int32, device=device)
+    key = (str(device), value, n)
+    t = _CONST_I32.get(key)
+    if t is None:
+        t = _CONST_I32[key] = torch.full((n,), value, dtype=torch.int32, device=device)
+    return t
 
 
 def sm_count(device) -> int:
@@ -230,10 +255,7 @@ def decode(consts: LayerConstants, pool: BlockPool, ws: Workspace, query: torch.
     h = pool.num_kv_heads
     splits = num_splits or choose_splits(b, h, max_seq_len, sm_count(consts.device), max_ring_len)
     if not static_scratch:
-        need = C.c_size_t(0)
-        check(lib().tq_decode_workspace_bytes(C.byref(consts.cfg), b, qh, h, splits, C.byref(need)),
-              "tq_decode_workspace_bytes")
-        ws.ensure(need.value)
+        ws.ensure_decode(consts, b, qh, h, splits)
     a = _lib.tq_decode_args()
     a.query, a.q_dtype, a.batch, a.num_q_heads = query.data_ptr(), dtype_code(query.dtype), b, qh
     a.block_table = block_table.data_ptr()

@@ -8,6 +8,7 @@ from typing import Optional
 
 import torch
 
+from . import _engine as E
 from .store import CompressedKVStore
 
 
@@ -18,7 +19,8 @@ class RingBuffer:
     drained to make room (the whole buffer at once), else None.
     """
 
-    __slots__ = ("capacity", "num_kv_heads", "head_dim", "device", "dtype", "_k", "_v", "_pos", "_total_written")
+    __slots__ = ("capacity", "num_kv_heads", "head_dim", "device", "dtype", "_k", "_v", "_pos", "_total_written",
+                 "_len_dev", "_len_dev_val")
 
     def __init__(self, capacity: int, num_kv_heads: int, head_dim: int, device, dtype: torch.dtype = torch.bfloat16):
         self.capacity, self.num_kv_heads, self.head_dim = capacity, num_kv_heads, head_dim
@@ -27,6 +29,30 @@ class RingBuffer:
         self._v = torch.zeros(capacity, num_kv_heads, head_dim, device=device, dtype=dtype)
         self._pos = 0
         self._total_written = 0
+        self._len_dev: Optional[torch.Tensor] = None      # device copy of _pos, kept by device_len()
+        self._len_dev_val = -1
+
+    def device_len(self) -> torch.Tensor:
+        """(1,) int32 device tensor equal to `size`.  The fused decode step lets
+        the kernel write the new token at this position and increment it; the
+        host mirror is advanced by `advance_after_device_append`."""
+        if self._len_dev is None:
+            self._len_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self._len_dev_val = 0
+        if self._len_dev_val != self._pos:
+            self._len_dev.fill_(self._pos)
+            self._len_dev_val = self._pos
+        return self._len_dev
+
+    def advance_after_device_append(self) -> None:
+        self._pos += 1
+        self._len_dev_val += 1
+        self._total_written += 1
+
+    @property
+    def storage(self):
+        """The whole (capacity, H, D) key and value buffers."""
+        return self._k, self._v
 
     @property
     def size(self) -> int:
@@ -121,6 +147,35 @@ class KVCaptureEngine:
         overflow = self.ring.write(key[:num_tokens], value[:num_tokens], num_tokens)
         if overflow is not None:
             self.store.append_chunk(*overflow)
+
+    def decode_step(self, query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, num_query_heads: int,
+                    scale: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One decode token in one library call: `ingest_decode(key, value, 1)`
+        followed by `compute_hybrid_attention(query, store, *ring.peek(), ...)`
+        of the reference (capture.py:205-222, score.py:33-91), with the ring
+        write done on the device by the query-preparation launch.
+
+        query (1, Qh, D); key / value (1, H, D) in the ring's dtype -> (1, Qh, D).
+        Same results as the two separate calls; no reference counterpart as a
+        single call.
+        """
+        ring, store = self.ring, self.store
+        if ring.is_full:                      # the rare step: compress the full ring first
+            self.store.append_chunk(*ring.drain())
+        E.require_cuda(query, "query")
+        if key.dtype != ring.dtype or value.dtype != ring.dtype:
+            raise TypeError(f"key/value must be {ring.dtype} like the ring")
+        t, qh, d = query.shape
+        if t != 1 or qh != num_query_heads or d != store.head_dim:
+            raise ValueError(f"decode_step takes one query token of {num_query_heads} x {store.head_dim}")
+        rk, rv = ring.storage
+        lens = ring.device_len()
+        res = E.decode(store.consts, store.pool, store.workspace, query, store.block_table, store.seq_len_device,
+                       store.num_tokens, scale=scale, min_history=16, ring_k=rk, ring_v=rv, ring_lens=lens,
+                       max_ring_len=ring.size + 1, ring_stride_seq=0, ring_stride_token=rk.stride(0),
+                       append_k=key.contiguous(), append_v=value.contiguous(), out=out)
+        ring.advance_after_device_append()
+        return res
 
     def flush(self) -> None:
         data = self.ring.drain()

@@ -52,7 +52,7 @@ def compute_hybrid_attention(query: torch.Tensor, store: CompressedKVStore, rece
         if recent_k.stride(2) != 1 or recent_k.stride(1) != d or recent_v.stride() != recent_k.stride():
             recent_k, recent_v = recent_k.contiguous(), recent_v.contiguous()
         kwargs = dict(ring_k=recent_k, ring_v=recent_v,
-                      ring_lens=torch.full((t,), r, dtype=torch.int32, device=dev), max_ring_len=r,
+                      ring_lens=E.const_i32(dev, r, t), max_ring_len=r,
                       ring_stride_seq=0, ring_stride_token=recent_k.stride(0))
     return E.decode(store.consts, store.pool, store.workspace, query, bt, seq_lens, n, scale=scale,
                     min_history=MIN_HISTORY_FOR_TQ, **kwargs)
