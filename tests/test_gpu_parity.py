@@ -448,6 +448,56 @@ def test_tensor_core_kernel_matches_cuda_core_kernel(d, h, qh, vb, n, kb, dev):
             torch.testing.assert_close(a, b, rtol=3e-2, atol=3e-3)
 
 
+@pytest.mark.parametrize("d,h,qh,kb,vb", [(128, 8, 64, 3, 2), (256, 4, 16, 3, 2), (128, 8, 32, 4, 4)])
+def test_batched_paged_decode_many_ctas(d, h, qh, kb, vb, dev):
+    """More CTAs than SMs (the launch then uses two 8-warp CTAs per SM; with one slot per
+    (sequence, head) the CTA writes the output itself): 40 sequences of ragged length over a
+    shuffled block table, tensor-core kernel against the fp32 CUDA-core kernel and, for three
+    sequences, against the oracle's own store and attention."""
+    from turboquant_b200 import _engine as E
+    nseq, nmax, per = 40, 1200, 80            # `per` blocks per sequence in the table
+    c = E.LayerConstants(d, kb, vb, dev, seed=77)
+    k, v = O.synth_kv(nmax, h, d, seed=5, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(3)
+    perm = torch.randperm(nseq * per, generator=g).to(torch.int32)
+    bt = perm.view(nseq, per).to(dev)
+    pool = E.BlockPool(c, h, nseq * per)
+    lens_l = [int(x) for x in torch.randint(16, nmax + 1, (nseq,), generator=g)]
+    lens_l[0], lens_l[1], lens_l[2] = nmax, 5, 16      # full, below the 16-token minimum, exactly one block
+    shift = [int(x) for x in torch.randint(0, 50, (nseq,), generator=g)]
+    for s in range(nseq):
+        n = lens_l[s]
+        ks, vs = k.roll(shift[s], 0)[:n].to(dev), v.roll(shift[s], 0)[:n].to(dev)
+        E.store(c, pool, ks.contiguous(), vs.contiguous(), stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h,
+                block_table=bt[s], start_pos=0)
+    lens = torch.tensor(lens_l, dtype=torch.int32, device=dev)
+    q = O.synth_query(nseq, qh, d, seed=12, dtype=torch.bfloat16).to(dev)
+    rk = k[:48].to(dev).contiguous().unsqueeze(0).expand(nseq, -1, -1, -1).contiguous()
+    rv = v[:48].to(dev).contiguous().unsqueeze(0).expand(nseq, -1, -1, -1).contiguous()
+    rl = torch.tensor([(7 * s) % 49 for s in range(nseq)], dtype=torch.int32, device=dev)
+    ws = E.Workspace(dev)
+    for splits, ring in ((1, False), (1, True), (3, False)):
+        kw = dict(ring_k=rk, ring_v=rv, ring_lens=rl, max_ring_len=48, ring_stride_seq=48 * h * d,
+                  ring_stride_token=h * d) if ring else {}
+        a = E.decode(c, pool, ws, q, bt, lens, nmax, num_splits=splits, kernel=0, **kw).float()
+        b = E.decode(c, pool, ws, q, bt, lens, nmax, num_splits=splits, kernel=1, **kw).float()
+        assert ws.status() == 0
+        assert torch.isfinite(a).all()
+        if not ring:
+            assert float(a[1].abs().max()) == 0.0            # history below 16 tokens is ignored
+        assert _cos(a, b) >= 0.99995, (splits, ring, _cos(a, b))
+        torch.testing.assert_close(a, b, rtol=3e-2, atol=3e-3)
+    # the oracle's own store + attention for a few sequences (no ring, one slot)
+    a = E.decode(c, pool, ws, q, bt, lens, nmax, num_splits=1).cpu()
+    for s in (0, 2, 7):
+        n = lens_l[s]
+        ost = O.OracleStore(d, h, kb, vb, c.centroids_cpu, c.boundaries_cpu, pi=c.Pi.cpu(), s=c.S.cpu())
+        ost.append_chunk(k.roll(shift[s], 0)[:n], v.roll(shift[s], 0)[:n])
+        ref = O.hybrid_attention(q[s:s + 1].cpu(), ost.get_flat_cache(), None, None, h, c.Pi.cpu(), c.S.cpu(),
+                                 c.centroids_cpu)
+        assert _cos(a[s:s + 1], ref) >= COS_MIN, (s, _cos(a[s:s + 1], ref))
+
+
 @pytest.mark.parametrize("kb,vb,h,n", [(3, 2, 8, 8192), (4, 4, 4, 3000), (3, 4, 2, 129), (4, 2, 1, 16), (3, 2, 3, 2047)])
 def test_tensor_core_store_matches_fp32_store_and_oracle(kb, vb, h, n, dev):
     """tcgen05 store kernel (head_dim 128, bf16, block-aligned start) against the fp32 store

@@ -32,8 +32,11 @@ using namespace tqdec;
 namespace {
 
 constexpr int NSTW = 4;    // bulk-copy stages per warp, one block record each
-constexpr int NW = 12;     // warps per CTA; one CTA per SM
-constexpr int NT = NW * 32;
+// Warps per CTA.  A launch that fits one wave runs 12-warp CTAs, one per SM (all of an SM's warps
+// share one set of query fragments and one merge).  A launch of several waves runs 8-warp CTAs, two
+// per SM, so that the set-up and the merge of one CTA overlap the main loop of the other.
+constexpr int NW_WAVE = 12;
+constexpr int NW_MULTI = 8;
 constexpr int BT_MAX = 1024;   // block-table entries a CTA keeps in shared memory
 
 #ifdef TQ_TRACE
@@ -83,9 +86,10 @@ __device__ __forceinline__ uint32_t hmul2_sat(uint32_t a, uint32_t b) {
 // nibbles are byte-table selectors - two PRMTs look up the low and high bytes of four fp16 centroids, two more
 // interleave them into two A registers - so the A operand holds true centroid values, one plane, and the
 // rotated query needs no per-position scaling; it always uses separate rotated / sketched fragment sets.
-template <int D, int MSE_BITS, int VAL_BITS, bool SPLITB>
-__global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams p) {
+template <int D, int MSE_BITS, int VAL_BITS, bool SPLITB, int NW>
+__global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma_kernel(const DecodeParams p) {
     static_assert(MSE_BITS == 2 || SPLITB, "3-bit codes use separate rotated / sketched fragment sets");
+    constexpr int NT = NW * 32;
     constexpr int GP = SPLITB ? 8 : 4;
     constexpr int KS = D / 16;    // score k-steps
     constexpr int NWK = D / 64;   // 32-bit words of 2-bit codes per thread per token; twice the sign words
@@ -546,6 +550,31 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
         mxl[GP + tid] = lsum;
     }
     __syncthreads();
+    if (p.num_splits + p.ring_splits == 1) {
+        // the only CTA of this (sequence, kv head): normalise and write the output, no global round trip
+        for (int i = tid; i < p.G * (D / 4); i += NT) {
+            const int g = i / (D / 4), d = (i % (D / 4)) * 4;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int w = 0; w < NW; ++w) {
+                const float f = wt[w * GP + g];
+                const float4 v = *reinterpret_cast<const float4*>(osm + (w * GP + g) * D + d);
+                acc.x = fmaf(f, v.x, acc.x);
+                acc.y = fmaf(f, v.y, acc.y);
+                acc.z = fmaf(f, v.z, acc.z);
+                acc.w = fmaf(f, v.w, acc.w);
+            }
+            const float l = mxl[GP + g];
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const int64_t dst = ((int64_t)b * p.Qh + h * p.G + g) * D + d;
+            tq_store_any(p.out, dst + 0, acc.x * inv, p.q_dtype);
+            tq_store_any(p.out, dst + 1, acc.y * inv, p.q_dtype);
+            tq_store_any(p.out, dst + 2, acc.z * inv, p.q_dtype);
+            tq_store_any(p.out, dst + 3, acc.w * inv, p.q_dtype);
+        }
+        TQ_STAMP(6);
+        return;
+    }
     {
         float* mine = partial_ptr<D, GP>(p, b, h, x);
         for (int i = tid; i < GP * (D / 4); i += NT) {
@@ -573,7 +602,7 @@ __global__ void __launch_bounds__(NT, 1) tq_decode_mma_kernel(const DecodeParams
     TQ_STAMP(6);
 }
 
-template <int D, bool SPLITB>
+template <int D, bool SPLITB, int NW>
 size_t mma_smem_bytes(int block_bytes, int nslot) {
     constexpr int GP = SPLITB ? 8 : 4;
     size_t s = (size_t)NW * NSTW * block_bytes;
@@ -583,12 +612,23 @@ size_t mma_smem_bytes(int block_bytes, int nslot) {
     return s;
 }
 
-template <int D, int MSE_BITS, int VAL_BITS, bool SPLITB>
-int launch_mma(const DecodeParams& p, int batch, cudaStream_t st) {
+int sm_count_cached() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, n = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        sms = n;
+    }
+    return sms;
+}
+
+template <int D, int MSE_BITS, int VAL_BITS, bool SPLITB, int NW>
+int launch_mma_nw(const DecodeParams& p, int batch, cudaStream_t st) {
+    constexpr int NT = NW * 32;
     const TqLayout L = tq_make_layout(D, MSE_BITS + 1, VAL_BITS);
     const int nslot = p.num_splits + p.ring_splits;
-    const size_t smem = mma_smem_bytes<D, SPLITB>(L.block_bytes, nslot);
-    auto kern = tq_decode_mma_kernel<D, MSE_BITS, VAL_BITS, SPLITB>;
+    const size_t smem = mma_smem_bytes<D, SPLITB, NW>(L.block_bytes, nslot);
+    auto kern = tq_decode_mma_kernel<D, MSE_BITS, VAL_BITS, SPLITB, NW>;
     static size_t smem_set = 0;
     if (smem > smem_set) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
@@ -606,6 +646,15 @@ int launch_mma(const DecodeParams& p, int batch, cudaStream_t st) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, p) == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
+}
+
+template <int D, int MSE_BITS, int VAL_BITS, bool SPLITB>
+int launch_mma(const DecodeParams& p, int batch, cudaStream_t st) {
+    const int64_t ctas = (int64_t)(p.num_splits + p.ring_splits) * p.H * batch;
+    // two 8-warp CTAs per SM need two merge scratch areas in shared memory: only with few slots
+    if (ctas > sm_count_cached() && p.num_splits + p.ring_splits <= 128)
+        return launch_mma_nw<D, MSE_BITS, VAL_BITS, SPLITB, NW_MULTI>(p, batch, st);
+    return launch_mma_nw<D, MSE_BITS, VAL_BITS, SPLITB, NW_WAVE>(p, batch, st);
 }
 
 }  // namespace
