@@ -70,6 +70,11 @@ __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ 
     const int lane = threadIdx.x & 31, ks = threadIdx.x >> 5;
     const int col = chunk * 32 + lane;
     const float* __restrict__ m = which ? s_t : pi_t;
+    // the matrix slice does not depend on the query: request it first, the query arrives meanwhile
+    const int k0 = ks * (D / 8);
+    float mv[D / 8];
+#pragma unroll
+    for (int k = 0; k < D / 8; ++k) mv[k] = __ldg(m + (size_t)(k0 + k) * D + col);
     for (int i = threadIdx.x; i < 4 * D; i += 256) {
         const int v = i / D;
         qsm[i] = v < nv ? tq_load_any(q, (v0 + v) * D + (i % D), dt) : 0.f;
@@ -82,10 +87,6 @@ __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ 
         if (lane == 0) qn2[ks] = s2;
     }
     float a[4] = {0.f, 0.f, 0.f, 0.f};
-    const int k0 = ks * (D / 8);
-    float mv[D / 8];
-#pragma unroll
-    for (int k = 0; k < D / 8; ++k) mv[k] = __ldg(m + (size_t)(k0 + k) * D + col);
 #pragma unroll
     for (int k = 0; k < D / 8; ++k) {
 #pragma unroll
@@ -521,6 +522,7 @@ extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_
     p.block_table = a->block_table;
     p.bt_stride = a->block_table_stride;
     p.seq_lens = a->seq_lens;
+    p.max_seq_len = a->max_seq_len;
     p.min_history = a->min_history;
     p.qprep = qprep;
     p.qfrag = qfrag;
@@ -544,6 +546,8 @@ extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_
     p.status = (int32_t*)ws;
     p.num_splits = splits;
     p.ring_splits = rsplits;
+    p.land_bytes = 0;
+    p.frags_ready = a->query_prepared ? 1 : 0;
 
     const int mse_bits = consts->cfg.key_bits - 1, vb = consts->cfg.value_bits;
     if (a->kernel != 1) {   // tensor-core kernel where it applies

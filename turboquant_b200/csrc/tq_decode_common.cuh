@@ -12,6 +12,25 @@ constexpr int TILE_TOK = TILE_BLOCKS * TQ_BLOCK_TOKENS;  // 64
 constexpr int NSTAGE = 3;
 constexpr int RING_TOK = 32;  // ring tokens per ring CTA
 
+#ifdef TQ_TRACE
+// Debug build only: per-CTA phase time stamps (ns) for latency analysis.
+static __device__ unsigned long long g_tq_trace[4096 * 16];
+__device__ __forceinline__ unsigned long long tq_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define TQ_STAMP(i)                                                                                       \
+    do {                                                                                                  \
+        if (threadIdx.x == 0) {                                                                           \
+            const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);               \
+            if (cta < 4096) g_tq_trace[cta * 16 + (i)] = tq_now();                                         \
+        }                                                                                                 \
+    } while (0)
+#else
+#define TQ_STAMP(i)
+#endif
+
 struct DecodeParams {
     const uint8_t* pool;
     int64_t num_blocks;
@@ -19,6 +38,7 @@ struct DecodeParams {
     const int32_t* block_table;
     int bt_stride;
     const int32_t* seq_lens;
+    int max_seq_len;     // host upper bound of seq_lens
     int min_history;
     const float* qprep;  // [B][Qh][2][D] rotated / sketched query
     const uint32_t* qfrag;   // per (sequence, kv head): the same query as fp16 MMA fragments (see QF_*)
@@ -36,6 +56,8 @@ struct DecodeParams {
     int32_t* tickets;
     int32_t* status;
     int num_splits, ring_splits;
+    int frags_ready;       // the query fragments were written before this launch was enqueued (no query-prep grid ahead)
+    uint32_t land_bytes;   // tensor-core kernel: shared memory in front of its barriers, reusable by the merge
 };
 
 // ---- operand geometry of the tensor-core kernel, shared with the query preparation ----
@@ -165,14 +187,21 @@ __device__ __forceinline__ void write_partial_regs(const DecodeParams& p, int b,
 // (sequence, kv head) merges all partials and writes the output.  Nobody waits.
 // Every partial is always fully written with finite numbers, so the merge is
 // branch free: a float4 of one head per thread, slots unrolled.
+//
+// `land` / `land_bytes`: shared memory the CTA no longer needs.  When all the
+// partials of the pair fit there, the last CTA fetches them with bulk copies
+// (one trip to L2 instead of a chain of dependent loads) and merges out of
+// shared memory; otherwise it reads them from global memory.
 template <int D, int GP>
 __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, int h,
-                                                 float* wsm /* [max(nslot,128)*GP + 2*GP] */) {
+                                                 float* wsm /* [max(nslot,128)*GP + 2*GP] */,
+                                                 uint8_t* land = nullptr, uint32_t land_bytes = 0) {
     constexpr int PS = GP * (D + 2);
     const int tid = threadIdx.x, nt = blockDim.x;
     const int nslot = p.num_splits + p.ring_splits;
     __threadfence();
     __shared__ int s_last;
+    __shared__ __align__(8) uint64_t s_bar;
     __syncthreads();
     if (tid == 0) {
         const int t = atomicAdd(p.tickets + b * p.H + h, 1);
@@ -181,19 +210,40 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
     __syncthreads();
     if (!s_last) return;
     __threadfence();
+    TQ_STAMP(7);
 
     const float* base = p.partials + (int64_t)(b * p.H + h) * nslot * PS;
+    const uint32_t total = (uint32_t)nslot * PS * 4u;
+    const bool staged = land != nullptr && total <= land_bytes && total < (1u << 20);
+    if (staged) {
+        if (tid == 0) {
+            tq_mbar_init(&s_bar, 1);
+            tq_mbar_fence_init();
+            asm volatile("fence.proxy.async;" ::: "memory");   // other CTAs' generic writes -> this bulk read
+            tq_mbar_expect_tx(&s_bar, total);
+            for (uint32_t off = 0; off < total; off += 32768u)
+                tq_bulk_g2s(land + off, reinterpret_cast<const uint8_t*>(base) + off, min(32768u, total - off), &s_bar);
+        }
+        __syncthreads();
+        bool ok = tq_mbar_wait_bounded(&s_bar, 0u);
+        if (!__syncthreads_and(ok)) {   // never arrived: report; the kernel must not touch `land` again
+            if (tid == 0) atomicCAS(p.status, 0, (int)TQ_ERR_TIMEOUT);
+            return;
+        }
+        base = reinterpret_cast<const float*>(land);
+    }
+
     float* wL = wsm;             // [GP] global sum
     float* w = wsm + 2 * GP;     // [nslot][GP] weight of each partial
     const int warp = tid >> 5, lane = tid & 31;
     for (int g = warp; g < GP; g += nt / 32) {
         float mx = -INFINITY;
-        for (int s = lane; s < nslot; s += 32) mx = fmaxf(mx, __ldcg(base + (int64_t)s * PS + g));
+        for (int s = lane; s < nslot; s += 32) mx = fmaxf(mx, staged ? base[s * PS + g] : __ldcg(base + (int64_t)s * PS + g));
         mx = tq_warp_max(mx);
         float sum = 0.f;
         for (int s = lane; s < nslot; s += 32) {
-            const float ms = __ldcg(base + (int64_t)s * PS + g);
-            const float ls = __ldcg(base + (int64_t)s * PS + GP + g);
+            const float ms = staged ? base[s * PS + g] : __ldcg(base + (int64_t)s * PS + g);
+            const float ls = staged ? base[s * PS + GP + g] : __ldcg(base + (int64_t)s * PS + GP + g);
             const float ws = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
             w[s * GP + g] = ws;
             sum += ws * ls;
@@ -207,6 +257,17 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
         const float4* src = reinterpret_cast<const float4*>(base + 2 * GP + g * D + d);   // PS*4 and (2GP+gD+d)*4 are multiples of 16
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
         int s = 0;
+        if (staged) {
+#pragma unroll 4
+            for (; s < nslot; ++s) {
+                const float4 v = src[s * (PS / 4)];
+                const float ws = w[s * GP + g];
+                o.x = fmaf(ws, v.x, o.x);
+                o.y = fmaf(ws, v.y, o.y);
+                o.z = fmaf(ws, v.z, o.z);
+                o.w = fmaf(ws, v.w, o.w);
+            }
+        }
         for (; s + 8 <= nslot; s += 8) {
             float4 v[8];
 #pragma unroll

@@ -39,24 +39,6 @@ constexpr int NW_WAVE = 12;
 constexpr int NW_MULTI = 8;
 constexpr int BT_MAX = 1024;   // block-table entries a CTA keeps in shared memory
 
-#ifdef TQ_TRACE
-// Debug build only: per-CTA phase time stamps (ns) for latency analysis.
-__device__ unsigned long long g_tq_trace[4096 * 8];
-__device__ __forceinline__ unsigned long long tq_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define TQ_STAMP(i)                                                                                       \
-    do {                                                                                                  \
-        if (threadIdx.x == 0) {                                                                           \
-            const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);               \
-            if (cta < 4096) g_tq_trace[cta * 8 + (i)] = tq_now();                                         \
-        }                                                                                                 \
-    } while (0)
-#else
-#define TQ_STAMP(i)
-#endif
 
 __device__ __forceinline__ float pow2i(int e) { return __int_as_float((127 + e) << 23); }   // 2^e, -126 <= e <= 127
 
@@ -66,6 +48,14 @@ __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1
         "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// Same with a zero accumulator coming in (the first k-step of a record: no register clearing).
+__device__ __forceinline__ void mma16816_z(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                           uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
     uint32_t y;
@@ -99,11 +89,14 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
     const int BB = L.block_bytes;
 
     extern __shared__ __align__(128) uint8_t smem[];
+    // [0, land_bytes): stages, ml, bt_s (+ padding) - all dead once the CTA's partial is written, so the
+    // merge may land every partial of the pair there
     uint8_t* stages = smem;                                              // [NW warps][NSTW][BB]; reused after the loop
     float* ml = reinterpret_cast<float*>(smem + NW * NSTW * BB);         // [NW warps][2][GP]
     int* bt_s = reinterpret_cast<int*>(ml + 2 * NW * GP);                // [BT_MAX] physical blocks of this CTA
-    uint64_t* bars = reinterpret_cast<uint64_t*>(bt_s + BT_MAX);         // [NW][NSTW]
-    float* wsm = reinterpret_cast<float*>(bars + NW * NSTW);             // merge scratch
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + p.land_bytes);   // [NW][NSTW] + 1 for the query fragments
+    uint32_t* qf_s = reinterpret_cast<uint32_t*>(bars + NW * NSTW + 2);  // query fragments of this (sequence, kv head)
+    float* wsm = reinterpret_cast<float*>(qf_s + qf_words(D, SPLITB ? 8 : 4));   // merge scratch
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tig = lane & 3;
@@ -119,17 +112,28 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
         ring_part<D, GP>(p, b, h, x, scratch, scratch + D * GP, scratch + D * GP + GP * RING_TOK, ml, kst,
                          kst + RING_TOK * D * 4);
         TQ_STAMP(5);
-        ticket_and_merge<D, GP>(p, b, h, wsm);
+        ticket_and_merge<D, GP>(p, b, h, wsm, smem, p.land_bytes);
         TQ_STAMP(6);
         return;
     }
 
     // ------------------------------ this CTA's share of the history ------------------------------
+    // Fragments that exist already are fetched ahead of everything else: behind the first burst of
+    // record copies they would arrive last and hold up every warp.
+    constexpr uint32_t QF_BYTES = qf_words(D, SPLITB ? 8 : 4) * 4u;
+    if (p.frags_ready && tid == 0) {
+        tq_mbar_init(bars + NW * NSTW, 1);
+        tq_mbar_fence_init();
+        tq_mbar_expect_tx(bars + NW * NSTW, QF_BYTES);
+        tq_bulk_g2s(qf_s, p.qfrag + (int64_t)(b * p.H + h) * qf_words(D, SPLITB ? 8 : 4), QF_BYTES, bars + NW * NSTW);
+    }
     int n = p.seq_lens[b];
     if (n < p.min_history) n = 0;
-    const int nblk = (n + TQ_BLOCK_TOKENS - 1) / TQ_BLOCK_TOKENS;
-    const int blk0 = (int)((int64_t)x * nblk / p.num_splits);
-    const int blk1 = (int)((int64_t)(x + 1) * nblk / p.num_splits);
+    TQ_STAMP(8);
+    const uint32_t nblk = (uint32_t)(n + TQ_BLOCK_TOKENS - 1) / TQ_BLOCK_TOKENS;
+    // 32-bit arithmetic: the launcher keeps num_splits * nblk below 2^31
+    const int blk0 = (int)((uint32_t)x * nblk / (uint32_t)p.num_splits);
+    const int blk1 = (int)((uint32_t)(x + 1) * nblk / (uint32_t)p.num_splits);
     const int nmine = min(blk1 - blk0, BT_MAX);   // the launcher guarantees <= BT_MAX blocks per split
     const int cnt = nmine > warp ? (nmine - warp + NW - 1) / NW : 0;   // records of this warp
 
@@ -143,19 +147,28 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
         }
         bt_s[i] = phys;
     }
-    if (tid == 0) {
-        for (int s = 0; s < NW * NSTW; ++s) tq_mbar_init(bars + s, 1);
+    TQ_STAMP(9);
+    if (tid < NW * NSTW + (p.frags_ready ? 0 : 1)) {   // one barrier per thread
+        tq_mbar_init(bars + tid, 1);
         tq_mbar_fence_init();
     }
     __syncthreads();
+    TQ_STAMP(10);
     uint8_t* my_stage = stages + warp * NSTW * BB;
     uint64_t* my_bar = bars + warp * NSTW;
-    if (lane == 0) {
-        for (int i = 0; i < NSTW && i < cnt; ++i) {
-            tq_mbar_expect_tx(my_bar + i, (uint32_t)BB);
-            tq_bulk_g2s(my_stage + i * BB, p.pool + ((int64_t)bt_s[warp + NW * i] * p.H + h) * BB, (uint32_t)BB,
-                        my_bar + i);
-        }
+    // The fragments of a query-prep grid still running ahead of this launch: thread 0 waits for that
+    // grid and asks for them before its own warp's records, so that they queue behind as few record
+    // copies as possible; the other warps start their copies at once.
+    if (!p.frags_ready && tid == 0) {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        tq_mbar_expect_tx(bars + NW * NSTW, QF_BYTES);
+        tq_bulk_g2s(qf_s, p.qfrag + (int64_t)(b * p.H + h) * qf_words(D, SPLITB ? 8 : 4), QF_BYTES, bars + NW * NSTW);
+    }
+    __syncwarp();
+    if (lane < NSTW && lane < cnt) {   // one stage per lane
+        tq_mbar_expect_tx(my_bar + lane, (uint32_t)BB);
+        tq_bulk_g2s(my_stage + lane * BB, p.pool + ((int64_t)bt_s[warp + NW * lane] * p.H + h) * BB, (uint32_t)BB,
+                    my_bar + lane);
     }
 
     // ---- query fragments, prepared once per (sequence, kv head) by the query-prep kernel ----
@@ -163,51 +176,57 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
     TQ_STAMP(1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
     TQ_STAMP(2);
+    bool failed = !__all_sync(0xffffffffu, tq_mbar_wait_bounded(bars + NW * NSTW, 0u));   // then no record is processed
+    TQ_STAMP(12);
     uint32_t bq[2 * KS];
     uint32_t bsk[SPLITB ? 2 * KS : 1];
     float k0[2], k1[2], kb0[2], ksg[2], kq[2];
     {
-        const uint32_t* qf = p.qfrag + (int64_t)(b * p.H + h) * qf_words(D, SPLITB ? 8 : 4);
+        const uint32_t* qf = qf_s;
         const float* hdr = reinterpret_cast<const float*>(qf);
-        const bool is_sk = !SPLITB && gid >= 4;
         const int g_col = SPLITB ? gid : (gid & 3);             // head of this thread's B-fragment column
         const bool col_live = g_col < p.G;
-        const int e_a = (int)hdr[(is_sk ? 8 : 0) + g_col], e_b = (int)hdr[8 + g_col];
 #pragma unroll
         for (int r = 0; r < 2 * KS; ++r) {
             bq[r] = col_live ? qf[QF_HDR + r * 32 + lane] : 0u;
             if (SPLITB) bsk[r] = col_live ? qf[QF_HDR + (2 * KS + r) * 32 + lane] : 0u;
         }
-        // sums of the fp16-rounded query over all dims (the constant terms of the bit-plane form)
-        float sum_a = 0.f, sum_b = 0.f;
+        TQ_STAMP(11);
+        // Sums of the fp16-rounded query over all dims (the constant terms of the bit-plane form), taken
+        // with the score MMAs themselves: an A operand with every code (sign) bit set multiplies each
+        // fragment entry by the power of two its position stands for, so the accumulator of column g is
+        // 2^(e-24) * sum_d q[g][d], in the lanes that hold column g's scores later.
+        float one_c[4] = {0.f, 0.f, 0.f, 0.f}, one_s[4] = {0.f, 0.f, 0.f, 0.f};
+        float one_c2[4] = {0.f, 0.f, 0.f, 0.f}, one_s2[4] = {0.f, 0.f, 0.f, 0.f};   // odd k-steps: shorter chains
 #pragma unroll
-        for (int r = 0; r < 2 * KS; ++r) {
-            const int wi = r >> 3, j = r & 7;
-            const float up_code = (float)(1 << (2 * code_pos(j))), up_sign = (float)(1 << sign_pos(sign_bit(wi, j)));
-            const float2 v = __half22float2(*reinterpret_cast<const __half2*>(&bq[r]));
-            if (MSE_BITS == 2) sum_a = fmaf(v.x + v.y, is_sk ? up_sign : up_code, sum_a);
-            if (SPLITB) {
-                const float2 v2 = __half22float2(*reinterpret_cast<const __half2*>(&bsk[r]));
-                sum_b = fmaf(v2.x + v2.y, up_sign, sum_b);
+        for (int s = 0; s < KS; ++s) {
+            const int wi = s >> 2, jj = s & 3;
+            if (MSE_BITS == 2) {
+                const uint32_t m0 = 0x00010001u << (2 * code_pos(2 * jj)), m1 = 0x00010001u << (2 * code_pos(2 * jj + 1));
+                mma16816((s & 1) ? one_c2 : one_c, m0, m0, m1, m1, bq[2 * s], bq[2 * s + 1]);
             }
+            const uint32_t n0 = 0x00010001u << sign_pos(sign_bit(wi, 2 * jj));
+            const uint32_t n1 = 0x00010001u << sign_pos(sign_bit(wi, 2 * jj + 1));
+            mma16816((s & 1) ? one_s2 : one_s, n0, n0, n1, n1, SPLITB ? bsk[SPLITB ? 2 * s : 0] : bq[2 * s],
+                     SPLITB ? bsk[SPLITB ? 2 * s + 1 : 0] : bq[2 * s + 1]);
         }
-        sum_a *= pow2i(-e_a);
-        sum_b *= pow2i(-e_b);
-        sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 1);
-        sum_a += __shfl_xor_sync(0xffffffffu, sum_a, 2);
-        sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 1);
-        sum_b += __shfl_xor_sync(0xffffffffu, sum_b, 2);
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            one_c[c] += one_c2[c];
+            one_s[c] += one_s2[c];
+        }
+        if (!SPLITB) {   // sketched-query columns 4..7 live two lanes to the right
+            one_s[0] = __shfl_xor_sync(0xffffffffu, one_s[0], 2);
+            one_s[1] = __shfl_xor_sync(0xffffffffu, one_s[1], 2);
+        }
         // constants of this thread's two score columns g = 2*tig, 2*tig+1:
         // logit*log2e*scale = nk * (k0 + k1*acc1 + kb0*acc0) + rk * (ks*accs - kq)
         const float c0 = p.cb.centroids[0], c1 = p.cb.centroids[1], c2 = p.cb.centroids[2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const int g = (2 * tig + i) & (GP - 1);
-            // column g's sums sit in the lanes with gid == g (rotated) and, merged layout, gid == g + 4 (sketched)
-            const float s_rot = __shfl_sync(0xffffffffu, sum_a, g * 4);
-            const float s_sk = SPLITB ? __shfl_sync(0xffffffffu, sum_b, g * 4)
-                                      : __shfl_sync(0xffffffffu, sum_a, ((g + 4) & 7) * 4);
             const int e_rot = (int)hdr[g], e_sk = (int)hdr[8 + g];
+            const float s_rot = one_c[i] * pow2i(24 - e_rot), s_sk = one_s[i] * pow2i(24 - e_sk);
             if (MSE_BITS == 2) {
                 k0[i] = c0 * s_rot;
                 k1[i] = (c2 - c0) * pow2i(23 - e_rot);
@@ -247,10 +266,9 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
             t_hi1 |= (c >> 8) << (8 * i);
         }
     }
-    bool failed = false;
     TQ_STAMP(3);
 
-    for (int it = 0; it < cnt; ++it) {
+    for (int it = 0; it < cnt && !failed; ++it) {
         const int st = it % NSTW;
         bool ok = tq_mbar_wait_bounded(my_bar + st, (uint32_t)((it / NSTW) & 1));
         ok = __all_sync(0xffffffffu, ok);
@@ -258,12 +276,23 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
             failed = true;
             break;
         }
-        const uint8_t* rec = my_stage + st * BB;
+        uint8_t* rec = my_stage + st * BB;
         const int blk = blk0 + warp + NW * it;
         const int valid = min(TQ_BLOCK_TOKENS, n - blk * TQ_BLOCK_TOKENS);
+        if (valid < TQ_BLOCK_TOKENS) {
+            // the sequence's last, partly filled record: unused slots may hold anything.  Their scores are
+            // masked below; their value scales and zero points ([grp][16 tok] fp16, contiguous) are cleared
+            // here, so that probability 0 times a stale Inf/NaN cannot reach the value MMAs.
+            __half* sz = reinterpret_cast<__half*>(rec + L.off_vscale);
+            for (int i = lane; i < 2 * NG * TQ_BLOCK_TOKENS; i += 32)
+                if ((i & (TQ_BLOCK_TOKENS - 1)) >= valid) sz[i] = __float2half(0.f);
+            tq_fence_proxy_async();   // generic writes to a stage that a later bulk copy may refill
+            __syncwarp();
+        }
 
         // ------------------------------ scores ------------------------------
-        float acc1[4] = {0.f, 0.f, 0.f, 0.f}, acc0[4] = {0.f, 0.f, 0.f, 0.f}, accs[4] = {0.f, 0.f, 0.f, 0.f};
+        float acc1[4], acc0[4], accs[4];   // written by the first k-step's MMAs
+        if (MSE_BITS == 3) acc1[0] = acc1[1] = acc1[2] = acc1[3] = 0.f;
         if (MSE_BITS == 2) {
             const uint32_t* cwA = reinterpret_cast<const uint32_t*>(rec + L.off_kcodes + tokA * L.kcode_row) + tig * NWK;
             const uint32_t* cwB = reinterpret_cast<const uint32_t*>(rec + L.off_kcodes + tokB * L.kcode_row) + tig * NWK;
@@ -298,14 +327,23 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
                     const uint32_t m0 = 0x00010001u << (2 * code_pos(j0)), m1 = 0x00010001u << (2 * code_pos(j1));
                     const uint32_t xa0 = j0 <= 4 ? a_lo : a_hi, xb0 = j0 <= 4 ? b_lo : b_hi;
                     const uint32_t xa1 = j1 <= 4 ? a_lo : a_hi, xb1 = j1 <= 4 ? b_lo : b_hi;
-                    mma16816(acc0, xa0 & m0, xb0 & m0, xa1 & m1, xb1 & m1, bq[2 * s], bq[2 * s + 1]);
-                    mma16816(acc1, xa0 & (m0 << 1), xb0 & (m0 << 1), xa1 & (m1 << 1), xb1 & (m1 << 1), bq[2 * s],
-                             bq[2 * s + 1]);
+                    if (s == 0) {
+                        mma16816_z(acc0, xa0 & m0, xb0 & m0, xa1 & m1, xb1 & m1, bq[2 * s], bq[2 * s + 1]);
+                        mma16816_z(acc1, xa0 & (m0 << 1), xb0 & (m0 << 1), xa1 & (m1 << 1), xb1 & (m1 << 1), bq[2 * s],
+                                   bq[2 * s + 1]);
+                    } else {
+                        mma16816(acc0, xa0 & m0, xb0 & m0, xa1 & m1, xb1 & m1, bq[2 * s], bq[2 * s + 1]);
+                        mma16816(acc1, xa0 & (m0 << 1), xb0 & (m0 << 1), xa1 & (m1 << 1), xb1 & (m1 << 1), bq[2 * s],
+                                 bq[2 * s + 1]);
+                    }
                     const int sb0 = sign_bit(wi, j0), sb1 = sign_bit(wi, j1);
                     const uint32_t n0 = 0x00010001u << sign_pos(sb0), n1 = 0x00010001u << sign_pos(sb1);
                     const uint32_t ya0 = sb0 <= 9 ? sa_lo : sa_hi, yb0 = sb0 <= 9 ? sb_lo : sb_hi;
                     const uint32_t ya1 = sb1 <= 9 ? sa_lo : sa_hi, yb1 = sb1 <= 9 ? sb_lo : sb_hi;
-                    if (SPLITB)
+                    if (s == 0)
+                        mma16816_z(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, SPLITB ? bsk[0] : bq[0],
+                                   SPLITB ? bsk[1] : bq[1]);
+                    else if (SPLITB)
                         mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, bsk[2 * s], bsk[2 * s + 1]);
                     else
                         mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, bq[2 * s], bq[2 * s + 1]);
@@ -332,8 +370,12 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
                         const uint32_t sa = hf ? wa[wi] >> 16 : wa[wi], sb = hf ? wb[wi] >> 16 : wb[wi];
                         const uint32_t la = __byte_perm(t_lo0, t_lo1, sa), ha = __byte_perm(t_hi0, t_hi1, sa);
                         const uint32_t lb = __byte_perm(t_lo0, t_lo1, sb), hb = __byte_perm(t_hi0, t_hi1, sb);
-                        mma16816(acc0, __byte_perm(la, ha, 0x5140), __byte_perm(lb, hb, 0x5140),
-                                 __byte_perm(la, ha, 0x7362), __byte_perm(lb, hb, 0x7362), bq[2 * s], bq[2 * s + 1]);
+                        if (s == 0)
+                            mma16816_z(acc0, __byte_perm(la, ha, 0x5140), __byte_perm(lb, hb, 0x5140),
+                                       __byte_perm(la, ha, 0x7362), __byte_perm(lb, hb, 0x7362), bq[0], bq[1]);
+                        else
+                            mma16816(acc0, __byte_perm(la, ha, 0x5140), __byte_perm(lb, hb, 0x5140),
+                                     __byte_perm(la, ha, 0x7362), __byte_perm(lb, hb, 0x7362), bq[2 * s], bq[2 * s + 1]);
                     }
                 }
             }
@@ -350,8 +392,11 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
                         const uint32_t n0 = 0x00010001u << sign_pos(sb0), n1 = 0x00010001u << sign_pos(sb1);
                         const uint32_t ya0 = sb0 <= 9 ? sa_lo : sa_hi, yb0 = sb0 <= 9 ? sb_lo : sb_hi;
                         const uint32_t ya1 = sb1 <= 9 ? sa_lo : sa_hi, yb1 = sb1 <= 9 ? sb_lo : sb_hi;
-                        mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, bsk[SPLITB ? 2 * s : 0],
-                                 bsk[SPLITB ? 2 * s + 1 : 0]);
+                        if (s == 0)
+                            mma16816_z(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, bsk[0], bsk[SPLITB ? 1 : 0]);
+                        else
+                            mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, bsk[SPLITB ? 2 * s : 0],
+                                     bsk[SPLITB ? 2 * s + 1 : 0]);
                     }
                 }
             }
@@ -373,8 +418,10 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
         for (int i = 0; i < 2; ++i) {
             sA[i] = nA * (k0[i] + k1[i] * acc1[i] + kb0[i] * acc0[i]) + rA * (ksg[i] * accs[i] - kq[i]);
             sB[i] = nB * (k0[i] + k1[i] * acc1[2 + i] + kb0[i] * acc0[2 + i]) + rB * (ksg[i] * accs[2 + i] - kq[i]);
-            if (tokA >= valid) sA[i] = -INFINITY;
-            if (tokB >= valid) sB[i] = -INFINITY;
+            if (valid < TQ_BLOCK_TOKENS) {   // warp-uniform: only the sequence's last record
+                if (tokA >= valid) sA[i] = -INFINITY;
+                if (tokB >= valid) sB[i] = -INFINITY;
+            }
             float mx = fmaxf(sA[i], sB[i]);
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 4));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 8));
@@ -408,18 +455,13 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
         // ------------------------------ values ------------------------------
         {
             // tokens of this thread's contraction slots: 4*tig .. 4*tig+3
-            uint32_t keep01 = 0xffffffffu, keep23 = 0xffffffffu;
-            if (valid < TQ_BLOCK_TOKENS) {   // never let stale bytes of unused slots in
-                keep01 = (4 * tig < valid ? 0x0000ffffu : 0u) | (4 * tig + 1 < valid ? 0xffff0000u : 0u);
-                keep23 = (4 * tig + 2 < valid ? 0x0000ffffu : 0u) | (4 * tig + 3 < valid ? 0xffff0000u : 0u);
-            }
             const uint2* vsc = reinterpret_cast<const uint2*>(rec + L.off_vscale) + tig;   // [grp][16 tok] fp16: 4 uint2 per group
             const uint2* vzr = reinterpret_cast<const uint2*>(rec + L.off_vzero) + tig;
             // zero-point term: rows = groups
             {
                 uint2 z = make_uint2(0u, 0u);
                 if (gid < NG) z = vzr[gid * 4];
-                mma16816(zacc, z.x & keep01, 0u, z.y & keep23, 0u, t0, t1);
+                mma16816(zacc, z.x, 0u, z.y, 0u, t0, t1);
             }
             const uint4* vcw = reinterpret_cast<const uint4*>(rec + L.off_vcodes) + lane;   // [chunk][lane] 16 B
             if (VAL_BITS == 2) {
@@ -442,7 +484,7 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
                     for (int odd = 0; odd < 2; ++odd) {
                         const int grp = 2 * gp + odd;
                         const uint2 sc = vsc[grp * 4];
-                        const uint32_t bp0 = hmul2_sat(t0, sc.x & keep01), bp1 = hmul2_sat(t1, sc.y & keep23);
+                        const uint32_t bp0 = hmul2_sat(t0, sc.x), bp1 = hmul2_sat(t1, sc.y);
 #pragma unroll
                         for (int hb = 0; hb < 2; ++hb) {   // the two M-blocks of the group
                             const int i_lo = 2 * hb, i_hi = i_lo + 1;
@@ -469,7 +511,7 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
                     const uint32_t w0 = w[grp], w1 = w[NG + grp];
                     const uint32_t w0h = w0 >> 8, w1h = w1 >> 8;
                     const uint2 sc = vsc[grp * 4];
-                    const uint32_t bp0 = hmul2_sat(t0, sc.x & keep01), bp1 = hmul2_sat(t1, sc.y & keep23);
+                    const uint32_t bp0 = hmul2_sat(t0, sc.x), bp1 = hmul2_sat(t1, sc.y);
                     mma16816(o[2 * grp], w0 & 0x000f000fu, w0 & 0x00f000f0u, w1 & 0x000f000fu, w1 & 0x00f000f0u, bp0, bp1);
                     mma16816(o[2 * grp + 1], w0h & 0x000f000fu, w0h & 0x00f000f0u, w1h & 0x000f000fu,
                              w1h & 0x00f000f0u, bp0, bp1);
@@ -531,83 +573,72 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
         }
     }
     __syncthreads();
-    // weight of every warp's partial, once per (warp, head)
-    float* wt = wsm;            // [NW][GP]
-    float* mxl = wsm + NW * GP; // [2][GP]: max (log2 domain), sum
-    if (tid < GP) {
-        float mx = -INFINITY;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) mx = fmaxf(mx, ml[(w * 2) * GP + tid]);
-        float lsum = 0.f;
-#pragma unroll
-        for (int w = 0; w < NW; ++w) {
-            const float mw = ml[(w * 2) * GP + tid];
-            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mx);
-            wt[w * GP + tid] = f;
-            lsum = fmaf(f, ml[(w * 2 + 1) * GP + tid], lsum);
-        }
-        mxl[tid] = mx;
-        mxl[GP + tid] = lsum;
-    }
-    __syncthreads();
-    if (p.num_splits + p.ring_splits == 1) {
-        // the only CTA of this (sequence, kv head): normalise and write the output, no global round trip
-        for (int i = tid; i < p.G * (D / 4); i += NT) {
-            const int g = i / (D / 4), d = (i % (D / 4)) * 4;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int w = 0; w < NW; ++w) {
-                const float f = wt[w * GP + g];
-                const float4 v = *reinterpret_cast<const float4*>(osm + (w * GP + g) * D + d);
-                acc.x = fmaf(f, v.x, acc.x);
-                acc.y = fmaf(f, v.y, acc.y);
-                acc.z = fmaf(f, v.z, acc.z);
-                acc.w = fmaf(f, v.w, acc.w);
-            }
-            const float l = mxl[GP + g];
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            const int64_t dst = ((int64_t)b * p.Qh + h * p.G + g) * D + d;
-            tq_store_any(p.out, dst + 0, acc.x * inv, p.q_dtype);
-            tq_store_any(p.out, dst + 1, acc.y * inv, p.q_dtype);
-            tq_store_any(p.out, dst + 2, acc.z * inv, p.q_dtype);
-            tq_store_any(p.out, dst + 3, acc.w * inv, p.q_dtype);
-        }
-        TQ_STAMP(6);
-        return;
-    }
+    // Every thread owns four channels of one head: it weighs the warps' partials itself (NW exp2f)
+    // instead of waiting for a serial pass over the heads.
     {
+        const bool single = p.num_splits + p.ring_splits == 1;   // then this CTA writes the output itself
         float* mine = partial_ptr<D, GP>(p, b, h, x);
         for (int i = tid; i < GP * (D / 4); i += NT) {
             const int g = i / (D / 4), d = (i % (D / 4)) * 4;
+            float mx = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) mx = fmaxf(mx, ml[(w * 2) * GP + g]);
+            float lsum = 0.f;
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
             for (int w = 0; w < NW; ++w) {
-                const float f = wt[w * GP + g];
+                const float mw = ml[(w * 2) * GP + g];
+                const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mx);
+                lsum = fmaf(f, ml[(w * 2 + 1) * GP + g], lsum);
                 const float4 v = *reinterpret_cast<const float4*>(osm + (w * GP + g) * D + d);
                 acc.x = fmaf(f, v.x, acc.x);
                 acc.y = fmaf(f, v.y, acc.y);
                 acc.z = fmaf(f, v.z, acc.z);
                 acc.w = fmaf(f, v.w, acc.w);
             }
-            *reinterpret_cast<float4*>(mine + 2 * GP + g * D + d) = acc;
+            if (single) {
+                if (g < p.G) {
+                    const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+                    const int64_t dst = ((int64_t)b * p.Qh + h * p.G + g) * D + d;
+                    tq_store_any(p.out, dst + 0, acc.x * inv, p.q_dtype);
+                    tq_store_any(p.out, dst + 1, acc.y * inv, p.q_dtype);
+                    tq_store_any(p.out, dst + 2, acc.z * inv, p.q_dtype);
+                    tq_store_any(p.out, dst + 3, acc.w * inv, p.q_dtype);
+                }
+            } else {
+                *reinterpret_cast<float4*>(mine + 2 * GP + g * D + d) = acc;
+                if (d == 0) {
+                    mine[g] = mx * 0.6931471805599453f;   // back to the natural-log domain of the merge
+                    mine[GP + g] = lsum;
+                }
+            }
         }
-        if (tid < GP) {
-            mine[tid] = mxl[tid] * 0.6931471805599453f;   // back to the natural-log domain of the merge
-            mine[GP + tid] = mxl[GP + tid];
+        if (single) {
+            TQ_STAMP(6);
+            return;
         }
     }
     __syncthreads();   // wsm is reused by the merge
     TQ_STAMP(5);
-    ticket_and_merge<D, GP>(p, b, h, wsm);
+    ticket_and_merge<D, GP>(p, b, h, wsm, smem, p.land_bytes);
     TQ_STAMP(6);
 }
 
+// Bytes in front of the barriers: stages, ml, bt_s, grown (one CTA per SM only) until the merge
+// can land all `nslot` partials of a (sequence, kv head) there.
+template <int D, bool SPLITB, int NW>
+size_t mma_land_bytes(int block_bytes, int nslot) {
+    constexpr int GP = SPLITB ? 8 : 4;
+    size_t s = (size_t)NW * NSTW * block_bytes + sizeof(float) * (2 * NW * GP) + sizeof(int) * BT_MAX;
+    const size_t want = (size_t)nslot * GP * (D + 2) * sizeof(float);
+    if (NW == NW_WAVE && want > s && want <= 200 * 1024) s = want;
+    return (s + 127) / 128 * 128;
+}
 template <int D, bool SPLITB, int NW>
 size_t mma_smem_bytes(int block_bytes, int nslot) {
     constexpr int GP = SPLITB ? 8 : 4;
-    size_t s = (size_t)NW * NSTW * block_bytes;
-    s += sizeof(float) * (2 * NW * GP);
-    s += sizeof(int) * BT_MAX + sizeof(uint64_t) * NW * NSTW;
+    size_t s = mma_land_bytes<D, SPLITB, NW>(block_bytes, nslot);
+    s += sizeof(uint64_t) * (NW * NSTW + 2) + sizeof(uint32_t) * qf_words(D, SPLITB ? 8 : 4);
     s += sizeof(float) * ((size_t)(nslot > 128 ? nslot : 128) * GP + 2 * GP);
     return s;
 }
@@ -623,11 +654,13 @@ int sm_count_cached() {
 }
 
 template <int D, int MSE_BITS, int VAL_BITS, bool SPLITB, int NW>
-int launch_mma_nw(const DecodeParams& p, int batch, cudaStream_t st) {
+int launch_mma_nw(const DecodeParams& p_in, int batch, cudaStream_t st) {
+    DecodeParams p = p_in;
     constexpr int NT = NW * 32;
     const TqLayout L = tq_make_layout(D, MSE_BITS + 1, VAL_BITS);
     const int nslot = p.num_splits + p.ring_splits;
     const size_t smem = mma_smem_bytes<D, SPLITB, NW>(L.block_bytes, nslot);
+    p.land_bytes = (uint32_t)mma_land_bytes<D, SPLITB, NW>(L.block_bytes, nslot);
     auto kern = tq_decode_mma_kernel<D, MSE_BITS, VAL_BITS, SPLITB, NW>;
     static size_t smem_set = 0;
     if (smem > smem_set) {
@@ -672,6 +705,7 @@ int tq_decode_mma_launch(const DecodeParams& p, int D, int mse_bits, int val_bit
     *handled = 0;
     const int nblk = (max_seq_len + TQ_BLOCK_TOKENS - 1) / TQ_BLOCK_TOKENS;
     if ((nblk + p.num_splits - 1) / p.num_splits + 1 > BT_MAX) return TQ_OK;   // block-table slice kept in shared memory
+    if ((int64_t)(p.num_splits + 1) * nblk >= (int64_t)1 << 31) return TQ_OK;   // 32-bit split arithmetic in the kernel
     if (mse_bits == 3) {
         if (D != 128) return TQ_OK;                  // two fragment sets of 32 registers do not fit at 256
         *handled = 1;
