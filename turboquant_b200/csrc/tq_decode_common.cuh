@@ -199,17 +199,17 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
     constexpr int PS = GP * (D + 2);
     const int tid = threadIdx.x, nt = blockDim.x;
     const int nslot = p.num_splits + p.ring_splits;
-    __threadfence();
     __shared__ int s_last;
     __shared__ __align__(8) uint64_t s_bar;
-    __syncthreads();
+    __syncthreads();          // every thread's part of the partial is written ...
     if (tid == 0) {
+        __threadfence();      // ... and, the fence being cumulative, visible device-wide before the ticket
         const int t = atomicAdd(p.tickets + b * p.H + h, 1);
         s_last = (t == nslot - 1);
+        if (s_last) __threadfence();
     }
     __syncthreads();
     if (!s_last) return;
-    __threadfence();
     TQ_STAMP(7);
 
     const float* base = p.partials + (int64_t)(b * p.H + h) * nslot * PS;
@@ -230,7 +230,37 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
             if (tid == 0) atomicCAS(p.status, 0, (int)TQ_ERR_TIMEOUT);
             return;
         }
-        base = reinterpret_cast<const float*>(land);
+        TQ_STAMP(13);
+        // Out of shared memory: a thread owns four channels of one head (the head is the same for a whole
+        // warp, so the per-slot max and sum are broadcast reads) and weighs the slots itself.
+        const float* sb = reinterpret_cast<const float*>(land);
+        for (int i = tid; i < p.G * (D / 4); i += nt) {
+            const int g = i / (D / 4), d = (i % (D / 4)) * 4;
+            float mx = -INFINITY;
+            for (int s = 0; s < nslot; ++s) mx = fmaxf(mx, sb[s * PS + g]);
+            const float4* src = reinterpret_cast<const float4*>(sb + 2 * GP + g * D + d);
+            float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+            float l = 0.f;
+#pragma unroll 4
+            for (int s = 0; s < nslot; ++s) {
+                const float ms = sb[s * PS + g];
+                const float ws = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
+                l = fmaf(ws, sb[s * PS + GP + g], l);
+                const float4 v = src[s * (PS / 4)];
+                o.x = fmaf(ws, v.x, o.x);
+                o.y = fmaf(ws, v.y, o.y);
+                o.z = fmaf(ws, v.z, o.z);
+                o.w = fmaf(ws, v.w, o.w);
+            }
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const int64_t dst = ((int64_t)b * p.Qh + h * p.G + g) * D + d;
+            tq_store_any(p.out, dst + 0, o.x * inv, p.q_dtype);
+            tq_store_any(p.out, dst + 1, o.y * inv, p.q_dtype);
+            tq_store_any(p.out, dst + 2, o.z * inv, p.q_dtype);
+            tq_store_any(p.out, dst + 3, o.w * inv, p.q_dtype);
+        }
+        if (tid == 0) p.tickets[b * p.H + h] = 0;  // ready for the next launch
+        return;
     }
 
     float* wL = wsm;             // [GP] global sum
@@ -238,12 +268,12 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
     const int warp = tid >> 5, lane = tid & 31;
     for (int g = warp; g < GP; g += nt / 32) {
         float mx = -INFINITY;
-        for (int s = lane; s < nslot; s += 32) mx = fmaxf(mx, staged ? base[s * PS + g] : __ldcg(base + (int64_t)s * PS + g));
+        for (int s = lane; s < nslot; s += 32) mx = fmaxf(mx, __ldcg(base + (int64_t)s * PS + g));
         mx = tq_warp_max(mx);
         float sum = 0.f;
         for (int s = lane; s < nslot; s += 32) {
-            const float ms = staged ? base[s * PS + g] : __ldcg(base + (int64_t)s * PS + g);
-            const float ls = staged ? base[s * PS + GP + g] : __ldcg(base + (int64_t)s * PS + GP + g);
+            const float ms = __ldcg(base + (int64_t)s * PS + g);
+            const float ls = __ldcg(base + (int64_t)s * PS + GP + g);
             const float ws = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
             w[s * GP + g] = ws;
             sum += ws * ls;
@@ -257,17 +287,6 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
         const float4* src = reinterpret_cast<const float4*>(base + 2 * GP + g * D + d);   // PS*4 and (2GP+gD+d)*4 are multiples of 16
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
         int s = 0;
-        if (staged) {
-#pragma unroll 4
-            for (; s < nslot; ++s) {
-                const float4 v = src[s * (PS / 4)];
-                const float ws = w[s * GP + g];
-                o.x = fmaf(ws, v.x, o.x);
-                o.y = fmaf(ws, v.y, o.y);
-                o.z = fmaf(ws, v.z, o.z);
-                o.w = fmaf(ws, v.w, o.w);
-            }
-        }
         for (; s + 8 <= nslot; s += 8) {
             float4 v[8];
 #pragma unroll

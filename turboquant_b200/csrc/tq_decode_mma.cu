@@ -40,6 +40,12 @@ constexpr int NW_MULTI = 8;
 constexpr int BT_MAX = 1024;   // block-table entries a CTA keeps in shared memory
 
 
+// 2^x for x <= 0 (softmax terms): the bare approximation instruction, results below 2^-126 flush to 0
+__device__ __forceinline__ float ex2_fast(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ float pow2i(int e) { return __int_as_float((127 + e) << 23); }   // 2^e, -126 <= e <= 127
 
 __device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -428,9 +434,9 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
             const float m_new = fmaxf(m_run[i], mx);
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-            alpha[i] = exp2f(m_run[i] - m_use);
-            pA[i] = exp2f(sA[i] - m_use);
-            pB[i] = exp2f(sB[i] - m_use);
+            alpha[i] = ex2_fast(m_run[i] - m_use);
+            pA[i] = ex2_fast(sA[i] - m_use);
+            pB[i] = ex2_fast(sB[i] - m_use);
             l_run[i] = l_run[i] * alpha[i] + pA[i] + pB[i];
             rescale |= (m_new != m_run[i]);
             m_run[i] = m_new;
