@@ -176,7 +176,7 @@ typedef struct tq_decode_args {
     int32_t max_ring_len;       /* host upper bound of ring_lens */
     int64_t ring_stride_seq, ring_stride_token;
     float scale;                /* softmax scale, 1/sqrt(D) by default in the reference */
-    void* out;                  /* (batch, num_q_heads, D) in q_dtype */
+    void* out;                  /* (batch, num_q_heads, D) in q_dtype, 16-byte aligned */
     void* workspace;
     size_t workspace_bytes;
     int32_t num_splits;         /* sequence splits per (sequence, kv head); 0 = choose */
@@ -198,6 +198,21 @@ typedef struct tq_decode_args {
  * compute_hybrid_attention (score.py:29-173) and the fused Triton decode
  * (triton_kernels.py:209-356,505-607). */
 int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* args, void* stream);
+
+/* tq_decode for a caller whose step inputs and result live in HOST memory (pinned for the
+ * copies to be asynchronous): on `stream`, copies `in_bytes` from `host_in` to the device
+ * buffer `dev_in`, runs tq_decode(args), and copies `out_bytes` from args->out to `host_out`.
+ * args->query / append_k / append_v normally point into `dev_in`.  Nothing is synchronised; either
+ * copy is skipped when its host pointer is NULL.  Transfers of at most 64 KiB to or from
+ * page-locked host memory that the GPU can address (cudaHostAlloc / cudaHostRegister; checked
+ * with cudaPointerGetAttributes) do not use the copy engines: a one-CTA kernel pulls the input,
+ * and the decode kernel writes the result into `host_out` itself (args->out is then left
+ * untouched); anything else goes through cudaMemcpyAsync.
+ * Replaces the .to(device) / .cpu() traffic around compute_hybrid_attention in the
+ * reference's hooks (integration/vllm.py:205-222 hands over tensors that are already on the
+ * device; a host-side caller of score.py does these copies itself). */
+int tq_decode_host_io(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* args, const void* host_in,
+                      void* dev_in, size_t in_bytes, void* host_out, size_t out_bytes, void* stream);
 
 /* tq_decode without caller-provided scratch: `workspace` / `workspace_bytes` of
  * the arguments are ignored and a fixed array inside the library, resident on

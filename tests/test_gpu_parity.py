@@ -596,6 +596,16 @@ def test_engine_decode_step_equals_two_calls(dev):
     out_a = a.decode_step(q, k[1:2].to(dev), v[1:2].to(dev), qh)
     b.ingest_decode(k[1:2].to(dev), v[1:2].to(dev), 1)
     assert torch.equal(out_a, compute_hybrid_attention(q, b.store, *b.ring.peek(), qh))
+    # the host-buffer form of the same step
+    hin = torch.cat([k[2:3].reshape(-1), v[2:3].reshape(-1), q.cpu().reshape(-1)]).pin_memory()
+    hout = torch.empty(qh * d, dtype=torch.bfloat16).pin_memory()
+    for rep in range(20):          # crosses a ring overflow
+        a.decode_step_host(hin, hout, qh)
+        torch.cuda.synchronize()
+        b.ingest_decode(k[2:3].to(dev), v[2:3].to(dev), 1)
+        ref = compute_hybrid_attention(q, b.store, *b.ring.peek(), qh)
+        assert torch.equal(hout.view(1, qh, d), ref.cpu()), rep
+    assert (a.total_compressed_tokens, a.total_buffered_tokens) == (b.total_compressed_tokens, b.total_buffered_tokens)
 
 
 def test_vllm_adapter_hybrid_decode(dev):

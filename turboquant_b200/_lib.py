@@ -75,6 +75,8 @@ SIGNATURES = {
                            C.c_void_p]),
     "tq_store_read_status": (C.c_int, [C.POINTER(C.c_int32)]),
     "tq_decode": (C.c_int, [C.POINTER(tq_consts), C.POINTER(tq_pool), C.POINTER(tq_decode_args), C.c_void_p]),
+    "tq_decode_host_io": (C.c_int, [C.POINTER(tq_consts), C.POINTER(tq_pool), C.POINTER(tq_decode_args), C.c_void_p,
+                                    C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p]),
     "tq_decode_static": (C.c_int, [C.POINTER(tq_consts), C.POINTER(tq_pool), C.POINTER(tq_decode_args), C.c_void_p]),
     "tq_decode_static_scratch_bytes": (C.c_size_t, []),
     "tq_scores": (C.c_int, [C.POINTER(tq_consts), C.POINTER(tq_pool), C.c_void_p, C.c_int64, C.c_void_p, C.c_int,

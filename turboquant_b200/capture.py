@@ -6,9 +6,12 @@ from __future__ import annotations
 
 from typing import Optional
 
+import ctypes as C
+
 import torch
 
 from . import _engine as E
+from . import _lib
 from .store import CompressedKVStore
 
 
@@ -111,6 +114,7 @@ class KVCaptureEngine:
         self.store = store
         self.ring = RingBuffer(ring_capacity, store.num_kv_heads, store.head_dim, device or store.device, dtype)
         self._prefill_done = False
+        self._host_io = None      # buffers and the argument block of decode_step_host
 
     @property
     def total_compressed_tokens(self) -> int:
@@ -176,6 +180,56 @@ class KVCaptureEngine:
                        append_k=key.contiguous(), append_v=value.contiguous(), out=out)
         ring.advance_after_device_append()
         return res
+
+    def decode_step_host(self, host_in: torch.Tensor, host_out: torch.Tensor, num_query_heads: int,
+                         scale: Optional[float] = None) -> None:
+        """`decode_step` for a caller whose step data lives in host memory.
+
+        host_in: pinned 1-D tensor in the ring's dtype, key (H*D) | value (H*D) | query (Qh*D) of the
+        new token; host_out: pinned tensor of Qh*D elements that receives the attention output.
+        One library call enqueues the host-to-device copy, the ring append + attention and the
+        device-to-host copy on the current stream; nothing is synchronised (synchronise the stream
+        before reading host_out).  Same results as `decode_step`.
+        """
+        ring, store = self.ring, self.store
+        if ring.is_full:
+            self.store.append_chunk(*ring.drain())
+        h, d, qh = store.num_kv_heads, store.head_dim, num_query_heads
+        nk, nq = h * d, qh * d
+        io = self._host_io
+        if io is None or io["qh"] != qh:
+            if host_in.dtype != ring.dtype or host_out.dtype != ring.dtype:
+                raise TypeError(f"host buffers must be {ring.dtype} like the ring")
+            stage = torch.empty(2 * nk + nq, dtype=ring.dtype, device=store.device)
+            out = torch.empty(1, qh, d, dtype=ring.dtype, device=store.device)
+            rk, rv = ring.storage
+            a = _lib.tq_decode_args()
+            es = stage.element_size()
+            a.append_k, a.append_v = stage.data_ptr(), stage.data_ptr() + nk * es
+            a.query, a.q_dtype, a.batch, a.num_q_heads = stage.data_ptr() + 2 * nk * es, E.dtype_code(ring.dtype), 1, qh
+            a.ring_k, a.ring_v, a.ring_dtype = rk.data_ptr(), rv.data_ptr(), E.dtype_code(ring.dtype)
+            a.ring_stride_seq, a.ring_stride_token, a.ring_capacity = 0, rk.stride(0), ring.capacity
+            a.min_history, a.out = 16, out.data_ptr()
+            a.scale = scale if scale is not None else 1.0 / (d ** 0.5)
+            io = self._host_io = dict(qh=qh, stage=stage, out=out, args=a, in_bytes=(2 * nk + nq) * es,
+                                      out_bytes=nq * es, sms=E.sm_count(store.device))
+        if host_in.numel() != 2 * nk + nq or host_out.numel() != nq or not host_in.is_pinned():
+            raise ValueError("host_in must be a pinned tensor of key | value | query, host_out of Qh*D elements")
+        a = io["args"]
+        n, r = store.num_tokens, ring.size + 1
+        splits = E.choose_splits(1, h, n, io["sms"], r)
+        store.workspace.ensure_decode(store.consts, 1, qh, h, splits)
+        a.block_table, a.block_table_stride = store.block_table.data_ptr(), store.block_table.numel()
+        a.seq_lens, a.max_seq_len = store.seq_len_device.data_ptr(), n
+        a.ring_lens, a.max_ring_len, a.num_splits = ring.device_len().data_ptr(), r, splits
+        a.workspace, a.workspace_bytes = store.workspace.ptr, store.workspace.nbytes
+        if scale is not None:
+            a.scale = scale
+        E.check(E.lib().tq_decode_host_io(C.byref(store.consts.c), C.byref(store.pool.c), C.byref(a),
+                                          host_in.data_ptr(), io["stage"].data_ptr(), io["in_bytes"],
+                                          host_out.data_ptr(), io["out_bytes"], E.stream_ptr(store.device)),
+                "tq_decode_host_io")
+        ring.advance_after_device_append()
 
     def flush(self) -> None:
         data = self.ring.drain()

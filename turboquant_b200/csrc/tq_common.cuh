@@ -122,6 +122,21 @@ __device__ __forceinline__ void tq_store_any(void* p, int64_t i, float x, int dt
     else ((__half*)p)[i] = __float2half_rn(x);
 }
 
+// four consecutive elements starting at an index that is a multiple of 4, one store
+__device__ __forceinline__ void tq_store4_any(void* p, int64_t i, float a, float b, float c, float d, int dt) {
+    if (dt == TQ_F32) {
+        *reinterpret_cast<float4*>((float*)p + i) = make_float4(a, b, c, d);
+    } else if (dt == TQ_BF16) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        *reinterpret_cast<uint2*>((__nv_bfloat16*)p + i) =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    } else {
+        const __half2 lo = __floats2half2_rn(a, b), hi = __floats2half2_rn(c, d);
+        *reinterpret_cast<uint2*>((__half*)p + i) =
+            make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    }
+}
+
 static inline size_t tq_dtype_size(int dt) { return dt == TQ_F32 ? 4 : 2; }
 
 // ---------------------------------------------------------------------------

@@ -462,7 +462,7 @@ extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_
     const bool has_ring = a->ring_k != nullptr && a->max_ring_len > 0;
     if (has_ring && (!a->ring_v || !a->ring_lens)) return TQ_ERR_NULL;
     if (has_ring && a->max_ring_len > 256) return TQ_ERR_UNSUPPORTED;
-    if (((uintptr_t)pool->base & 15) || ((uintptr_t)a->workspace & 255)) return TQ_ERR_ALIGN;
+    if (((uintptr_t)pool->base & 15) || ((uintptr_t)a->workspace & 255) || ((uintptr_t)a->out & 15)) return TQ_ERR_ALIGN;
     cudaStream_t st = (cudaStream_t)stream;
 
     const TqLayout L = tq_make_layout(D, consts->cfg.key_bits, consts->cfg.value_bits);
@@ -648,6 +648,73 @@ void* g_static_scratch_ptr[kMaxDevices];   // device address of the array, per d
 }  // namespace
 
 extern "C" size_t tq_decode_static_scratch_bytes(void) { return (size_t)TQ_STATIC_SCRATCH_BYTES; }
+
+namespace {
+
+// Small step inputs are pulled from mapped host memory by a one-CTA kernel: a copy-engine
+// transfer between two kernels of a stream costs several microseconds of switching.
+__global__ void __launch_bounds__(1024) tq_stage_in_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int n16) {
+    for (int i = threadIdx.x; i < n16; i += 1024) dst[i] = src[i];
+}
+
+constexpr size_t HOST_IO_DIRECT_MAX = 64 * 1024;
+
+// true when the GPU may dereference `ptr` itself: page-locked (pinned or registered) host memory
+// under unified addressing.  The last answers are remembered: step buffers are reused.
+bool host_ptr_is_mapped(const void* ptr, size_t bytes) {
+    static const void* ok_ptr[4] = {nullptr, nullptr, nullptr, nullptr};
+    static size_t ok_bytes[4] = {0, 0, 0, 0};
+    static int next = 0;
+    for (int i = 0; i < 4; ++i)
+        if (ok_ptr[i] == ptr && ok_bytes[i] >= bytes) return true;
+    cudaPointerAttributes at;
+    if (cudaPointerGetAttributes(&at, ptr) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+    }
+    if (at.type != cudaMemoryTypeHost || at.devicePointer != ptr) return false;
+    cudaPointerAttributes at2;   // the end of the range must belong to the same registration
+    if (cudaPointerGetAttributes(&at2, (const char*)ptr + bytes - 1) != cudaSuccess || at2.type != cudaMemoryTypeHost) {
+        cudaGetLastError();
+        return false;
+    }
+    ok_ptr[next] = ptr;
+    ok_bytes[next] = bytes;
+    next = (next + 1) & 3;
+    return true;
+}
+
+}  // namespace
+
+extern "C" int tq_decode_host_io(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* a,
+                                 const void* host_in, void* dev_in, size_t in_bytes, void* host_out, size_t out_bytes,
+                                 void* stream) {
+    if (!a) return TQ_ERR_NULL;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (host_in != nullptr && in_bytes > 0) {
+        if (!dev_in) return TQ_ERR_NULL;
+        const bool direct = in_bytes <= HOST_IO_DIRECT_MAX && (in_bytes & 15) == 0 &&
+                            (((uintptr_t)host_in | (uintptr_t)dev_in) & 15) == 0 && host_ptr_is_mapped(host_in, in_bytes);
+        if (direct) {
+            tq_stage_in_kernel<<<1, 1024, 0, st>>>((const uint4*)host_in, (uint4*)dev_in, (int)(in_bytes / 16));
+            if (cudaGetLastError() != cudaSuccess) return TQ_ERR_CUDA;
+        } else if (cudaMemcpyAsync(dev_in, host_in, in_bytes, cudaMemcpyHostToDevice, st) != cudaSuccess) {
+            return TQ_ERR_CUDA;
+        }
+    }
+    tq_decode_args b = *a;
+    // a small result is written to mapped host memory by the merge itself
+    const bool out_direct = host_out != nullptr && out_bytes > 0 && out_bytes <= HOST_IO_DIRECT_MAX &&
+                            ((uintptr_t)host_out & 15) == 0 && host_ptr_is_mapped(host_out, out_bytes);
+    if (out_direct) b.out = host_out;
+    const int rc = tq_decode(consts, pool, &b, stream);
+    if (rc != TQ_OK) return rc;
+    if (host_out != nullptr && out_bytes > 0 && !out_direct) {
+        if (cudaMemcpyAsync(host_out, a->out, out_bytes, cudaMemcpyDeviceToHost, st) != cudaSuccess) return TQ_ERR_CUDA;
+    }
+    return TQ_OK;
+}
+
 
 extern "C" int tq_decode_static(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* a, void* stream) {
     if (!consts || !pool || !a) return TQ_ERR_NULL;

@@ -254,10 +254,7 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
             }
             const float inv = l > 0.f ? 1.f / l : 0.f;
             const int64_t dst = ((int64_t)b * p.Qh + h * p.G + g) * D + d;
-            tq_store_any(p.out, dst + 0, o.x * inv, p.q_dtype);
-            tq_store_any(p.out, dst + 1, o.y * inv, p.q_dtype);
-            tq_store_any(p.out, dst + 2, o.z * inv, p.q_dtype);
-            tq_store_any(p.out, dst + 3, o.w * inv, p.q_dtype);
+            tq_store4_any(p.out, dst, o.x * inv, o.y * inv, o.z * inv, o.w * inv, p.q_dtype);
         }
         if (tid == 0) p.tickets[b * p.H + h] = 0;  // ready for the next launch
         return;
@@ -311,10 +308,7 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
         const float l = wL[g];
         const float inv = l > 0.f ? 1.f / l : 0.f;
         const int64_t dst = ((int64_t)b * p.Qh + h * p.G + g) * D + d;
-        tq_store_any(p.out, dst + 0, o.x * inv, p.q_dtype);
-        tq_store_any(p.out, dst + 1, o.y * inv, p.q_dtype);
-        tq_store_any(p.out, dst + 2, o.z * inv, p.q_dtype);
-        tq_store_any(p.out, dst + 3, o.w * inv, p.q_dtype);
+        tq_store4_any(p.out, dst, o.x * inv, o.y * inv, o.z * inv, o.w * inv, p.q_dtype);
     }
     if (tid == 0) p.tickets[b * p.H + h] = 0;  // ready for the next launch
 }

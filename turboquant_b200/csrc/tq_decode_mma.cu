@@ -606,10 +606,7 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
                 if (g < p.G) {
                     const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
                     const int64_t dst = ((int64_t)b * p.Qh + h * p.G + g) * D + d;
-                    tq_store_any(p.out, dst + 0, acc.x * inv, p.q_dtype);
-                    tq_store_any(p.out, dst + 1, acc.y * inv, p.q_dtype);
-                    tq_store_any(p.out, dst + 2, acc.z * inv, p.q_dtype);
-                    tq_store_any(p.out, dst + 3, acc.w * inv, p.q_dtype);
+                    tq_store4_any(p.out, dst, acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv, p.q_dtype);
                 }
             } else {
                 *reinterpret_cast<float4*>(mine + 2 * GP + g * D + d) = acc;
