@@ -34,6 +34,7 @@ struct RingAppend {
     int32_t* ring_lens;    // position of the new token; incremented
     int elem_bytes, B, H, capacity;
     int64_t stride_seq, stride_token;   // in elements
+    int trace_slot;
 };
 
 template <int D>
@@ -44,21 +45,12 @@ __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ 
                                                        const RingAppend ap) {
     // the decode kernel may start its set-up now; it waits for this grid before it reads our output
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    if (ap.new_k != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
-        const int row_bytes = D * ap.elem_bytes, chunks_per_row = row_bytes / 16;
-        for (int i = threadIdx.x; i < ap.B * ap.H * chunks_per_row; i += 256) {
-            const int c = i % chunks_per_row, h = (i / chunks_per_row) % ap.H, b = i / (chunks_per_row * ap.H);
-            const int pos = ap.ring_lens[b];
-            if (pos < 0 || pos >= ap.capacity) continue;
-            const int64_t dst = ((int64_t)b * ap.stride_seq + (int64_t)pos * ap.stride_token + (int64_t)h * D) * ap.elem_bytes;
-            const int64_t src = ((int64_t)(b * ap.H + h) * D) * ap.elem_bytes;
-            *reinterpret_cast<uint4*>((char*)ap.ring_k + dst + c * 16) = *reinterpret_cast<const uint4*>((const char*)ap.new_k + src + c * 16);
-            *reinterpret_cast<uint4*>((char*)ap.ring_v + dst + c * 16) = *reinterpret_cast<const uint4*>((const char*)ap.new_v + src + c * 16);
-        }
-        __syncthreads();
-        for (int b = threadIdx.x; b < ap.B; b += 256)
-            if (ap.ring_lens[b] >= 0 && ap.ring_lens[b] < ap.capacity) ap.ring_lens[b] += 1;
-    }
+#ifdef TQ_TRACE
+#define TQ_QSTAMP(i) do { if (threadIdx.x == 0) { const int c = blockIdx.x + gridDim.x * blockIdx.y; if (c < 256) g_tq_trace_q[((ap.trace_slot & 1) * 256 + c) * 4 + (i)] = tq_now(); } } while (0)
+#else
+#define TQ_QSTAMP(i)
+#endif
+    TQ_QSTAMP(0);
     __shared__ float qsm[4 * D];          // queries
     __shared__ float red[8 * 4 * 32];     // partial sums
     __shared__ float qn2[4];              // squared norms
@@ -75,6 +67,25 @@ __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ 
     float mv[D / 8];
 #pragma unroll
     for (int k = 0; k < D / 8; ++k) mv[k] = __ldg(m + (size_t)(k0 + k) * D + col);
+    // This grid may itself have been started before the kernel ahead of it in the stream finished
+    // (programmatic dependent launch): the query and the ring belong to that kernel until here.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    TQ_QSTAMP(1);
+    if (ap.new_k != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
+        const int row_bytes = D * ap.elem_bytes, chunks_per_row = row_bytes / 16;
+        for (int i = threadIdx.x; i < ap.B * ap.H * chunks_per_row; i += 256) {
+            const int c = i % chunks_per_row, h = (i / chunks_per_row) % ap.H, b = i / (chunks_per_row * ap.H);
+            const int pos = ap.ring_lens[b];
+            if (pos < 0 || pos >= ap.capacity) continue;
+            const int64_t dst = ((int64_t)b * ap.stride_seq + (int64_t)pos * ap.stride_token + (int64_t)h * D) * ap.elem_bytes;
+            const int64_t src = ((int64_t)(b * ap.H + h) * D) * ap.elem_bytes;
+            *reinterpret_cast<uint4*>((char*)ap.ring_k + dst + c * 16) = *reinterpret_cast<const uint4*>((const char*)ap.new_k + src + c * 16);
+            *reinterpret_cast<uint4*>((char*)ap.ring_v + dst + c * 16) = *reinterpret_cast<const uint4*>((const char*)ap.new_v + src + c * 16);
+        }
+        __syncthreads();
+        for (int b = threadIdx.x; b < ap.B; b += 256)
+            if (ap.ring_lens[b] >= 0 && ap.ring_lens[b] < ap.capacity) ap.ring_lens[b] += 1;
+    }
     for (int i = threadIdx.x; i < 4 * D; i += 256) {
         const int v = i / D;
         qsm[i] = v < nv ? tq_load_any(q, (v0 + v) * D + (i % D), dt) : 0.f;
@@ -129,16 +140,28 @@ __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ 
             }
         }
     }
+    TQ_QSTAMP(2);
 }
 
 int launch_qprep(const void* q, int dt, int64_t nvec, int D, const float* pi_t, const float* s_t, float* out,
                  uint32_t* frag, int G, int Qh, int mse_bits, const RingAppend& ap, cudaStream_t st) {
-    dim3 grid((unsigned)(2 * D / 32), (unsigned)((nvec + 3) / 4));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(2 * D / 32), (unsigned)((nvec + 3) / 4));
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // its matrix loads may run under the previous kernel's tail
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const int dti = dt;
+    cudaError_t e;
     if (D == 128)
-        tq_qprep_kernel<128><<<grid, 256, 0, st>>>(q, dt, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
+        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<128>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
     else
-        tq_qprep_kernel<256><<<grid, 256, 0, st>>>(q, dt, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
-    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
+        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<256>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
+    return e == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 
 template <int D, int MSE_BITS, int VAL_BITS, int GP>
@@ -487,6 +510,10 @@ extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_
     float* qprep = (float*)(ws + w.off_qprep);
     uint32_t* qfrag = (uint32_t*)(ws + w.off_qfrag);
     RingAppend ap = {};
+#ifdef TQ_TRACE
+    static int trace_launch_q = 0;
+    ap.trace_slot = trace_launch_q++;
+#endif
     if (a->append_k != nullptr) {
         if (!has_ring || !a->append_v || a->query_prepared) return TQ_ERR_NULL;
         if (a->ring_capacity < a->max_ring_len) return TQ_ERR_SHAPE;
@@ -548,6 +575,10 @@ extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_
     p.ring_splits = rsplits;
     p.land_bytes = 0;
     p.frags_ready = a->query_prepared ? 1 : 0;
+#ifdef TQ_TRACE
+    static int trace_launch = 0;
+    p.trace_slot = trace_launch++;
+#endif
 
     const int mse_bits = consts->cfg.key_bits - 1, vb = consts->cfg.value_bits;
     if (a->kernel != 1) {   // tensor-core kernel where it applies
@@ -741,3 +772,9 @@ extern "C" int tq_decode_static(const tq_consts* consts, const tq_pool* pool, co
     b.query_prepared = 0;   // the prepared query of an earlier call may have been overwritten by another caller
     return tq_decode(consts, pool, &b, stream);   // answers TQ_ERR_WORKSPACE when the launch needs more than the array
 }
+
+#ifdef TQ_TRACE
+extern "C" int tq_debug_read_trace_q(unsigned long long* out, int n) {
+    return cudaMemcpyFromSymbol(out, tqdec::g_tq_trace_q, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -5;
+}
+#endif

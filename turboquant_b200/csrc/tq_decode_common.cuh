@@ -14,7 +14,8 @@ constexpr int RING_TOK = 32;  // ring tokens per ring CTA
 
 #ifdef TQ_TRACE
 // Debug build only: per-CTA phase time stamps (ns) for latency analysis.
-static __device__ unsigned long long g_tq_trace[4096 * 16];
+static __device__ unsigned long long g_tq_trace[4096 * 16];   // two launches of up to 2048 CTAs, alternating
+static __device__ unsigned long long g_tq_trace_q[2 * 256 * 4];    // query-prep launches, same alternation
 __device__ __forceinline__ unsigned long long tq_now() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -24,7 +25,7 @@ __device__ __forceinline__ unsigned long long tq_now() {
     do {                                                                                                  \
         if (threadIdx.x == 0) {                                                                           \
             const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);               \
-            if (cta < 4096) g_tq_trace[cta * 16 + (i)] = tq_now();                                         \
+            if (cta < 2048) g_tq_trace[((p.trace_slot & 1) * 2048 + cta) * 16 + (i)] = tq_now();          \
         }                                                                                                 \
     } while (0)
 #else
@@ -56,6 +57,9 @@ struct DecodeParams {
     int32_t* tickets;
     int32_t* status;
     int num_splits, ring_splits;
+#ifdef TQ_TRACE
+    int trace_slot;
+#endif
     int frags_ready;       // the query fragments were written before this launch was enqueued (no query-prep grid ahead)
     uint32_t land_bytes;   // tensor-core kernel: shared memory in front of its barriers, reusable by the merge
 };

@@ -108,6 +108,9 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
     const int gid = lane >> 2, tig = lane & 3;
     const int b = blockIdx.z, h = blockIdx.y, x = blockIdx.x;
     TQ_STAMP(0);
+    // a kernel launched behind this one with programmatic stream serialisation may be scheduled as soon
+    // as every CTA of this grid is running; whatever it reads of ours it reads after its own wait
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (x >= p.num_splits) {
         // exact ring tokens: CUDA-core fp32 path shared with the generic kernel.  The ring and its
