@@ -14,7 +14,8 @@ so that the bytes touched between two visits of a layer (8 x 25.8 MB) exceed the
 
 `value` is KV tokens attended per second with everything resident in HBM (steps
 replayed from CUDA graphs); `e2e` is the same metric through the Python API with
-host buffers, H2D/D2H copies inside the timed region.  With N > 1 every rank runs
+pinned host buffers: every step moves the new key/value/query to the device and the
+attention output back inside the timed region.  With N > 1 every rank runs
 its own sequences (weak scaling, no data-path collective) and the time is the max
 over ranks.
 """
@@ -40,6 +41,9 @@ WL = dict(name="config1: decode D=256 Hkv=4 Hq=16 N=32768 ring=128 key3b/val2b b
 METRIC = "decode_attention_kv_tokens_per_s"
 UNIT = "tokens/s"
 N_NEW = 256  # distinct new tokens / queries per layer, reused cyclically
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch of this workload, from the ncu capture
+# summarised in profiles/tq_decode_mma_kernel.md (25.94 MB read, 0 written: outputs stay in L2)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 25.94e6
 
 
 def _peaks():
@@ -467,7 +471,8 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "kernel": "tq_decode_mma_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                          "frac_of_nominal_8TBs": achieved / 8000.0, "us_per_launch": kern_ms * 1e3,
-                         "bytes_per_launch": bytes_per_launch, "traffic": None},
+                         "bytes_per_launch": bytes_per_launch, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                         "traffic_source": "ncu capture of one launch, profiles/tq_decode_mma_kernel.md"},
             "e2e": {"value": e2e_tokens / e2e_s, "unit": UNIT, "steps": e2e_steps,
                     "ms_per_step": e2e_s / e2e_steps * 1e3,
                     "call": "KVCaptureEngine.decode_step_host (pinned host buffers; H2D copy, ring append + attention, "

@@ -38,24 +38,33 @@ __device__ __forceinline__ void gemm_tile(const float* __restrict__ a_t, const f
     for (int t = 0; t < NTQ; ++t)
 #pragma unroll
         for (int c = 0; c < 4; ++c) acc[t][c] = 0.f;
-#pragma unroll 4
-    for (int k = 0; k < D; ++k) {
-        const float4 bv = __ldg(reinterpret_cast<const float4*>(b + (size_t)k * D + col));
-        float av[NTQ];
+    // rows of B come from L2: eight are requested before the first is used, so the loop is not
+    // a chain of dependent memory latencies; the summation order over k is unchanged
+    constexpr int KB = 8;
+#pragma unroll 1
+    for (int k0 = 0; k0 < D; k0 += KB) {
+        float4 bv[KB];
 #pragma unroll
-        for (int t4 = 0; t4 < NTQ / 4; ++t4) {
-            const float4 a4 = *reinterpret_cast<const float4*>(a_t + k * LDT + t_base + 4 * t4);
-            av[4 * t4 + 0] = a4.x;
-            av[4 * t4 + 1] = a4.y;
-            av[4 * t4 + 2] = a4.z;
-            av[4 * t4 + 3] = a4.w;
-        }
+        for (int kk = 0; kk < KB; ++kk) bv[kk] = __ldg(reinterpret_cast<const float4*>(b + (size_t)(k0 + kk) * D + col));
 #pragma unroll
-        for (int t = 0; t < NTQ; ++t) {
-            acc[t][0] = fmaf(av[t], bv.x, acc[t][0]);
-            acc[t][1] = fmaf(av[t], bv.y, acc[t][1]);
-            acc[t][2] = fmaf(av[t], bv.z, acc[t][2]);
-            acc[t][3] = fmaf(av[t], bv.w, acc[t][3]);
+        for (int kk = 0; kk < KB; ++kk) {
+            const int k = k0 + kk;
+            float av[NTQ];
+#pragma unroll
+            for (int t4 = 0; t4 < NTQ / 4; ++t4) {
+                const float4 a4 = *reinterpret_cast<const float4*>(a_t + k * LDT + t_base + 4 * t4);
+                av[4 * t4 + 0] = a4.x;
+                av[4 * t4 + 1] = a4.y;
+                av[4 * t4 + 2] = a4.z;
+                av[4 * t4 + 3] = a4.w;
+            }
+#pragma unroll
+            for (int t = 0; t < NTQ; ++t) {
+                acc[t][0] = fmaf(av[t], bv[kk].x, acc[t][0]);
+                acc[t][1] = fmaf(av[t], bv[kk].y, acc[t][1]);
+                acc[t][2] = fmaf(av[t], bv[kk].z, acc[t][2]);
+                acc[t][3] = fmaf(av[t], bv[kk].w, acc[t][3]);
+            }
         }
     }
 }
