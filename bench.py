@@ -266,6 +266,12 @@ def measure_decode_large(dev, n_seq: int = 256, n_tok: int = 8192):
 
 def cpu_baseline(steps: int, warmup: int, n_hist: int):
     """The oracle (a torch-CPU restatement of the reference's path) on the host cores."""
+    # all host threads the process may use, whatever OMP_NUM_THREADS the launcher exported (torchrun sets 1)
+    try:
+        n_cpu = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n_cpu = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n_cpu))
     from oracle import tq_oracle as O
     from turboquant_b200.codebook import get_codebook_tensors
     w = WL
