@@ -206,12 +206,14 @@ def sm_count(device) -> int:
 
 def choose_splits(batch: int, num_kv_heads: int, max_seq_len: int, sms: int, max_ring_len: int = 0) -> int:
     """Sequence splits per (sequence, kv head).  The decode kernel runs one
-    12-warp CTA per SM: with few (sequence, head) pairs the sequence is cut so
-    that every SM gets one CTA; with many pairs a CTA takes at most 512 records
-    (8192 tokens) so that long and short sequences balance out."""
+    12-warp CTA per SM when the launch fits one wave: with few (sequence, head)
+    pairs the sequence is cut so that every SM gets one CTA, the ring tokens
+    taking CTAs of their own (64 tokens each when the launch fits one wave -
+    the library applies the same rule); with many pairs a CTA takes at most
+    512 records (8192 tokens) so that long and short sequences balance out."""
     nblk = (max_seq_len + TQ_BLOCK_TOKENS - 1) // TQ_BLOCK_TOKENS
     pairs = max(1, batch * num_kv_heads)
-    ring_ctas = (max_ring_len + 31) // 32          # the ring tokens take CTAs of their own: keep it one wave
+    ring_ctas = (max_ring_len + 63) // 64
     want = max(sms // pairs - ring_ctas, -(-nblk // 512), 1)
     return max(1, min(want, max(1, nblk // 12)))
 

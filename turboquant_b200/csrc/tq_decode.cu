@@ -444,7 +444,25 @@ WsLayout decode_ws_layout(int D, int B, int Qh, int H, int max_slots) {
     return w;
 }
 
-int ring_splits_for(int max_ring_len) { return (max_ring_len + RING_TOK - 1) / RING_TOK; }
+int ring_splits_for(int max_ring_len, int ring_tok) { return (max_ring_len + ring_tok - 1) / ring_tok; }
+
+int sm_count_of_current_device() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0, n = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        sms = n > 0 ? n : 148;
+    }
+    return sms;
+}
+
+// Ring tokens per ring CTA: 64 when the whole launch then fits one wave (fewer ring CTAs leave more
+// SMs to the history), else 32.  A pure function of the launch shape, so that callers can plan with it.
+int ring_tok_for(int max_ring_len, int64_t pairs, int splits) {
+    if (max_ring_len <= RING_TOK) return RING_TOK;
+    const int r64 = (max_ring_len + 2 * RING_TOK - 1) / (2 * RING_TOK);
+    return pairs * (splits + r64) <= sm_count_of_current_device() ? 2 * RING_TOK : RING_TOK;
+}
 
 }  // namespace
 
@@ -502,7 +520,8 @@ extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_
     }
     if (splits < 1) splits = 1;
     if (splits > ntile && ntile > 0) splits = ntile;
-    const int rsplits = has_ring ? ring_splits_for(a->max_ring_len) : 0;
+    const int ring_tok = has_ring ? ring_tok_for(a->max_ring_len, (int64_t)a->batch * H, splits) : RING_TOK;
+    const int rsplits = has_ring ? ring_splits_for(a->max_ring_len, ring_tok) : 0;
     const WsLayout w = decode_ws_layout(D, a->batch, a->num_q_heads, H, splits + rsplits);
     if (w.total > a->workspace_bytes) return TQ_ERR_WORKSPACE;
 
@@ -573,6 +592,7 @@ extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_
     p.status = (int32_t*)ws;
     p.num_splits = splits;
     p.ring_splits = rsplits;
+    p.ring_tok = ring_tok;
     p.land_bytes = 0;
     p.frags_ready = a->query_prepared ? 1 : 0;
 #ifdef TQ_TRACE

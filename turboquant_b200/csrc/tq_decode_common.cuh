@@ -10,7 +10,7 @@ constexpr int DEC_THREADS = 128;
 constexpr int TILE_BLOCKS = 4;
 constexpr int TILE_TOK = TILE_BLOCKS * TQ_BLOCK_TOKENS;  // 64
 constexpr int NSTAGE = 3;
-constexpr int RING_TOK = 32;  // ring tokens per ring CTA
+constexpr int RING_TOK = 32;  // ring tokens a ring CTA stages at a time
 
 #ifdef TQ_TRACE
 // Debug build only: per-CTA phase time stamps (ns) for latency analysis.
@@ -57,6 +57,7 @@ struct DecodeParams {
     int32_t* tickets;
     int32_t* status;
     int num_splits, ring_splits;
+    int ring_tok;          // ring tokens per ring CTA, a multiple of RING_TOK
 #ifdef TQ_TRACE
     int trace_slot;
 #endif
@@ -317,29 +318,37 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
     if (tid == 0) p.tickets[b * p.H + h] = 0;  // ready for the next launch
 }
 
-// Exact attention over this CTA's slice of the ring (up to RING_TOK tokens),
-// fp32 like the reference's matmul path (score.py:154-170); works for any
-// block size.  The slice's key and value rows are first staged in shared
-// memory with 16-byte loads that are all in flight at once; everything after
-// that runs out of shared memory.  Writes the CTA's partial itself.
+// Exact attention over this CTA's slice of the ring: p.ring_tok tokens, taken RING_TOK (32) at a
+// time, fp32 like the reference's matmul path (score.py:154-170); works for any block size.  The
+// sub-slice's key and value rows are first staged in shared memory with 16-byte loads that are all
+// in flight at once; everything after that runs out of shared memory.  Sub-slices are merged with
+// the usual running max / sum; the CTA writes its partial itself.
 // scratch: qf [D][GP], sc [GP][RING_TOK], pp [RING_TOK][GP] floats, ml [2*GP],
 //          kst / vst: RING_TOK * D * element size bytes each, 16-byte aligned.
 template <int D, int GP>
 __device__ __forceinline__ void ring_part(const DecodeParams& p, int b, int h, int slot_idx, float* qf, float* sc,
                                           float* pp, float* ml, uint8_t* kst, uint8_t* vst) {
+    constexpr int MAX_OWN = (GP * D + 127) / 128;   // outputs per thread with at least 128 threads
     const int tid = threadIdx.x, nt = blockDim.x, warp = tid >> 5, lane = tid & 31;
     const int rs = slot_idx - p.num_splits;
     const int R = p.ring_lens ? p.ring_lens[b] : 0;
-    const int r0 = rs * RING_TOK;
-    const int nr = max(0, min(RING_TOK, R - r0));
     float* mine = partial_ptr<D, GP>(p, b, h, slot_idx);
+    // running state: ml[0..GP) max, ml[GP..2GP) sum (shared), acc of this thread's outputs (registers)
+    float acc[MAX_OWN];
+#pragma unroll
+    for (int u = 0; u < MAX_OWN; ++u) acc[u] = 0.f;
     if (tid < GP) {
         ml[tid] = -INFINITY;
         ml[GP + tid] = 0.f;
     }
-    if (nr > 0) {
-        const int eb = p.ring_dtype == TQ_F32 ? 4 : 2;
-        const int row_chunks = D * eb / 16;
+    const int eb = p.ring_dtype == TQ_F32 ? 4 : 2;
+    const int row_chunks = D * eb / 16;
+    bool have_q = false;
+    for (int sub = 0; sub < p.ring_tok / RING_TOK; ++sub) {
+        const int r0 = rs * p.ring_tok + sub * RING_TOK;
+        const int nr = max(0, min(RING_TOK, R - r0));
+        if (nr <= 0) break;   // uniform over the CTA
+        __syncthreads();      // the previous sub-slice is consumed
         for (int i = tid; i < nr * row_chunks; i += nt) {
             const int t = i / row_chunks, c = i % row_chunks;
             const int64_t off = ((int64_t)b * p.ring_stride_seq + (int64_t)(r0 + t) * p.ring_stride_token +
@@ -347,9 +356,12 @@ __device__ __forceinline__ void ring_part(const DecodeParams& p, int b, int h, i
             reinterpret_cast<uint4*>(kst)[i] = *reinterpret_cast<const uint4*>((const char*)p.ring_k + off);
             reinterpret_cast<uint4*>(vst)[i] = *reinterpret_cast<const uint4*>((const char*)p.ring_v + off);
         }
-        for (int i = tid; i < D * GP; i += nt) {
-            const int j = i / GP, g = i % GP;
-            qf[i] = g < p.G ? tq_load_any(p.query, ((int64_t)b * p.Qh + h * p.G + g) * D + j, p.q_dtype) : 0.f;
+        if (!have_q) {
+            for (int i = tid; i < D * GP; i += nt) {
+                const int j = i / GP, g = i % GP;
+                qf[i] = g < p.G ? tq_load_any(p.query, ((int64_t)b * p.Qh + h * p.G + g) * D + j, p.q_dtype) : 0.f;
+            }
+            have_q = true;
         }
         __syncthreads();
         for (int t = warp; t < nr; t += nt / 32) {
@@ -368,24 +380,38 @@ __device__ __forceinline__ void ring_part(const DecodeParams& p, int b, int h, i
             }
         }
         __syncthreads();
+        // per head: new running max, probabilities of this sub-slice, factor for what came before
         for (int g = warp; g < GP; g += nt / 32) {
             const float s0 = lane < nr ? sc[g * RING_TOK + lane] : -INFINITY;
-            const float m_new = tq_warp_max(s0);
+            const float m_old = ml[g];
+            const float m_new = fmaxf(m_old, tq_warp_max(s0));
             const float p0 = (s0 == -INFINITY) ? 0.f : __expf(s0 - m_new);
             const float sum = tq_warp_sum(p0);
             pp[lane * GP + g] = p0;
             if (lane == 0) {
+                const float alpha = (m_old == -INFINITY) ? 0.f : __expf(m_old - m_new);
+                sc[g * RING_TOK] = alpha;        // the scores of this head are consumed: reuse slot 0
                 ml[g] = m_new;
-                ml[GP + g] = sum;
+                ml[GP + g] = ml[GP + g] * alpha + sum;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int u = 0; u < MAX_OWN; ++u) {
+            const int i = tid + u * nt;
+            if (i < GP * D) {
+                const int g = i / D, d = i % D;
+                float a = acc[u] * sc[g * RING_TOK];
+                for (int t = 0; t < nr; ++t) a = fmaf(pp[t * GP + g], tq_load_any(vst, t * D + d, p.ring_dtype), a);
+                acc[u] = a;
             }
         }
     }
     __syncthreads();
-    for (int i = tid; i < GP * D; i += nt) {
-        const int g = i / D, d = i % D;
-        float acc = 0.f;
-        for (int t = 0; t < nr; ++t) acc = fmaf(pp[t * GP + g], tq_load_any(vst, t * D + d, p.ring_dtype), acc);
-        mine[2 * GP + i] = acc;
+#pragma unroll
+    for (int u = 0; u < MAX_OWN; ++u) {
+        const int i = tid + u * nt;
+        if (i < GP * D) mine[2 * GP + i] = acc[u];
     }
     if (tid < 2 * GP) mine[tid] = ml[tid];
 }
