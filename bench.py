@@ -264,6 +264,57 @@ def measure_decode_large(dev, n_seq: int = 256, n_tok: int = 8192):
             "kv_tokens_per_s": n_seq * n_tok / ms * 1e3, "device_status": ws.status()}
 
 
+def measure_decode_paged(dev, n_seq: int = 64, lo: int = 1024, hi: int = 32768):
+    """Batched paged decode of BASELINE config 2: 64 sequences of length U[1024, 32768], block size 16, head_dim 128,
+    8 kv heads, 32 query heads, bf16, 4-bit keys (3-bit codes + QJL sign) and 4-bit values, one query per sequence,
+    block tables = a seeded random permutation of a shared pool."""
+    from turboquant_b200 import _engine as E
+    d, h, qh = 128, 8, 32
+    c = E.LayerConstants(d, 4, 4, dev, seed=42)
+    gcpu = torch.Generator().manual_seed(11)
+    lens_l = [int(x) for x in torch.randint(lo, hi + 1, (n_seq,), generator=gcpu)]
+    per = [(n + 15) // 16 for n in lens_l]
+    total = sum(per)
+    perm = torch.randperm(total, generator=gcpu).to(torch.int32)
+    bt = torch.zeros(n_seq, max(per), dtype=torch.int32)
+    pos = 0
+    for s_, nb in enumerate(per):
+        bt[s_, :nb] = perm[pos:pos + nb]
+        pos += nb
+    bt = bt.to(dev)
+    pool = E.BlockPool(c, h, total)
+    g = torch.Generator(device=dev)
+    g.manual_seed(6)
+    ch = torch.exp(0.5 * torch.randn(d, generator=g, device=dev))
+    for s_ in range(n_seq):
+        n = lens_l[s_]
+        k = (torch.randn(n, h, d, generator=g, device=dev) * ch).to(torch.bfloat16)
+        v = torch.randn(n, h, d, generator=g, device=dev).to(torch.bfloat16)
+        E.store(c, pool, k, v, stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h, block_table=bt[s_],
+                start_pos=0)
+    q = torch.randn(n_seq, qh, d, generator=g, device=dev).to(torch.bfloat16)
+    lens = torch.tensor(lens_l, dtype=torch.int32, device=dev)
+    ws = E.Workspace(dev)
+    out = torch.empty_like(q)
+    for _ in range(3):
+        E.decode(c, pool, ws, q, bt, lens, max(lens_l), out=out)
+    torch.cuda.synchronize()
+    reps = 10
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        E.decode(c, pool, ws, q, bt, lens, max(lens_l), out=out)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    nbytes = sum(lens_l) * h * c.bytes_per_token
+    peak, kind = _peaks()
+    return {"workload": f"config2: {n_seq} seqs x U[{lo},{hi}] tok paged, Hkv=8 Hq=32 D=128 key4b/val4b",
+            "ms_per_step": ms, "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak, "peak_kind": f"of {kind}",
+            "kv_tokens_per_s": sum(lens_l) / ms * 1e3, "includes": "query preparation + decode per step",
+            "device_status": ws.status()}
+
+
 def cpu_baseline(steps: int, warmup: int, n_hist: int):
     """The oracle (a torch-CPU restatement of the reference's path) on the host cores."""
     # all host threads the process may use, whatever OMP_NUM_THREADS the launcher exported (torchrun sets 1)
@@ -462,6 +513,7 @@ def run_ours(args):
 
     store = measure_store(dev) if rank == 0 else None
     large = measure_decode_large(dev) if (rank == 0 and not args.no_large) else None
+    paged = measure_decode_paged(dev) if (rank == 0 and not args.no_large) else None
     base = cpu_baseline(3, 1, w["N"]) if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
 
     if rank == 0:
@@ -491,7 +543,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": (2 * w["H"] + w["Qh"]) * w["D"] * 2,
                     "d2h_bytes_per_step": w["Qh"] * w["D"] * 2},
             "gpu_launches": launches, "device_status": status, "clocks": clocks, "store": store,
-            "decode_large": large,
+            "decode_large": large, "decode_paged": paged,
         }
         if base is not None:
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -511,11 +563,15 @@ def main():
     ap.add_argument("--no-large", action="store_true", help="skip the batched 1.7 GB decode measurement")
     ap.add_argument("--only-large", action="store_true", help="run only the batched decode measurement (profiling)")
     ap.add_argument("--only-store", action="store_true", help="run only the store-path measurement (profiling)")
+    ap.add_argument("--only-paged", action="store_true", help="run only the paged batched decode measurement (profiling)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.only_store:
         torch.cuda.set_device(0)
         print(json.dumps(measure_store(torch.device("cuda", 0))), flush=True)
+    elif args.only_paged:
+        torch.cuda.set_device(0)
+        print(json.dumps(measure_decode_paged(torch.device("cuda", 0))), flush=True)
     elif args.only_large:
         torch.cuda.set_device(0)
         print(json.dumps(measure_decode_large(torch.device("cuda", 0))), flush=True)
