@@ -703,9 +703,24 @@ extern "C" size_t tq_decode_static_scratch_bytes(void) { return (size_t)TQ_STATI
 namespace {
 
 // Small step inputs are pulled from mapped host memory by a one-CTA kernel: a copy-engine
-// transfer between two kernels of a stream costs several microseconds of switching.
+// transfer between two kernels of a stream costs several microseconds of switching.  Launched
+// with programmatic stream serialisation, it reads the host buffer into registers while the
+// kernel ahead of it is still running and writes the device buffer (which that kernel may be
+// reading) only after it has completed.
 __global__ void __launch_bounds__(1024) tq_stage_in_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int n16) {
-    for (int i = threadIdx.x; i < n16; i += 1024) dst[i] = src[i];
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    uint4 v[4];   // n16 <= 4096
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = threadIdx.x + u * 1024;
+        if (i < n16) v[u] = src[i];
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = threadIdx.x + u * 1024;
+        if (i < n16) dst[i] = v[u];
+    }
 }
 
 constexpr size_t HOST_IO_DIRECT_MAX = 64 * 1024;
@@ -747,8 +762,18 @@ extern "C" int tq_decode_host_io(const tq_consts* consts, const tq_pool* pool, c
         const bool direct = in_bytes <= HOST_IO_DIRECT_MAX && (in_bytes & 15) == 0 &&
                             (((uintptr_t)host_in | (uintptr_t)dev_in) & 15) == 0 && host_ptr_is_mapped(host_in, in_bytes);
         if (direct) {
-            tq_stage_in_kernel<<<1, 1024, 0, st>>>((const uint4*)host_in, (uint4*)dev_in, (int)(in_bytes / 16));
-            if (cudaGetLastError() != cudaSuccess) return TQ_ERR_CUDA;
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(1);
+            cfg.blockDim = dim3(1024);
+            cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaLaunchKernelEx(&cfg, tq_stage_in_kernel, (const uint4*)host_in, (uint4*)dev_in, (int)(in_bytes / 16)) !=
+                cudaSuccess)
+                return TQ_ERR_CUDA;
         } else if (cudaMemcpyAsync(dev_in, host_in, in_bytes, cudaMemcpyHostToDevice, st) != cudaSuccess) {
             return TQ_ERR_CUDA;
         }
