@@ -41,4 +41,6 @@ def main(ref_root: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: python " + os.path.basename(__file__) + " <path to a checkout of the reference (0xSero/turboquant)>")
+    main(sys.argv[1])
