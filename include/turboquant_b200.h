@@ -205,12 +205,12 @@ int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_decode_args
  * args->query / append_k / append_v normally point into `dev_in`.  Nothing is synchronised; either
  * copy is skipped when its host pointer is NULL.  Transfers of at most 64 KiB to or from
  * page-locked host memory that the GPU can address (cudaHostAlloc / cudaHostRegister; checked
- * with cudaPointerGetAttributes) do not use the copy engines: a one-CTA kernel pulls the input,
- * and the decode kernel writes the result into `host_out` itself (args->out is then left
- * untouched); anything else goes through cudaMemcpyAsync.
- * Replaces the .to(device) / .cpu() traffic around compute_hybrid_attention in the
- * reference's hooks (integration/vllm.py:205-222 hands over tensors that are already on the
- * device; a host-side caller of score.py does these copies itself). */
+ * with cudaPointerGetAttributes) do not use the copy engines: when query / append_k / append_v
+ * all point into `dev_in`, the query-preparation kernel reads them straight from `host_in`
+ * (before it waits for the kernel ahead of it on the stream) and `dev_in` is not written at
+ * all; otherwise a one-CTA kernel pulls `host_in` into `dev_in`.  The decode kernel writes the
+ * result into `host_out` itself (args->out is then left untouched).  Anything else goes through
+ * cudaMemcpyAsync.  `host_in` must stay unchanged until the step has completed. */
 int tq_decode_host_io(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* args, const void* host_in,
                       void* dev_in, size_t in_bytes, void* host_out, size_t out_bytes, void* stream);
 

@@ -35,6 +35,8 @@ struct RingAppend {
     int elem_bytes, B, H, capacity;
     int64_t stride_seq, stride_token;   // in elements
     int trace_slot;
+    int early_inputs;   // query and new token come from host memory that no earlier kernel writes:
+                        // read them before waiting for the kernel ahead (their latency hides under it)
 };
 
 template <int D>
@@ -68,27 +70,54 @@ __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ 
 #pragma unroll
     for (int k = 0; k < D / 8; ++k) mv[k] = __ldg(m + (size_t)(k0 + k) * D + col);
     // This grid may itself have been started before the kernel ahead of it in the stream finished
-    // (programmatic dependent launch): the query and the ring belong to that kernel until here.
+    // (programmatic dependent launch): the query and the ring belong to that kernel until the wait -
+    // unless they are host buffers nobody on the device writes, which are then fetched first.
+    const bool do_append = ap.new_k != nullptr && blockIdx.x == 0 && blockIdx.y == 0;
+    const int row_bytes = D * ap.elem_bytes, chunks_per_row = row_bytes / 16;
+    const int n_app = do_append ? ap.B * ap.H * chunks_per_row : 0;
+    uint4 ak = make_uint4(0u, 0u, 0u, 0u), av = ak;   // first append chunk of this thread, when fetched early
+    float qv[4 * D / 256];
+    if (ap.early_inputs) {
+#pragma unroll
+        for (int u = 0; u < 4 * D / 256; ++u) {
+            const int i = threadIdx.x + u * 256, v = i / D;
+            qv[u] = v < nv ? tq_load_any(q, (v0 + v) * D + (i % D), dt) : 0.f;
+        }
+        if ((int)threadIdx.x < n_app) {
+            const int i = threadIdx.x;
+            const int c = i % chunks_per_row, h = (i / chunks_per_row) % ap.H, b = i / (chunks_per_row * ap.H);
+            const int64_t src = ((int64_t)(b * ap.H + h) * D) * ap.elem_bytes;
+            ak = *reinterpret_cast<const uint4*>((const char*)ap.new_k + src + c * 16);
+            av = *reinterpret_cast<const uint4*>((const char*)ap.new_v + src + c * 16);
+        }
+    }
     asm volatile("griddepcontrol.wait;" ::: "memory");
     TQ_QSTAMP(1);
-    if (ap.new_k != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
-        const int row_bytes = D * ap.elem_bytes, chunks_per_row = row_bytes / 16;
-        for (int i = threadIdx.x; i < ap.B * ap.H * chunks_per_row; i += 256) {
+    if (do_append) {
+        for (int i = threadIdx.x; i < n_app; i += 256) {
             const int c = i % chunks_per_row, h = (i / chunks_per_row) % ap.H, b = i / (chunks_per_row * ap.H);
             const int pos = ap.ring_lens[b];
             if (pos < 0 || pos >= ap.capacity) continue;
             const int64_t dst = ((int64_t)b * ap.stride_seq + (int64_t)pos * ap.stride_token + (int64_t)h * D) * ap.elem_bytes;
             const int64_t src = ((int64_t)(b * ap.H + h) * D) * ap.elem_bytes;
-            *reinterpret_cast<uint4*>((char*)ap.ring_k + dst + c * 16) = *reinterpret_cast<const uint4*>((const char*)ap.new_k + src + c * 16);
-            *reinterpret_cast<uint4*>((char*)ap.ring_v + dst + c * 16) = *reinterpret_cast<const uint4*>((const char*)ap.new_v + src + c * 16);
+            const bool early = ap.early_inputs && i == (int)threadIdx.x;
+            *reinterpret_cast<uint4*>((char*)ap.ring_k + dst + c * 16) =
+                early ? ak : *reinterpret_cast<const uint4*>((const char*)ap.new_k + src + c * 16);
+            *reinterpret_cast<uint4*>((char*)ap.ring_v + dst + c * 16) =
+                early ? av : *reinterpret_cast<const uint4*>((const char*)ap.new_v + src + c * 16);
         }
         __syncthreads();
         for (int b = threadIdx.x; b < ap.B; b += 256)
             if (ap.ring_lens[b] >= 0 && ap.ring_lens[b] < ap.capacity) ap.ring_lens[b] += 1;
     }
-    for (int i = threadIdx.x; i < 4 * D; i += 256) {
-        const int v = i / D;
-        qsm[i] = v < nv ? tq_load_any(q, (v0 + v) * D + (i % D), dt) : 0.f;
+    if (ap.early_inputs) {
+#pragma unroll
+        for (int u = 0; u < 4 * D / 256; ++u) qsm[threadIdx.x + u * 256] = qv[u];
+    } else {
+        for (int i = threadIdx.x; i < 4 * D; i += 256) {
+            const int v = i / D;
+            qsm[i] = v < nv ? tq_load_any(q, (v0 + v) * D + (i % D), dt) : 0.f;
+        }
     }
     __syncthreads();
     if (ks < 4) {
@@ -487,7 +516,8 @@ extern "C" int tq_scores_workspace_bytes(const tq_config* cfg, int64_t n_vectors
     return TQ_OK;
 }
 
-extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* a, void* stream) {
+static int decode_impl(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* a, void* stream,
+                       int early_inputs) {
     if (!consts || !pool || !a) return TQ_ERR_NULL;
     if (!pool->base || !a->query || !a->out || !a->workspace || !a->block_table || !a->seq_lens) return TQ_ERR_NULL;
     if (!consts->pi_t || !consts->s_t) return TQ_ERR_NULL;
@@ -529,6 +559,7 @@ extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_
     float* qprep = (float*)(ws + w.off_qprep);
     uint32_t* qfrag = (uint32_t*)(ws + w.off_qfrag);
     RingAppend ap = {};
+    ap.early_inputs = early_inputs;
 #ifdef TQ_TRACE
     static int trace_launch_q = 0;
     ap.trace_slot = trace_launch_q++;
@@ -619,6 +650,10 @@ extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_
         TQ_DEC(256, 3, 4);
     }
 #undef TQ_DEC
+}
+
+extern "C" int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* a, void* stream) {
+    return decode_impl(consts, pool, a, stream, 0);
 }
 
 extern "C" int tq_scores(const tq_consts* consts, const tq_pool* pool, const int32_t* block_table, int64_t n_tokens,
@@ -757,11 +792,28 @@ extern "C" int tq_decode_host_io(const tq_consts* consts, const tq_pool* pool, c
                                  void* stream) {
     if (!a) return TQ_ERR_NULL;
     cudaStream_t st = (cudaStream_t)stream;
+    tq_decode_args b = *a;
+    int early_inputs = 0;
     if (host_in != nullptr && in_bytes > 0) {
         if (!dev_in) return TQ_ERR_NULL;
         const bool direct = in_bytes <= HOST_IO_DIRECT_MAX && (in_bytes & 15) == 0 &&
                             (((uintptr_t)host_in | (uintptr_t)dev_in) & 15) == 0 && host_ptr_is_mapped(host_in, in_bytes);
-        if (direct) {
+        // Arguments that point into dev_in can be redirected into the mapped host buffer: the query
+        // preparation then reads them itself, before it waits for the kernel ahead of it, and no
+        // transfer of its own sits on the stream.  (The ring CTAs read the raw query from there too.)
+        auto inside = [&](const void* p) {
+            return p != nullptr && (const char*)p >= (const char*)dev_in && (const char*)p < (const char*)dev_in + in_bytes;
+        };
+        auto redirect = [&](const void* p) { return (const void*)((const char*)host_in + ((const char*)p - (const char*)dev_in)); };
+        const bool all_inside = inside(a->query) && (a->append_k == nullptr || (inside(a->append_k) && inside(a->append_v)));
+        if (direct && all_inside && !a->query_prepared) {
+            b.query = redirect(a->query);
+            if (a->append_k != nullptr) {
+                b.append_k = redirect(a->append_k);
+                b.append_v = redirect(a->append_v);
+            }
+            early_inputs = 1;
+        } else if (direct) {
             cudaLaunchConfig_t cfg = {};
             cfg.gridDim = dim3(1);
             cfg.blockDim = dim3(1024);
@@ -778,12 +830,11 @@ extern "C" int tq_decode_host_io(const tq_consts* consts, const tq_pool* pool, c
             return TQ_ERR_CUDA;
         }
     }
-    tq_decode_args b = *a;
     // a small result is written to mapped host memory by the merge itself
     const bool out_direct = host_out != nullptr && out_bytes > 0 && out_bytes <= HOST_IO_DIRECT_MAX &&
                             ((uintptr_t)host_out & 15) == 0 && host_ptr_is_mapped(host_out, out_bytes);
     if (out_direct) b.out = host_out;
-    const int rc = tq_decode(consts, pool, &b, stream);
+    const int rc = decode_impl(consts, pool, &b, stream, early_inputs);
     if (rc != TQ_OK) return rc;
     if (host_out != nullptr && out_bytes > 0 && !out_direct) {
         if (cudaMemcpyAsync(host_out, a->out, out_bytes, cudaMemcpyDeviceToHost, st) != cudaSuccess) return TQ_ERR_CUDA;
