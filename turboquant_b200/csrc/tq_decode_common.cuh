@@ -236,26 +236,40 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
             return;
         }
         TQ_STAMP(13);
-        // Out of shared memory: a thread owns four channels of one head (the head is the same for a whole
-        // warp, so the per-slot max and sum are broadcast reads) and weighs the slots itself.
+        // Out of shared memory: a thread owns four channels of one head; the head is the same for a
+        // whole warp, so the warp works out the slots' weights once - lane s takes slots s, s+32, ... -
+        // and hands them round by shuffle while every lane accumulates its channels.
         const float* sb = reinterpret_cast<const float*>(land);
-        for (int i = tid; i < p.G * (D / 4); i += nt) {
-            const int g = i / (D / 4), d = (i % (D / 4)) * 4;
+        const int lane = tid & 31;
+        const int items = p.G * (D / 4);
+        for (int i0 = (tid >> 5) * 32; i0 < items; i0 += nt) {   // D/4 is a multiple of 32: one head per warp pass
+            const int i = i0 + lane;
+            const int g = i0 / (D / 4), d = (i % (D / 4)) * 4;
             float mx = -INFINITY;
-            for (int s = 0; s < nslot; ++s) mx = fmaxf(mx, sb[s * PS + g]);
+            for (int s = lane; s < nslot; s += 32) mx = fmaxf(mx, sb[s * PS + g]);
+            mx = tq_warp_max(mx);
             const float4* src = reinterpret_cast<const float4*>(sb + 2 * GP + g * D + d);
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             float l = 0.f;
+            for (int s0 = 0; s0 < nslot; s0 += 32) {
+                const int sm = s0 + lane;
+                float wm = 0.f, wl = 0.f;     // this lane's slot: weight, weight * sum
+                if (sm < nslot) {
+                    const float ms = sb[sm * PS + g];
+                    wm = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
+                    wl = wm * sb[sm * PS + GP + g];
+                }
+                l += tq_warp_sum(wl);
+                const int cnt = min(32, nslot - s0);
 #pragma unroll 4
-            for (int s = 0; s < nslot; ++s) {
-                const float ms = sb[s * PS + g];
-                const float ws = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
-                l = fmaf(ws, sb[s * PS + GP + g], l);
-                const float4 v = src[s * (PS / 4)];
-                o.x = fmaf(ws, v.x, o.x);
-                o.y = fmaf(ws, v.y, o.y);
-                o.z = fmaf(ws, v.z, o.z);
-                o.w = fmaf(ws, v.w, o.w);
+                for (int k = 0; k < cnt; ++k) {
+                    const float ws = __shfl_sync(0xffffffffu, wm, k);
+                    const float4 v = src[(s0 + k) * (PS / 4)];
+                    o.x = fmaf(ws, v.x, o.x);
+                    o.y = fmaf(ws, v.y, o.y);
+                    o.z = fmaf(ws, v.z, o.z);
+                    o.w = fmaf(ws, v.w, o.w);
+                }
             }
             const float inv = l > 0.f ? 1.f / l : 0.f;
             const int64_t dst = ((int64_t)b * p.Qh + h * p.G + g) * D + d;

@@ -553,24 +553,30 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
         zrow[grp][1] = __shfl_sync(0xffffffffu, zacc[1], grp * 4 + tig);
     }
     __syncthreads();   // every warp is done with its stages: reuse them
-    float* osm = reinterpret_cast<float*>(stages);   // [NW warps][GP][D]
+    // [NW warps][GP][D + 4]: the padding spreads the four lanes that share a channel quad (one per
+    // pair of heads) over different banks; a thread stores the quad of a head with one 16-byte store
+    constexpr int DP = D + 4;
+    float* osm = reinterpret_cast<float*>(stages);
     if (col_ok) {
 #pragma unroll
-        for (int mb = 0; mb < NMB; ++mb) {
-            const int grp = mb >> 1, hb = mb & 1, odd = grp & 1;
+        for (int grp = 0; grp < NG; ++grp) {
+            const int odd = grp & 1;
+            float f[4];   // A value = code * 2^(sh - 24); probabilities carried x16
 #pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const int i = 2 * hb + half;
-                int sh;   // A value = code * 2^(sh - 24); probabilities carried x16
+            for (int i = 0; i < 4; ++i) {
+                int sh;
                 if (VAL_BITS == 2) sh = 2 * (odd ? (i == 0 ? 4 : i + 1) : i);
                 else sh = 4 * (i & 1);
-                const float f = pow2i(24 - sh - 4);
-                const int d = 32 * grp + 4 * gid + i;
+                f[i] = pow2i(24 - sh - 4);
+            }
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    const int g = 2 * tig + c;
-                    osm[(warp * GP + g) * D + d] = o[mb][2 * half + c] * f + zrow[grp][c] * 0.0625f;
-                }
+            for (int c = 0; c < 2; ++c) {
+                const int g = 2 * tig + c;
+                const float z = zrow[grp][c] * 0.0625f;
+                // channels 4*gid + i of the group: i = 2*hb + half sits in M-block 2*grp + hb, register 2*half + c
+                const float4 v = make_float4(fmaf(o[2 * grp][c], f[0], z), fmaf(o[2 * grp][2 + c], f[1], z),
+                                             fmaf(o[2 * grp + 1][c], f[2], z), fmaf(o[2 * grp + 1][2 + c], f[3], z));
+                *reinterpret_cast<float4*>(osm + (warp * GP + g) * DP + 32 * grp + 4 * gid) = v;
             }
         }
         if (gid == 0) {
@@ -599,7 +605,7 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
                 const float mw = ml[(w * 2) * GP + g];
                 const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - mx);
                 lsum = fmaf(f, ml[(w * 2 + 1) * GP + g], lsum);
-                const float4 v = *reinterpret_cast<const float4*>(osm + (w * GP + g) * D + d);
+                const float4 v = *reinterpret_cast<const float4*>(osm + (w * GP + g) * DP + d);
                 acc.x = fmaf(f, v.x, acc.x);
                 acc.y = fmaf(f, v.y, acc.y);
                 acc.z = fmaf(f, v.z, acc.z);
