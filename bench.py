@@ -315,6 +315,73 @@ def measure_decode_paged(dev, n_seq: int = 64, lo: int = 1024, hi: int = 32768):
             "device_status": ws.status()}
 
 
+def run_sharded(args):
+    """`--sharded`: one layer of BASELINE config 4 (256 sequences x 8192 tokens, 8 kv heads, 64 query heads,
+    head_dim 128, 3-bit keys / 2-bit values) partitioned over the ranks - kv heads first, then sequences -
+    with an all-gather of the head outputs (NCCL) after the local decode.  Total work is fixed (strong
+    scaling); the time of a step is the max over ranks of decode + all-gather, from CUDA events."""
+    from turboquant_b200 import _engine as E
+    from turboquant_b200 import sharding
+    dist, rank, world = _dist()
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    d, h, qh, n_seq, n_tok = 128, 8, 64, 256, 8192
+    g_heads = qh // h
+    sh = sharding.partition(n_seq, h, world, rank)
+    hl, sl = sh.num_heads, sh.num_seqs
+    c = E.LayerConstants(d, 3, 2, dev, seed=42)
+    nblk = n_tok // 16
+    pool = E.BlockPool(c, hl, sl * nblk)
+    bt = torch.arange(sl * nblk, dtype=torch.int32, device=dev).view(sl, nblk)
+    g = torch.Generator(device=dev)
+    g.manual_seed(100 + rank)
+    ch = torch.exp(0.5 * torch.randn(d, generator=g, device=dev))
+    for s_ in range(sl):
+        k = (torch.randn(n_tok, hl, d, generator=g, device=dev) * ch).to(torch.bfloat16)
+        v = torch.randn(n_tok, hl, d, generator=g, device=dev).to(torch.bfloat16)
+        E.store(c, pool, k, v, stride_token=hl * d, stride_head=d, n_tokens=n_tok, n_heads=hl, block_table=bt[s_],
+                start_pos=0)
+    q = torch.randn(sl, hl * g_heads, d, generator=g, device=dev).to(torch.bfloat16)
+    lens = torch.full((sl,), n_tok, dtype=torch.int32, device=dev)
+    ws = E.Workspace(dev)
+    out_local = torch.empty_like(q)
+    out_full = torch.empty(n_seq, qh, d, dtype=torch.bfloat16, device=dev)
+
+    def step():
+        E.decode(c, pool, ws, q, bt, lens, n_tok, out=out_local)
+        sharding.gather_head_outputs(out_local, sh, n_seq, h, out=out_full)
+
+    for _ in range(max(3, args.warmup)):
+        step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+        torch.cuda.synchronize()
+    steps = min(args.steps, 64)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms, tokens = sharding.reduce_timing(e0.elapsed_time(e1) / steps, float(sl * n_tok), dev)
+    status = ws.status()
+    if rank == 0:
+        nbytes = n_seq * n_tok * h * c.bytes_per_token
+        print(json.dumps({"metric": "sharded_layer_decode_kv_tokens_per_s", "value": n_seq * n_tok / ms * 1e3,
+                          "unit": UNIT, "n_gpus": world, "steps": steps, "ms_per_step": ms, "higher_is_better": True,
+                          "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": "config4 layer: 256 seqs x 8192 tok, Hkv=8 Hq=64 D=128 key3b/val2b",
+                                     "partition": f"{min(world, h)} head groups x {max(1, world // h)} sequence groups",
+                                     "collective": "all-gather of head outputs (torch.distributed, NCCL)",
+                                     "gathered_bytes_per_step": n_seq * qh * d * 2},
+                          "aggregate_hbm_gbs": nbytes / ms / 1e6, "device_status": status}), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def cpu_baseline(steps: int, warmup: int, n_hist: int):
     """The oracle (a torch-CPU restatement of the reference's path) on the host cores."""
     # all host threads the process may use, whatever OMP_NUM_THREADS the launcher exported (torchrun sets 1)
@@ -564,6 +631,8 @@ def main():
     ap.add_argument("--only-large", action="store_true", help="run only the batched decode measurement (profiling)")
     ap.add_argument("--only-store", action="store_true", help="run only the store-path measurement (profiling)")
     ap.add_argument("--only-paged", action="store_true", help="run only the paged batched decode measurement (profiling)")
+    ap.add_argument("--sharded", action="store_true",
+                    help="config-4 layer partitioned over the ranks with an all-gather of head outputs (strong scaling)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.only_store:
@@ -575,6 +644,8 @@ def main():
     elif args.only_large:
         torch.cuda.set_device(0)
         print(json.dumps(measure_decode_large(torch.device("cuda", 0))), flush=True)
+    elif args.sharded:
+        run_sharded(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -90,5 +90,8 @@ def test_null_and_shape_errors_come_before_any_launch(lib):
     args = _lib.tq_decode_args()
     assert lib.tq_decode(C.byref(consts), C.byref(pool), C.byref(args), None) == -1
     assert lib.tq_decode(None, None, None, None) == -1
+    assert lib.tq_decode_host_io(C.byref(consts), C.byref(pool), None, None, None, 0, None, 0, None) == -1
+    assert lib.tq_decode_host_io(C.byref(consts), C.byref(pool), C.byref(args), None, None, 0, None, 0, None) == -1
+    assert lib.tq_decode_static(C.byref(consts), C.byref(pool), None, None) == -1
     assert lib.tq_scores(C.byref(consts), C.byref(pool), None, 16, None, 0, 1, None, None, 0, None) == -1
     assert lib.tq_workspace_init(None, 1024, None) == -1

@@ -172,6 +172,17 @@ def _make_patched_forward(orig_fn, state: LayerState, no_alloc: bool = False, ca
                 output_block_scale)
         if capture_in_forward and mode != MODE_OFF and attn_metadata is not None:
             n = getattr(attn_metadata, "num_actual_tokens", key.shape[0])
+            c = state.config
+            if (mode == MODE_HYBRID and n == 1 and getattr(attn_metadata, "max_query_len", 1) == 1
+                    and state.supports_hybrid and state.store.num_tokens >= MIN_HISTORY
+                    and key.dtype == state.engine.ring.dtype and query.dtype == key.dtype):
+                # one decode token: ring append and attention in ONE library call, same result as
+                # capturing first and attending afterwards
+                result = state.engine.decode_step(_as_heads(query, 1, c.num_query_heads, c.head_dim),
+                                                  _as_heads(key, 1, c.num_kv_heads, c.head_dim),
+                                                  _as_heads(value, 1, c.num_kv_heads, c.head_dim),
+                                                  c.num_query_heads, scale=getattr(self_impl, "scale", None))
+                return _deliver(result, query, output, 1)
             _capture(state, key[:n], value[:n], n)
         if mode in (MODE_OFF, MODE_CAPTURE_ONLY) or attn_metadata is None:
             return original(*args)
