@@ -1,0 +1,64 @@
+"""Host-side logic that needs no GPU: the ring buffer's drain policy (reference
+capture.py:21-120), the split planner and the sharding arithmetic."""
+
+import pytest
+import torch
+
+from turboquant_b200 import _engine as E
+from turboquant_b200.capture import RingBuffer
+
+
+def _tok(i, h=2, d=4):
+    return torch.full((1, h, d), float(i))
+
+
+def test_ring_buffer_drains_whole_buffer_when_the_next_token_arrives():
+    rb = RingBuffer(4, 2, 4, "cpu", torch.float32)
+    assert rb.peek() is None and rb.drain() is None and rb.size == 0
+    for i in range(4):
+        assert rb.write(_tok(i), _tok(10 + i), 1) is None
+    assert rb.is_full and rb.size == 4
+    k, v = rb.peek()
+    assert [float(x) for x in k[:, 0, 0]] == [0, 1, 2, 3] and float(v[3, 0, 0]) == 13
+    out = rb.write(_tok(4), _tok(14), 1)              # the fifth token pushes the four out, as one chunk
+    assert out is not None and out[0].shape == (4, 2, 4)
+    assert [float(x) for x in out[0][:, 0, 0]] == [0, 1, 2, 3]
+    assert rb.size == 1 and rb.total_written == 5
+    k, _ = rb.peek()
+    assert float(k[0, 0, 0]) == 4
+
+
+def test_ring_buffer_long_write_drains_every_full_buffer():
+    rb = RingBuffer(4, 1, 2, "cpu", torch.float32)
+    keys = torch.arange(11, dtype=torch.float32).view(11, 1, 1).expand(11, 1, 2).contiguous()
+    out = rb.write(keys, keys, 11)
+    # 11 tokens through a 4-token ring: two full buffers leave, three tokens stay
+    assert out is not None and out[0].shape[0] == 8
+    assert [float(x) for x in out[0][:, 0, 0]] == list(range(8))
+    assert rb.size == 3 and [float(x) for x in rb.peek()[0][:, 0, 0]] == [8, 9, 10]
+    k, v = rb.drain()
+    assert k.shape[0] == 3 and rb.size == 0 and rb.peek() is None
+    rb.reset()
+    assert rb.total_written == 0
+
+
+@pytest.mark.parametrize("batch,h,n,ring", [(1, 4, 32768, 128), (1, 4, 32768, 0), (64, 8, 32768, 0), (256, 8, 8192, 0),
+                                            (1, 8, 1 << 20, 100), (2, 2, 100, 16), (1, 1, 16, 0), (1, 4, 0, 40)])
+def test_split_planner_keeps_the_kernels_limits(batch, h, n, ring):
+    sms = 148
+    s = E.choose_splits(batch, h, n, sms, ring)
+    nblk = (n + 15) // 16
+    assert s >= 1
+    # the tensor-core kernel keeps a split's block-table slice in shared memory: at most 1024 entries
+    assert -(-nblk // s) + 1 <= 1024
+    # with few (sequence, head) pairs and a history that does not need more CTAs than there are SMs (a CTA
+    # takes at most 512 records) the launch is one wave: history CTAs + ring CTAs of 64 tokens <= SMs
+    ring_ctas = (ring + 63) // 64
+    if -(-nblk // 512) <= sms // (batch * h) - ring_ctas and nblk >= 12 * s:
+        assert batch * h * (s + ring_ctas) <= sms
+
+
+def test_config1_split_is_five_record_rounds_per_warp():
+    s = E.choose_splits(1, 4, 32768, 148, 128)
+    assert s == 35                                    # 37 slots per head: 35 history + 2 ring CTAs
+    assert -(-2048 // s) <= 5 * 12                    # at most five records per warp of a 12-warp CTA
