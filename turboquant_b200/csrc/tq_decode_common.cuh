@@ -208,10 +208,11 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
     __shared__ __align__(8) uint64_t s_bar;
     __syncthreads();          // every thread's part of the partial is written ...
     if (tid == 0) {
-        __threadfence();      // ... and, the fence being cumulative, visible device-wide before the ticket
-        const int t = atomicAdd(p.tickets + b * p.H + h, 1);
+        // ... and, release being cumulative, visible device-wide before the ticket; the acquire half orders
+        // the last CTA's reads of the other partials behind it
+        int t;
+        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(t) : "l"(p.tickets + b * p.H + h) : "memory");
         s_last = (t == nslot - 1);
-        if (s_last) __threadfence();
     }
     __syncthreads();
     if (!s_last) return;
@@ -248,6 +249,7 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
             float mx = -INFINITY;
             for (int s = lane; s < nslot; s += 32) mx = fmaxf(mx, sb[s * PS + g]);
             mx = tq_warp_max(mx);
+            TQ_STAMP(14);
             const float4* src = reinterpret_cast<const float4*>(sb + 2 * GP + g * D + d);
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
             float l = 0.f;
@@ -271,6 +273,7 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
                     o.w = fmaf(ws, v.w, o.w);
                 }
             }
+            TQ_STAMP(15);
             const float inv = l > 0.f ? 1.f / l : 0.f;
             const int64_t dst = ((int64_t)b * p.Qh + h * p.G + g) * D + d;
             tq_store4_any(p.out, dst, o.x * inv, o.y * inv, o.z * inv, o.w * inv, p.q_dtype);

@@ -123,7 +123,8 @@ def main() -> None:
         blk = t[hh * nslot:(hh + 1) * nslot]
         i = int(np.argmax(blk[:, 6]))
         print(f"  kv head {hh}: merged by CTA {i}: partial written {(blk[i, 5] - t0) / 1e3:6.2f}, ticket known "
-              f"{(blk[i, 7] - t0) / 1e3:6.2f}, partials landed {(blk[i, 13] - t0) / 1e3:6.2f}, output written "
+              f"{(blk[i, 7] - t0) / 1e3:6.2f}, partials landed {(blk[i, 13] - t0) / 1e3:6.2f}, max known "
+              f"{(blk[i, 14] - t0) / 1e3:6.2f}, slots summed {(blk[i, 15] - t0) / 1e3:6.2f}, output written "
               f"{(blk[i, 6] - t0) / 1e3:6.2f}")
     print(f"  launch span {(t[:, 6].max() - t0) / 1e3:6.2f} us")
     sys.stdout.flush()
