@@ -237,12 +237,14 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
             return;
         }
         TQ_STAMP(13);
-        // Out of shared memory: a thread owns four channels of one head; the head is the same for a
-        // whole warp, so the warp works out the slots' weights once - lane s takes slots s, s+32, ... -
-        // and hands them round by shuffle while every lane accumulates its channels.
+        // Out of shared memory: a thread owns four channels of one head; the head is the same for a whole
+        // warp, so the warp works out the slots' weights once into its own row of `wsm` (padded with
+        // zeros to a multiple of eight) and then takes the slots eight at a time, all loads first.
         const float* sb = reinterpret_cast<const float*>(land);
         const int lane = tid & 31;
         const int items = p.G * (D / 4);
+        const int wstride = (nslot + 7) & ~7;
+        float* ww = wsm + (tid >> 5) * wstride;   // tensor-core kernel: wsm holds one row of max(nslot,128) + 8 floats per warp
         for (int i0 = (tid >> 5) * 32; i0 < items; i0 += nt) {   // D/4 is a multiple of 32: one head per warp pass
             const int i = i0 + lane;
             const int g = i0 / (D / 4), d = (i % (D / 4)) * 4;
@@ -250,29 +252,37 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
             for (int s = lane; s < nslot; s += 32) mx = fmaxf(mx, sb[s * PS + g]);
             mx = tq_warp_max(mx);
             TQ_STAMP(14);
+            float l = 0.f;
+            for (int s = lane; s < wstride; s += 32) {
+                float wm = 0.f;
+                if (s < nslot) {
+                    const float ms = sb[s * PS + g];
+                    wm = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
+                    l = fmaf(wm, sb[s * PS + GP + g], l);
+                }
+                ww[s] = wm;
+            }
+            l = tq_warp_sum(l);
+            __syncwarp();
             const float4* src = reinterpret_cast<const float4*>(sb + 2 * GP + g * D + d);
             float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
-            float l = 0.f;
-            for (int s0 = 0; s0 < nslot; s0 += 32) {
-                const int sm = s0 + lane;
-                float wm = 0.f, wl = 0.f;     // this lane's slot: weight, weight * sum
-                if (sm < nslot) {
-                    const float ms = sb[sm * PS + g];
-                    wm = (ms == -INFINITY) ? 0.f : __expf(ms - mx);
-                    wl = wm * sb[sm * PS + GP + g];
+            for (int s = 0; s < nslot; s += 8) {
+                float4 v[8];
+                float w8[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    v[u] = src[min(s + u, nslot - 1) * (PS / 4)];   // past the end: a valid slot, weight 0
+                    w8[u] = ww[s + u];
                 }
-                l += tq_warp_sum(wl);
-                const int cnt = min(32, nslot - s0);
-#pragma unroll 4
-                for (int k = 0; k < cnt; ++k) {
-                    const float ws = __shfl_sync(0xffffffffu, wm, k);
-                    const float4 v = src[(s0 + k) * (PS / 4)];
-                    o.x = fmaf(ws, v.x, o.x);
-                    o.y = fmaf(ws, v.y, o.y);
-                    o.z = fmaf(ws, v.z, o.z);
-                    o.w = fmaf(ws, v.w, o.w);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    o.x = fmaf(w8[u], v[u].x, o.x);
+                    o.y = fmaf(w8[u], v[u].y, o.y);
+                    o.z = fmaf(w8[u], v[u].z, o.z);
+                    o.w = fmaf(w8[u], v[u].w, o.w);
                 }
             }
+            __syncwarp();   // the row of weights is rewritten by the warp's next pass
             TQ_STAMP(15);
             const float inv = l > 0.f ? 1.f / l : 0.f;
             const int64_t dst = ((int64_t)b * p.Qh + h * p.G + g) * D + d;

@@ -651,7 +651,8 @@ size_t mma_smem_bytes(int block_bytes, int nslot) {
     constexpr int GP = SPLITB ? 8 : 4;
     size_t s = mma_land_bytes<D, SPLITB, NW>(block_bytes, nslot);
     s += sizeof(uint64_t) * (NW * NSTW + 2) + sizeof(uint32_t) * qf_words(D, SPLITB ? 8 : 4);
-    s += sizeof(float) * ((size_t)(nslot > 128 ? nslot : 128) * GP + 2 * GP);
+    // merge scratch: one row of slot weights per warp of the merging CTA
+    s += sizeof(float) * ((size_t)((nslot > 128 ? nslot : 128) + 8) * NW + 2 * GP);
     return s;
 }
 
