@@ -76,6 +76,17 @@ def gather_head_outputs(local_out: torch.Tensor, shard: Shard, num_seqs: int, nu
         out.copy_(local_out)
         return out
     shards = [partition(num_seqs, num_kv_heads, world, r) for r in range(world)]
+    rows = shards[0].num_seqs
+    if all(s.num_seqs == rows for s in shards):
+        # even split (the usual case): gather straight from the caller's slab and place all slabs
+        # with one strided copy - rank = head_slot * seq_ways + seq_slot
+        head_ways = min(world, num_kv_heads)
+        seq_ways = world // head_ways
+        hg = local_out.shape[1]
+        flat = _gather_buffer((world, rows, hg, d), local_out.dtype, local_out.device)
+        dist.all_gather_into_tensor(flat.view(world * rows, hg, d), local_out.contiguous(), group=group)
+        out.view(seq_ways, rows, head_ways, hg, d).copy_(flat.view(head_ways, seq_ways, rows, hg, d).permute(1, 2, 0, 3, 4))
+        return out
     max_rows = max(s.num_seqs for s in shards)
     send = torch.zeros(max_rows, local_out.shape[1], d, dtype=local_out.dtype, device=local_out.device)
     send[: shard.num_seqs].copy_(local_out)
@@ -85,6 +96,18 @@ def gather_head_outputs(local_out: torch.Tensor, shard: Shard, num_seqs: int, nu
     for s in shards:
         out[s.seq0:s.seq1, s.head0 * g_heads:s.head1 * g_heads].copy_(recv[s.rank, : s.num_seqs])
     return out
+
+
+_GATHER_BUFFERS: dict = {}
+
+
+def _gather_buffer(shape, dtype, device) -> torch.Tensor:
+    """Receive buffer of the all-gather, kept between calls (one per shape)."""
+    key = (tuple(shape), dtype, str(device))
+    buf = _GATHER_BUFFERS.get(key)
+    if buf is None:
+        buf = _GATHER_BUFFERS[key] = torch.empty(shape, dtype=dtype, device=device)
+    return buf
 
 
 def reduce_timing(local_ms: float, local_units: float, device, group=None) -> tuple[float, float]:
