@@ -39,8 +39,9 @@ struct RingAppend {
                         // read them before waiting for the kernel ahead (their latency hides under it)
 };
 
-template <int D>
-__global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ q, int dt, int64_t nvec,
+// VPC = query vectors per CTA.
+template <int D, int VPC>
+__global__ void __launch_bounds__(256, 2) tq_qprep_kernel(const void* __restrict__ q, int dt, int64_t nvec,
                                                        const float* __restrict__ pi_t,
                                                        const float* __restrict__ s_t, float* __restrict__ out,
                                                        uint32_t* __restrict__ frag, int G, int Qh, int mse_bits,
@@ -53,11 +54,11 @@ __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ 
 #define TQ_QSTAMP(i)
 #endif
     TQ_QSTAMP(0);
-    __shared__ float qsm[4 * D];          // queries
-    __shared__ float red[8 * 4 * 32];     // partial sums
-    __shared__ float qn2[4];              // squared norms
-    const int64_t v0 = (int64_t)blockIdx.y * 4;
-    const int nv = (int)min((int64_t)4, nvec - v0);
+    __shared__ float qsm[VPC * D];          // queries
+    __shared__ float red[8 * VPC * 32];     // partial sums
+    __shared__ float qn2[VPC];              // squared norms
+    const int64_t v0 = (int64_t)blockIdx.y * VPC;
+    const int nv = (int)min((int64_t)VPC, nvec - v0);
     constexpr int chunks = D / 32;
     const int which = blockIdx.x / chunks;            // 0: Pi^T, 1: S^T
     const int chunk = blockIdx.x % chunks;
@@ -76,10 +77,10 @@ __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ 
     const int row_bytes = D * ap.elem_bytes, chunks_per_row = row_bytes / 16;
     const int n_app = do_append ? ap.B * ap.H * chunks_per_row : 0;
     uint4 ak = make_uint4(0u, 0u, 0u, 0u), av = ak;   // first append chunk of this thread, when fetched early
-    float qv[4 * D / 256];
+    float qv[VPC * D / 256];
     if (ap.early_inputs) {
 #pragma unroll
-        for (int u = 0; u < 4 * D / 256; ++u) {
+        for (int u = 0; u < VPC * D / 256; ++u) {
             const int i = threadIdx.x + u * 256, v = i / D;
             qv[u] = v < nv ? tq_load_any(q, (v0 + v) * D + (i % D), dt) : 0.f;
         }
@@ -121,34 +122,36 @@ __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ 
     }
     if (ap.early_inputs) {
 #pragma unroll
-        for (int u = 0; u < 4 * D / 256; ++u) qsm[threadIdx.x + u * 256] = qv[u];
+        for (int u = 0; u < VPC * D / 256; ++u) qsm[threadIdx.x + u * 256] = qv[u];
     } else {
-        for (int i = threadIdx.x; i < 4 * D; i += 256) {
+        for (int i = threadIdx.x; i < VPC * D; i += 256) {
             const int v = i / D;
             qsm[i] = v < nv ? tq_load_any(q, (v0 + v) * D + (i % D), dt) : 0.f;
         }
     }
     __syncthreads();
-    if (ks < 4) {
+    if (ks < VPC) {
         float s2 = 0.f;
         for (int j = lane; j < D; j += 32) s2 = fmaf(qsm[ks * D + j], qsm[ks * D + j], s2);
         s2 = tq_warp_sum(s2);
         if (lane == 0) qn2[ks] = s2;
     }
-    float a[4] = {0.f, 0.f, 0.f, 0.f};
+    float a[VPC];
+#pragma unroll
+    for (int v = 0; v < VPC; ++v) a[v] = 0.f;
 #pragma unroll
     for (int k = 0; k < D / 8; ++k) {
 #pragma unroll
-        for (int v = 0; v < 4; ++v) a[v] = fmaf(qsm[v * D + k0 + k], mv[k], a[v]);
+        for (int v = 0; v < VPC; ++v) a[v] = fmaf(qsm[v * D + k0 + k], mv[k], a[v]);
     }
 #pragma unroll
-    for (int v = 0; v < 4; ++v) red[(ks * 4 + v) * 32 + lane] = a[v];
+    for (int v = 0; v < VPC; ++v) red[(ks * VPC + v) * 32 + lane] = a[v];
     __syncthreads();
-    if (threadIdx.x < 128) {
+    if (threadIdx.x < VPC * 32) {
         const int v = threadIdx.x >> 5;
         float t = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) t += red[(i * 4 + v) * 32 + lane];
+        for (int i = 0; i < 8; ++i) t += red[(i * VPC + v) * 32 + lane];
         if (v < nv) {
             if (live) out[((v0 + v) * 2 + which) * D + col] = t;
             if (frag != nullptr) {
@@ -186,7 +189,10 @@ __global__ void __launch_bounds__(256) tq_qprep_kernel(const void* __restrict__ 
 int launch_qprep(const void* q, int dt, int64_t nvec, int D, const float* pi_t, const float* s_t, float* out,
                  uint32_t* frag, int G, int Qh, int mse_bits, const RingAppend& ap, cudaStream_t st) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(2 * D / 32), (unsigned)((nvec + 3) / 4));
+    // four vectors per CTA: with eight the grid packs four CTAs onto each of the few SMs that free up first
+    // under a running decode kernel, and they then share one SM for the part after the wait (measured: slower)
+    constexpr int vpc = 4;
+    cfg.gridDim = dim3((unsigned)(2 * D / 32), (unsigned)((nvec + vpc - 1) / vpc));
     cfg.blockDim = dim3(256);
     cfg.dynamicSmemBytes = 0;
     cfg.stream = st;
@@ -198,9 +204,9 @@ int launch_qprep(const void* q, int dt, int64_t nvec, int D, const float* pi_t, 
     const int dti = dt;
     cudaError_t e;
     if (D == 128)
-        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<128>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
+        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<128, vpc>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
     else
-        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<256>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
+        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<256, vpc>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
     return e == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 

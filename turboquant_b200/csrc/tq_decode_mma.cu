@@ -106,7 +106,10 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int gid = lane >> 2, tig = lane & 3;
-    const int b = blockIdx.z, h = blockIdx.y, x = blockIdx.x;
+    // kv head fastest, slot next: the ring slots (x >= num_splits) are the last CTAs of a sequence in launch
+    // order.  When this grid starts under the tail of the previous kernels, the CTAs that find their SM still
+    // taken by the query preparation are then ring CTAs, which are off the critical path.
+    const int b = blockIdx.z, h = blockIdx.x, x = blockIdx.y;
     TQ_STAMP(0);
     // a kernel launched behind this one with programmatic stream serialisation may be scheduled as soon
     // as every CTA of this grid is running; whatever it reads of ours it reads after its own wait
@@ -682,7 +685,7 @@ int launch_mma_nw(const DecodeParams& p_in, int batch, cudaStream_t st) {
         smem_set = smem;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)nslot, (unsigned)p.H, (unsigned)batch);
+    cfg.gridDim = dim3((unsigned)p.H, (unsigned)nslot, (unsigned)batch);
     cfg.blockDim = dim3(NT);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;

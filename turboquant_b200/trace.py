@@ -106,7 +106,7 @@ def main() -> None:
     # the library alternates between two trace slots per launch; the last launch's slot holds the newest stamps
     slots = buf.reshape(2, 2048, 16)[:, :ncta].astype(np.int64)
     t = slots[int(np.argmax([s[:, 0].min() for s in slots]))]
-    x = np.arange(ncta) % nslot
+    x = np.arange(ncta) // h            # CTA index = kv head + H * slot
     hist, rg = t[x < splits], t[x >= splits]
     t0 = t[:, 0].min()
 
@@ -120,7 +120,7 @@ def main() -> None:
     if len(rg):
         print(f"  {'ring CTAs: partial written':30s} {fmt(rg[:, 5] - t0)}")
     for hh in range(h):
-        blk = t[hh * nslot:(hh + 1) * nslot]
+        blk = t[hh::h]
         i = int(np.argmax(blk[:, 6]))
         print(f"  kv head {hh}: merged by CTA {i}: partial written {(blk[i, 5] - t0) / 1e3:6.2f}, ticket known "
               f"{(blk[i, 7] - t0) / 1e3:6.2f}, partials landed {(blk[i, 13] - t0) / 1e3:6.2f}, max known "
