@@ -498,6 +498,57 @@ def test_batched_paged_decode_many_ctas(d, h, qh, kb, vb, dev):
         assert _cos(a[s:s + 1], ref) >= COS_MIN, (s, _cos(a[s:s + 1], ref))
 
 
+@pytest.mark.parametrize("seed", range(16))
+def test_random_shapes_tensor_core_vs_cuda_core(seed, dev):
+    """Seeded random shapes - head_dim, group size (also odd), bit widths, ragged lengths around
+    block and split boundaries, ring lengths around the 32/64-token slices, shuffled block tables,
+    any split count: the tensor-core kernel against the fp32 CUDA-core kernel on the same pool."""
+    from turboquant_b200 import _engine as E
+    g = torch.Generator().manual_seed(1000 + seed)
+    ri = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g))
+    d = (128, 256)[ri(0, 1)]
+    kb, vb = (3, 4)[ri(0, 1)], (2, 4)[ri(0, 1)]
+    h = ri(1, 4)
+    grp = ri(1, 8)
+    qh = h * grp
+    nseq = ri(1, 6)
+    nmax = (ri(16, 400), ri(900, 2600))[ri(0, 1)]
+    lens_l = [max(1, nmax - ri(0, 40) * ri(0, 1) * 7) for _ in range(nseq)]
+    lens_l[0] = nmax
+    if nseq > 1:
+        lens_l[-1] = ri(1, 17)                       # around the 16-token minimum
+    per = (nmax + 15) // 16
+    c = E.LayerConstants(d, kb, vb, dev, seed=5 + seed)
+    k, v = O.synth_kv(nmax + 80, h, d, seed=77 + seed, dtype=torch.bfloat16)
+    perm = torch.randperm(nseq * per, generator=g).to(torch.int32)
+    bt = perm.view(nseq, per).to(dev)
+    pool = E.BlockPool(c, h, nseq * per)
+    for s_ in range(nseq):
+        n = lens_l[s_]
+        E.store(c, pool, k[:n].to(dev).contiguous(), v[:n].to(dev).contiguous(), stride_token=h * d, stride_head=d,
+                n_tokens=n, n_heads=h, block_table=bt[s_], start_pos=0)
+    lens = torch.tensor(lens_l, dtype=torch.int32, device=dev)
+    q = O.synth_query(nseq, qh, d, seed=3 + seed, dtype=torch.bfloat16).to(dev)
+    rmax = (0, 1, 31, 33, 64, 65, 80)[ri(0, 6)]
+    kw = {}
+    if rmax > 0:
+        rk = k[nmax:nmax + rmax].to(dev).contiguous().unsqueeze(0).expand(nseq, -1, -1, -1).contiguous()
+        rv = v[nmax:nmax + rmax].to(dev).contiguous().unsqueeze(0).expand(nseq, -1, -1, -1).contiguous()
+        rl = torch.tensor([max(0, rmax - 3 * s_) for s_ in range(nseq)], dtype=torch.int32, device=dev)
+        kw = dict(ring_k=rk, ring_v=rv, ring_lens=rl, max_ring_len=rmax, ring_stride_seq=rmax * h * d,
+                  ring_stride_token=h * d)
+    ws = E.Workspace(dev)
+    splits = (0, 1, 2, 5)[ri(0, 3)]
+    if splits == 0:
+        splits = E.choose_splits(nseq, h, nmax, E.sm_count(dev), rmax)
+    a = E.decode(c, pool, ws, q, bt, lens, nmax, num_splits=splits, kernel=0, **kw).float()
+    b = E.decode(c, pool, ws, q, bt, lens, nmax, num_splits=splits, kernel=1, **kw).float()
+    assert ws.status() == 0
+    assert torch.isfinite(a).all() and torch.isfinite(b).all()
+    assert _cos(a, b) >= 0.9999, (d, kb, vb, h, grp, nseq, nmax, rmax, splits, _cos(a, b))
+    torch.testing.assert_close(a, b, rtol=3e-2, atol=3e-3)
+
+
 @pytest.mark.parametrize("kb,vb,h,n", [(3, 2, 8, 8192), (4, 4, 4, 3000), (3, 4, 2, 129), (4, 2, 1, 16), (3, 2, 3, 2047)])
 def test_tensor_core_store_matches_fp32_store_and_oracle(kb, vb, h, n, dev):
     """tcgen05 store kernel (head_dim 128, bf16, block-aligned start) against the fp32 store
