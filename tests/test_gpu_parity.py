@@ -215,7 +215,7 @@ def test_ragged_lengths(n, dev):
 
 @pytest.mark.parametrize("d,h,qh,kb,vb,n", [(128, 8, 32, 3, 2, 4096), (256, 4, 16, 3, 2, 3000),
                                             (128, 8, 32, 4, 4, 2500), (128, 8, 64, 3, 2, 1500),
-                                            (256, 2, 2, 4, 2, 700)])
+                                            (256, 2, 2, 4, 2, 700), (256, 4, 24, 3, 2, 2000), (256, 2, 16, 4, 4, 1100)])
 def test_store_and_decode_vs_oracle(d, h, qh, kb, vb, n, dev):
     from turboquant_b200 import CompressedKVStore, compute_hybrid_attention
     dtype = torch.float32 if (d, kb, vb, qh) == (128, 3, 2, 32) else torch.bfloat16
@@ -420,7 +420,11 @@ def test_errors_are_loud(dev):
 
 @pytest.mark.parametrize("d,h,qh,vb,n,kb", [(256, 4, 16, 2, 5000, 3), (128, 8, 32, 2, 3000, 3), (128, 8, 32, 4, 2000, 3),
                                             (128, 4, 32, 2, 2500, 3), (256, 2, 6, 4, 1111, 3), (128, 2, 14, 4, 999, 3),
-                                            (128, 8, 32, 4, 2100, 4), (128, 2, 16, 2, 777, 4), (128, 4, 4, 4, 1500, 4)])
+                                            (128, 8, 32, 4, 2100, 4), (128, 2, 16, 2, 777, 4), (128, 4, 4, 4, 1500, 4),
+                                            # head_dim 256 with more than four heads per kv head / 3-bit codes:
+                                            # query fragments stay in shared memory
+                                            (256, 4, 24, 2, 3000, 3), (256, 2, 16, 4, 1500, 3), (256, 2, 8, 2, 1200, 4),
+                                            (256, 4, 16, 4, 900, 4), (256, 1, 7, 2, 640, 4)])
 def test_tensor_core_kernel_matches_cuda_core_kernel(d, h, qh, vb, n, kb, dev):
     """The two decode kernels on the same pool, same splits: the tensor-core one
     (fp16 operands) against the fp32 CUDA-core one, with and without a ring."""

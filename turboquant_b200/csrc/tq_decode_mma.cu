@@ -190,18 +190,29 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
     TQ_STAMP(2);
     bool failed = !__all_sync(0xffffffffu, tq_mbar_wait_bounded(bars + NW * NSTW, 0u));   // then no record is processed
     TQ_STAMP(12);
-    uint32_t bq[2 * KS];
-    uint32_t bsk[SPLITB ? 2 * KS : 1];
+    // Head_dim 256 with separate rotated / sketched sets: two sets of 32 fragment registers do not fit beside
+    // the 64 value accumulators, so the fragments stay in shared memory and are read where they are used.
+    constexpr bool BSM = (D == 256) && SPLITB;
+    uint32_t bq[BSM ? 1 : 2 * KS];
+    uint32_t bsk[(SPLITB && !BSM) ? 2 * KS : 1];
+#define BQ(r) (BSM ? qf_s[QF_HDR + (r) * 32 + lane] : bq[BSM ? 0 : (r)])
+#define BSK(r) (BSM ? qf_s[QF_HDR + (2 * KS + (r)) * 32 + lane] : bsk[(SPLITB && !BSM) ? (r) : 0])
     float k0[2], k1[2], kb0[2], ksg[2], kq[2];
     {
         const uint32_t* qf = qf_s;
         const float* hdr = reinterpret_cast<const float*>(qf);
         const int g_col = SPLITB ? gid : (gid & 3);             // head of this thread's B-fragment column
         const bool col_live = g_col < p.G;
+        if (BSM) {
+            if (!col_live)   // columns without a head: nobody wrote their fragments - clear this lane's words
+                for (int r = 0; r < 4 * KS; ++r) qf_s[QF_HDR + r * 32 + lane] = 0u;
+            __syncwarp();
+        } else {
 #pragma unroll
-        for (int r = 0; r < 2 * KS; ++r) {
-            bq[r] = col_live ? qf[QF_HDR + r * 32 + lane] : 0u;
-            if (SPLITB) bsk[r] = col_live ? qf[QF_HDR + (2 * KS + r) * 32 + lane] : 0u;
+            for (int r = 0; r < 2 * KS; ++r) {
+                bq[BSM ? 0 : r] = col_live ? qf[QF_HDR + r * 32 + lane] : 0u;
+                if (SPLITB) bsk[(SPLITB && !BSM) ? r : 0] = col_live ? qf[QF_HDR + (2 * KS + r) * 32 + lane] : 0u;
+            }
         }
         TQ_STAMP(11);
         // Sums of the fp16-rounded query over all dims (the constant terms of the bit-plane form), taken
@@ -215,12 +226,12 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
             const int wi = s >> 2, jj = s & 3;
             if (MSE_BITS == 2) {
                 const uint32_t m0 = 0x00010001u << (2 * code_pos(2 * jj)), m1 = 0x00010001u << (2 * code_pos(2 * jj + 1));
-                mma16816((s & 1) ? one_c2 : one_c, m0, m0, m1, m1, bq[2 * s], bq[2 * s + 1]);
+                mma16816((s & 1) ? one_c2 : one_c, m0, m0, m1, m1, BQ(2 * s), BQ(2 * s + 1));
             }
             const uint32_t n0 = 0x00010001u << sign_pos(sign_bit(wi, 2 * jj));
             const uint32_t n1 = 0x00010001u << sign_pos(sign_bit(wi, 2 * jj + 1));
-            mma16816((s & 1) ? one_s2 : one_s, n0, n0, n1, n1, SPLITB ? bsk[SPLITB ? 2 * s : 0] : bq[2 * s],
-                     SPLITB ? bsk[SPLITB ? 2 * s + 1 : 0] : bq[2 * s + 1]);
+            mma16816((s & 1) ? one_s2 : one_s, n0, n0, n1, n1, SPLITB ? BSK(2 * s) : BQ(2 * s),
+                     SPLITB ? BSK(2 * s + 1) : BQ(2 * s + 1));
         }
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
@@ -340,25 +351,25 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
                     const uint32_t xa0 = j0 <= 4 ? a_lo : a_hi, xb0 = j0 <= 4 ? b_lo : b_hi;
                     const uint32_t xa1 = j1 <= 4 ? a_lo : a_hi, xb1 = j1 <= 4 ? b_lo : b_hi;
                     if (s == 0) {
-                        mma16816_z(acc0, xa0 & m0, xb0 & m0, xa1 & m1, xb1 & m1, bq[2 * s], bq[2 * s + 1]);
-                        mma16816_z(acc1, xa0 & (m0 << 1), xb0 & (m0 << 1), xa1 & (m1 << 1), xb1 & (m1 << 1), bq[2 * s],
-                                   bq[2 * s + 1]);
+                        mma16816_z(acc0, xa0 & m0, xb0 & m0, xa1 & m1, xb1 & m1, BQ(2 * s), BQ(2 * s + 1));
+                        mma16816_z(acc1, xa0 & (m0 << 1), xb0 & (m0 << 1), xa1 & (m1 << 1), xb1 & (m1 << 1), BQ(2 * s),
+                                   BQ(2 * s + 1));
                     } else {
-                        mma16816(acc0, xa0 & m0, xb0 & m0, xa1 & m1, xb1 & m1, bq[2 * s], bq[2 * s + 1]);
-                        mma16816(acc1, xa0 & (m0 << 1), xb0 & (m0 << 1), xa1 & (m1 << 1), xb1 & (m1 << 1), bq[2 * s],
-                                 bq[2 * s + 1]);
+                        mma16816(acc0, xa0 & m0, xb0 & m0, xa1 & m1, xb1 & m1, BQ(2 * s), BQ(2 * s + 1));
+                        mma16816(acc1, xa0 & (m0 << 1), xb0 & (m0 << 1), xa1 & (m1 << 1), xb1 & (m1 << 1), BQ(2 * s),
+                                 BQ(2 * s + 1));
                     }
                     const int sb0 = sign_bit(wi, j0), sb1 = sign_bit(wi, j1);
                     const uint32_t n0 = 0x00010001u << sign_pos(sb0), n1 = 0x00010001u << sign_pos(sb1);
                     const uint32_t ya0 = sb0 <= 9 ? sa_lo : sa_hi, yb0 = sb0 <= 9 ? sb_lo : sb_hi;
                     const uint32_t ya1 = sb1 <= 9 ? sa_lo : sa_hi, yb1 = sb1 <= 9 ? sb_lo : sb_hi;
                     if (s == 0)
-                        mma16816_z(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, SPLITB ? bsk[0] : bq[0],
-                                   SPLITB ? bsk[1] : bq[1]);
+                        mma16816_z(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, SPLITB ? BSK(0) : BQ(0),
+                                   SPLITB ? BSK(1) : BQ(1));
                     else if (SPLITB)
-                        mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, bsk[2 * s], bsk[2 * s + 1]);
+                        mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, BSK(2 * s), BSK(2 * s + 1));
                     else
-                        mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, bq[2 * s], bq[2 * s + 1]);
+                        mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, BQ(2 * s), BQ(2 * s + 1));
                 }
             }
         }
@@ -384,10 +395,10 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
                         const uint32_t lb = __byte_perm(t_lo0, t_lo1, sb), hb = __byte_perm(t_hi0, t_hi1, sb);
                         if (s == 0)
                             mma16816_z(acc0, __byte_perm(la, ha, 0x5140), __byte_perm(lb, hb, 0x5140),
-                                       __byte_perm(la, ha, 0x7362), __byte_perm(lb, hb, 0x7362), bq[0], bq[1]);
+                                       __byte_perm(la, ha, 0x7362), __byte_perm(lb, hb, 0x7362), BQ(0), BQ(1));
                         else
                             mma16816(acc0, __byte_perm(la, ha, 0x5140), __byte_perm(lb, hb, 0x5140),
-                                     __byte_perm(la, ha, 0x7362), __byte_perm(lb, hb, 0x7362), bq[2 * s], bq[2 * s + 1]);
+                                     __byte_perm(la, ha, 0x7362), __byte_perm(lb, hb, 0x7362), BQ(2 * s), BQ(2 * s + 1));
                     }
                 }
             }
@@ -405,10 +416,10 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
                         const uint32_t ya0 = sb0 <= 9 ? sa_lo : sa_hi, yb0 = sb0 <= 9 ? sb_lo : sb_hi;
                         const uint32_t ya1 = sb1 <= 9 ? sa_lo : sa_hi, yb1 = sb1 <= 9 ? sb_lo : sb_hi;
                         if (s == 0)
-                            mma16816_z(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, bsk[0], bsk[SPLITB ? 1 : 0]);
+                            mma16816_z(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, BSK(0), BSK(1));
                         else
-                            mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, bsk[SPLITB ? 2 * s : 0],
-                                     bsk[SPLITB ? 2 * s + 1 : 0]);
+                            mma16816(accs, ya0 & n0, yb0 & n0, ya1 & n1, yb1 & n1, BSK(2 * s),
+                                     BSK(2 * s + 1));
                     }
                 }
             }
@@ -697,13 +708,23 @@ int launch_mma_nw(const DecodeParams& p_in, int batch, cudaStream_t st) {
     return cudaLaunchKernelEx(&cfg, kern, p) == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 
+constexpr size_t SMEM_PER_CTA_MAX = 227 * 1024;
+
+// *handled = 0 when not even the 8-warp CTA's stages fit shared memory (the caller then runs the CUDA-core kernel)
 template <int D, int MSE_BITS, int VAL_BITS, bool SPLITB>
-int launch_mma(const DecodeParams& p, int batch, cudaStream_t st) {
-    const int64_t ctas = (int64_t)(p.num_splits + p.ring_splits) * p.H * batch;
+int launch_mma(const DecodeParams& p, int batch, cudaStream_t st, int* handled) {
+    const TqLayout L = tq_make_layout(D, MSE_BITS + 1, VAL_BITS);
+    const int nslot = p.num_splits + p.ring_splits;
+    const int64_t ctas = (int64_t)nslot * p.H * batch;
+    const bool fits_wave = mma_smem_bytes<D, SPLITB, NW_WAVE>(L.block_bytes, nslot) <= SMEM_PER_CTA_MAX;
+    const bool fits_multi = mma_smem_bytes<D, SPLITB, NW_MULTI>(L.block_bytes, nslot) <= SMEM_PER_CTA_MAX;
+    *handled = 1;
     // two 8-warp CTAs per SM need two merge scratch areas in shared memory: only with few slots
-    if (ctas > sm_count_cached() && p.num_splits + p.ring_splits <= 128)
+    if (fits_multi && ((ctas > sm_count_cached() && nslot <= 128) || !fits_wave))
         return launch_mma_nw<D, MSE_BITS, VAL_BITS, SPLITB, NW_MULTI>(p, batch, st);
-    return launch_mma_nw<D, MSE_BITS, VAL_BITS, SPLITB, NW_WAVE>(p, batch, st);
+    if (fits_wave) return launch_mma_nw<D, MSE_BITS, VAL_BITS, SPLITB, NW_WAVE>(p, batch, st);
+    *handled = 0;
+    return TQ_OK;
 }
 
 }  // namespace
@@ -723,24 +744,23 @@ int tq_decode_mma_launch(const DecodeParams& p, int D, int mse_bits, int val_bit
     if ((nblk + p.num_splits - 1) / p.num_splits + 1 > BT_MAX) return TQ_OK;   // block-table slice kept in shared memory
     if ((int64_t)(p.num_splits + 1) * nblk >= (int64_t)1 << 31) return TQ_OK;   // 32-bit split arithmetic in the kernel
     if (mse_bits == 3) {
-        if (D != 128) return TQ_OK;                  // two fragment sets of 32 registers do not fit at 256
-        *handled = 1;
-        return val_bits == 2 ? launch_mma<128, 3, 2, true>(p, batch, st) : launch_mma<128, 3, 4, true>(p, batch, st);
+        if (D == 128)
+            return val_bits == 2 ? launch_mma<128, 3, 2, true>(p, batch, st, handled) : launch_mma<128, 3, 4, true>(p, batch, st, handled);
+        return val_bits == 2 ? launch_mma<256, 3, 2, true>(p, batch, st, handled) : launch_mma<256, 3, 4, true>(p, batch, st, handled);
     }
     if (mse_bits != 2) return TQ_OK;
-    if (D == 256 && p.G > 4) return TQ_OK;           // would need two B-fragment sets of 32 registers
     // the bit-plane form needs a code book that is affine in the two code bits
     const float* c = p.cb.centroids;
     if (fabsf(c[3] - c[2] - c[1] + c[0]) > 1e-6f * fabsf(c[3] - c[0])) return TQ_OK;
-    *handled = 1;
     const bool split = p.G > 4;
     if (D == 128) {
         if (val_bits == 2)
-            return split ? launch_mma<128, 2, 2, true>(p, batch, st) : launch_mma<128, 2, 2, false>(p, batch, st);
-        return split ? launch_mma<128, 2, 4, true>(p, batch, st) : launch_mma<128, 2, 4, false>(p, batch, st);
+            return split ? launch_mma<128, 2, 2, true>(p, batch, st, handled) : launch_mma<128, 2, 2, false>(p, batch, st, handled);
+        return split ? launch_mma<128, 2, 4, true>(p, batch, st, handled) : launch_mma<128, 2, 4, false>(p, batch, st, handled);
     }
-    if (val_bits == 2) return launch_mma<256, 2, 2, false>(p, batch, st);
-    return launch_mma<256, 2, 4, false>(p, batch, st);
+    if (val_bits == 2)
+        return split ? launch_mma<256, 2, 2, true>(p, batch, st, handled) : launch_mma<256, 2, 2, false>(p, batch, st, handled);
+    return split ? launch_mma<256, 2, 4, true>(p, batch, st, handled) : launch_mma<256, 2, 4, false>(p, batch, st, handled);
 }
 
 }  // namespace tqdec
