@@ -39,9 +39,10 @@ struct RingAppend {
                         // read them before waiting for the kernel ahead (their latency hides under it)
 };
 
-// VPC = query vectors per CTA.
-template <int D, int VPC>
-__global__ void __launch_bounds__(256, 2) tq_qprep_kernel(const void* __restrict__ q, int dt, int64_t nvec,
+// VPC = query vectors per CTA; OCC = CTAs per SM the registers are budgeted for (2 for a grid that is resident
+// all at once - fewer CTAs share an SM for the latency-critical part after the wait - 3 for throughput).
+template <int D, int VPC, int OCC>
+__global__ void __launch_bounds__(256, OCC) tq_qprep_kernel(const void* __restrict__ q, int dt, int64_t nvec,
                                                        const float* __restrict__ pi_t,
                                                        const float* __restrict__ s_t, float* __restrict__ out,
                                                        uint32_t* __restrict__ frag, int G, int Qh, int mse_bits,
@@ -96,8 +97,9 @@ __global__ void __launch_bounds__(256, 2) tq_qprep_kernel(const void* __restrict
     // otherwise sit waiting for the kernel ahead of it: it computes on whatever the query buffer holds
     // and stores nothing outside shared memory, but it pulls the code of the second pass - which is on
     // the critical path of every decode step - into the instruction cache.
+    // (only a grid small enough to be resident all at once rehearses: a larger one has no idle wait to fill)
 #pragma unroll 1
-    for (int pass = 0; pass < 2; ++pass) {
+    for (int pass = (gridDim.x * gridDim.y <= 256u) ? 0 : 1; pass < 2; ++pass) {
     const bool live = pass == 1;
     if (live) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -203,10 +205,15 @@ int launch_qprep(const void* q, int dt, int64_t nvec, int D, const float* pi_t, 
     cfg.numAttrs = 1;
     const int dti = dt;
     cudaError_t e;
-    if (D == 128)
-        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<128, vpc>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
+    const bool small = cfg.gridDim.x * cfg.gridDim.y <= 256u;
+    if (D == 128 && small)
+        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<128, vpc, 2>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
+    else if (D == 128)
+        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<128, vpc, 3>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
+    else if (small)
+        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<256, vpc, 2>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
     else
-        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<256, vpc>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
+        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<256, vpc, 3>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
     return e == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 
