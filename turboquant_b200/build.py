@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(PKG_DIR, "libturboquant_b200.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-    "-shared", "-Xcompiler", "-fPIC",
+    "-shared", "-Xcompiler", "-fPIC", "--threads", "0",      # the .cu files compile in parallel
 ]
 
 
