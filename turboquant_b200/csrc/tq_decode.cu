@@ -571,6 +571,10 @@ static int decode_impl(const tq_consts* consts, const tq_pool* pool, const tq_de
         splits = want < 1 ? 1 : want;
         const int cap = (ntile + 1) / 2;
         if (splits > cap) splits = cap;
+        // at most 512 block records per split: the tensor-core kernel keeps a split's block-table slice in
+        // shared memory, and long and short sequences of a batch balance better
+        const int nblk = (a->max_seq_len + TQ_BLOCK_TOKENS - 1) / TQ_BLOCK_TOKENS;
+        if (splits < (nblk + 511) / 512) splits = (nblk + 511) / 512;
     }
     if (splits < 1) splits = 1;
     if (splits > ntile && ntile > 0) splits = ntile;
