@@ -12,6 +12,8 @@
 // the exact ring tokens.  Every CTA writes a partial (m, l, acc); the last one
 // to finish for a (sequence, kv head) - found with an atomic ticket, no
 // waiting - merges the partials and writes the output.
+#include <mutex>
+
 #include "tq_decode_common.cuh"
 
 using namespace tqdec;
@@ -794,6 +796,8 @@ bool host_ptr_is_mapped(const void* ptr, size_t bytes) {
     static const void* ok_ptr[4] = {nullptr, nullptr, nullptr, nullptr};
     static size_t ok_bytes[4] = {0, 0, 0, 0};
     static int next = 0;
+    static std::mutex mu;                 // callers may come from several host threads
+    std::lock_guard<std::mutex> lock(mu);
     for (int i = 0; i < 4; ++i)
         if (ok_ptr[i] == ptr && ok_bytes[i] >= bytes) return true;
     cudaPointerAttributes at;
