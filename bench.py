@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload (BASELINE config 1): decode attention of one long sequence shaped like a
+Workload: decode attention of one long sequence shaped like a
 hybrid model's full-attention layer - head_dim 256, 4 kv heads, 16 query heads,
 32768 compressed tokens (3-bit keys, 2-bit values), bf16, plus an exact bf16 ring
 of up to 128 recent tokens.  A step = append one new token through the store
@@ -41,9 +41,33 @@ WL = dict(name="config1: decode D=256 Hkv=4 Hq=16 N=32768 ring=128 key3b/val2b b
 METRIC = "decode_attention_kv_tokens_per_s"
 UNIT = "tokens/s"
 N_NEW = 256  # distinct new tokens / queries per layer, reused cyclically
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode launch of this workload, from the ncu capture
-# summarised in profiles/tq_decode_mma_kernel.md (25.94 MB read, 0 written: outputs stay in L2)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 25.94e6
+# Files whose contents decide what the decode kernel reads and writes: the recorded DRAM traffic of a
+# launch is only quoted while they are unchanged since the capture.
+TRAFFIC_RECORD = os.path.join(ROOT, "profiles", "decode_traffic.json")
+TRAFFIC_SOURCES = ("turboquant_b200/csrc/tq_decode_mma.cu", "turboquant_b200/csrc/tq_decode_common.cuh",
+                   "turboquant_b200/csrc/tq_common.cuh")
+
+
+def sources_digest() -> str:
+    import hashlib
+    hsh = hashlib.sha256()
+    for rel in TRAFFIC_SOURCES:
+        with open(os.path.join(ROOT, rel), "rb") as fh:
+            hsh.update(fh.read())
+    return hsh.hexdigest()[:16]
+
+
+def recorded_traffic():
+    """(bytes per launch, note): dram__bytes_read.sum + dram__bytes_write.sum of one decode launch of the
+    headline workload from the last ncu capture, or (None, why) when the kernel's sources changed since."""
+    try:
+        with open(TRAFFIC_RECORD) as fh:
+            rec = json.load(fh)
+    except (OSError, ValueError):
+        return None, "no ncu capture recorded"
+    if rec.get("sources_digest") != sources_digest():
+        return None, "kernel sources changed since the recorded ncu capture"
+    return float(rec["dram_bytes_per_launch"]), rec.get("source", "ncu capture")
 
 
 def _peaks():
@@ -224,7 +248,7 @@ def measure_store(dev):
 
 
 def measure_decode_large(dev, n_seq: int = 256, n_tok: int = 8192):
-    """Batched decode of one layer of BASELINE config 4 (Llama-3-70B-shaped): 256 sequences x
+    """Batched decode of one Llama-3-70B-shaped layer: 256 sequences x
     8192 compressed tokens, 8 kv heads, 64 query heads, head_dim 128, 3-bit keys / 2-bit values.
     1.68 GB of compressed records per launch: fixed launch costs are amortised, which shows
     what the kernel itself streams."""
@@ -249,23 +273,34 @@ def measure_decode_large(dev, n_seq: int = 256, n_tok: int = 8192):
     for _ in range(3):
         E.decode(c, pool, ws, q, bt, lens, n_tok, out=out)
     torch.cuda.synchronize()
-    reps = 10
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
-        E.decode(c, pool, ws, q, bt, lens, n_tok, out=out, query_prepared=True)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / reps
+    ms, ms_step = _time_decode(lambda prepared: E.decode(c, pool, ws, q, bt, lens, n_tok, out=out,
+                                                         query_prepared=prepared))
     nbytes = n_seq * n_tok * h * c.bytes_per_token
     peak, kind = _peaks()
     return {"workload": f"config4 layer: {n_seq} seqs x {n_tok} tok, Hkv=8 Hq=64 D=128 key3b/val2b",
             "ms_per_launch": ms, "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak, "peak_kind": f"of {kind}",
-            "kv_tokens_per_s": n_seq * n_tok / ms * 1e3, "device_status": ws.status()}
+            "ms_per_step_with_query_prep": ms_step, "frac_with_query_prep": nbytes / ms_step / 1e6 / peak,
+            "kv_tokens_per_s": n_seq * n_tok / ms_step * 1e3, "device_status": ws.status()}
+
+
+def _time_decode(call, reps: int = 10):
+    """(ms per decode launch with the query already prepared, ms per step including query preparation)."""
+    out = []
+    for prepared in (True, False):
+        call(False)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            call(prepared)
+        e1.record()
+        torch.cuda.synchronize()
+        out.append(e0.elapsed_time(e1) / reps)
+    return out[0], out[1]
 
 
 def measure_decode_paged(dev, n_seq: int = 64, lo: int = 1024, hi: int = 32768):
-    """Batched paged decode of BASELINE config 2: 64 sequences of length U[1024, 32768], block size 16, head_dim 128,
+    """Batched paged decode: 64 sequences of length U[1024, 32768], block size 16, head_dim 128,
     8 kv heads, 32 query heads, bf16, 4-bit keys (3-bit codes + QJL sign) and 4-bit values, one query per sequence,
     block tables = a seeded random permutation of a shared pool."""
     from turboquant_b200 import _engine as E
@@ -299,84 +334,136 @@ def measure_decode_paged(dev, n_seq: int = 64, lo: int = 1024, hi: int = 32768):
     for _ in range(3):
         E.decode(c, pool, ws, q, bt, lens, max(lens_l), out=out)
     torch.cuda.synchronize()
-    reps = 10
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(reps):
-        E.decode(c, pool, ws, q, bt, lens, max(lens_l), out=out)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / reps
+    ms, ms_step = _time_decode(lambda prepared: E.decode(c, pool, ws, q, bt, lens, max(lens_l), out=out,
+                                                         query_prepared=prepared))
     nbytes = sum(lens_l) * h * c.bytes_per_token
     peak, kind = _peaks()
     return {"workload": f"config2: {n_seq} seqs x U[{lo},{hi}] tok paged, Hkv=8 Hq=32 D=128 key4b/val4b",
-            "ms_per_step": ms, "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak, "peak_kind": f"of {kind}",
-            "kv_tokens_per_s": sum(lens_l) / ms * 1e3, "includes": "query preparation + decode per step",
-            "device_status": ws.status()}
+            "ms_per_launch": ms, "gbs": nbytes / ms / 1e6, "frac": nbytes / ms / 1e6 / peak, "peak_kind": f"of {kind}",
+            "ms_per_step_with_query_prep": ms_step, "frac_with_query_prep": nbytes / ms_step / 1e6 / peak,
+            "kv_tokens_per_s": sum(lens_l) / ms_step * 1e3, "device_status": ws.status()}
+
+
+def measure_sharded(dev, dist, rank: int, world: int, layers: int = 8, reps: int = 5):
+    """A stack of Llama-3-70B-shaped attention layers (256 sequences x 8192 compressed tokens, 8 kv heads,
+    64 query heads, head_dim 128, 3-bit keys / 2-bit values) partitioned over the ranks - sequences first -
+    with an all-gather of the head outputs (NCCL) per layer.  Total work is fixed (strong scaling).  A step =
+    every layer once: query preparation + decode written straight into the rank's band of the full output,
+    then the gather (a) serialised behind the decode on the same stream and (b) on a second stream, under
+    the decode of the next layer.  Times are CUDA events, max over ranks."""
+    from turboquant_b200 import _engine as E
+    from turboquant_b200 import sharding
+    d, h, qh, n_seq, n_tok = 128, 8, 64, 256, 8192
+    sh = sharding.partition(n_seq, h, world, rank)
+    hl, sl = sh.num_heads, sh.num_seqs
+    g_heads = qh // h
+    nblk = n_tok // 16
+    consts, pools, queries, outs = [], [], [], []
+    bt = torch.arange(sl * nblk, dtype=torch.int32, device=dev).view(sl, nblk)
+    g = torch.Generator(device=dev)
+    for layer in range(layers):
+        c = E.LayerConstants(d, 3, 2, dev, seed=42 + 7 * layer)
+        pool = E.BlockPool(c, hl, sl * nblk)
+        g.manual_seed(100003 * layer + 17 * rank + 1)      # one stream per (layer, shard): ranks build locally
+        ch = torch.exp(0.5 * torch.randn(d, generator=g, device=dev))
+        for s0 in range(0, sl, 16):
+            ns = min(16, sl - s0)
+            k = (torch.randn(ns, n_tok, hl, d, generator=g, device=dev) * ch).to(torch.bfloat16)
+            v = torch.randn(ns, n_tok, hl, d, generator=g, device=dev).to(torch.bfloat16)
+            for j in range(ns):
+                E.store(c, pool, k[j], v[j], stride_token=hl * d, stride_head=d, n_tokens=n_tok, n_heads=hl,
+                        block_table=bt[s0 + j], start_pos=0)
+        consts.append(c)
+        pools.append(pool)
+        queries.append(torch.randn(sl, hl * g_heads, d, generator=g, device=dev).to(torch.bfloat16))
+        outs.append(torch.empty(n_seq, qh, d, dtype=torch.bfloat16, device=dev))
+    lens = torch.full((sl,), n_tok, dtype=torch.int32, device=dev)
+    ws = E.Workspace(dev)
+    slabs = [sharding.output_slab(o, sh, h) for o in outs]
+    in_place = all(x is not None for x in slabs)
+    if not in_place:
+        slabs = [torch.empty(sl, hl * g_heads, d, dtype=torch.bfloat16, device=dev) for _ in outs]
+    comm = torch.cuda.Stream(device=dev)
+    main = torch.cuda.current_stream(dev)
+
+    def decode(layer):
+        E.decode(consts[layer], pools[layer], ws, queries[layer], bt, lens, n_tok, out=slabs[layer])
+
+    def gather(layer):
+        sharding.gather_head_outputs(slabs[layer], sh, n_seq, h, out=outs[layer])
+
+    def step_serial():
+        for layer in range(layers):
+            decode(layer)
+            gather(layer)
+
+    def step_overlap():
+        for layer in range(layers):
+            decode(layer)
+            comm.wait_stream(main)
+            with torch.cuda.stream(comm):
+                gather(layer)
+        main.wait_stream(comm)
+
+    def step_local():
+        for layer in range(layers):
+            decode(layer)
+
+    def step_gather_only():
+        for layer in range(layers):
+            gather(layer)
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        if dist is not None:
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    ms_local = timed(step_local)
+    ms_serial = timed(step_serial) if world > 1 else ms_local
+    ms_overlap = timed(step_overlap) if world > 1 else ms_local
+    ms_gather = timed(step_gather_only) if world > 1 else 0.0
+    status = ws.status()
+    nbytes = layers * n_seq * n_tok * h * consts[0].bytes_per_token
+    peak, kind = _peaks()
+    return {"workload": f"{layers} layers x 256 seqs x 8192 tok, Hkv=8 Hq=64 D=128 key3b/val2b (fixed total: strong scaling)",
+            "partition": f"sequences first: {sl} sequences x {hl} kv heads per rank", "layers": layers,
+            "collective": "all-gather of head outputs per layer (torch.distributed, NCCL), received in place",
+            "gathered_bytes_per_layer": n_seq * qh * d * 2,
+            "ms_per_step_decode_only": ms_local, "ms_per_step_serialised": ms_serial, "ms_per_step_overlapped": ms_overlap,
+            "allgather_us_per_layer": ms_gather / layers * 1e3,
+            "ms_per_layer_overlapped": ms_overlap / layers,
+            "kv_tokens_per_s": layers * n_seq * n_tok / ms_overlap * 1e3,
+            "aggregate_hbm_gbs": nbytes / ms_overlap / 1e6, "frac_per_gpu": nbytes / ms_overlap / 1e6 / world / peak,
+            "peak_kind": f"of {kind}", "timing": "CUDA events, max over ranks", "device_status": status}
 
 
 def run_sharded(args):
-    """`--sharded`: one layer of BASELINE config 4 (256 sequences x 8192 tokens, 8 kv heads, 64 query heads,
-    head_dim 128, 3-bit keys / 2-bit values) partitioned over the ranks - kv heads first, then sequences -
-    with an all-gather of the head outputs (NCCL) after the local decode.  Total work is fixed (strong
-    scaling); the time of a step is the max over ranks of decode + all-gather, from CUDA events."""
-    from turboquant_b200 import _engine as E
-    from turboquant_b200 import sharding
+    """`--sharded`: only the partitioned layer stack (see measure_sharded)."""
     dist, rank, world = _dist()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    d, h, qh, n_seq, n_tok = 128, 8, 64, 256, 8192
-    g_heads = qh // h
-    sh = sharding.partition(n_seq, h, world, rank)
-    hl, sl = sh.num_heads, sh.num_seqs
-    c = E.LayerConstants(d, 3, 2, dev, seed=42)
-    nblk = n_tok // 16
-    pool = E.BlockPool(c, hl, sl * nblk)
-    bt = torch.arange(sl * nblk, dtype=torch.int32, device=dev).view(sl, nblk)
-    g = torch.Generator(device=dev)
-    g.manual_seed(100 + rank)
-    ch = torch.exp(0.5 * torch.randn(d, generator=g, device=dev))
-    for s_ in range(sl):
-        k = (torch.randn(n_tok, hl, d, generator=g, device=dev) * ch).to(torch.bfloat16)
-        v = torch.randn(n_tok, hl, d, generator=g, device=dev).to(torch.bfloat16)
-        E.store(c, pool, k, v, stride_token=hl * d, stride_head=d, n_tokens=n_tok, n_heads=hl, block_table=bt[s_],
-                start_pos=0)
-    q = torch.randn(sl, hl * g_heads, d, generator=g, device=dev).to(torch.bfloat16)
-    lens = torch.full((sl,), n_tok, dtype=torch.int32, device=dev)
-    ws = E.Workspace(dev)
-    out_local = torch.empty_like(q)
-    out_full = torch.empty(n_seq, qh, d, dtype=torch.bfloat16, device=dev)
-
-    def step():
-        E.decode(c, pool, ws, q, bt, lens, n_tok, out=out_local)
-        sharding.gather_head_outputs(out_local, sh, n_seq, h, out=out_full)
-
-    for _ in range(max(3, args.warmup)):
-        step()
-    torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
-        torch.cuda.synchronize()
-    steps = min(args.steps, 64)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    ms, tokens = sharding.reduce_timing(e0.elapsed_time(e1) / steps, float(sl * n_tok), dev)
-    status = ws.status()
+    res = measure_sharded(dev, dist, rank, world)
     if rank == 0:
-        nbytes = n_seq * n_tok * h * c.bytes_per_token
-        print(json.dumps({"metric": "sharded_layer_decode_kv_tokens_per_s", "value": n_seq * n_tok / ms * 1e3,
-                          "unit": UNIT, "n_gpus": world, "steps": steps, "ms_per_step": ms, "higher_is_better": True,
-                          "scaling": "strong", "dtype": "bf16", "data": "synthetic",
-                          "config": {"workload": "config4 layer: 256 seqs x 8192 tok, Hkv=8 Hq=64 D=128 key3b/val2b",
-                                     "partition": f"{min(world, h)} head groups x {max(1, world // h)} sequence groups",
-                                     "collective": "all-gather of head outputs (torch.distributed, NCCL)",
-                                     "gathered_bytes_per_step": n_seq * qh * d * 2},
-                          "aggregate_hbm_gbs": nbytes / ms / 1e6, "device_status": status}), flush=True)
+        print(json.dumps({"metric": "sharded_layer_stack_decode_kv_tokens_per_s", "value": res["kv_tokens_per_s"],
+                          "unit": UNIT, "n_gpus": world, "ms_per_step": res["ms_per_step_overlapped"],
+                          "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": res["workload"]}, "sharded": res}), flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -509,6 +596,7 @@ def run_ours(args):
     kern_ms = k0.elapsed_time(k1) / (5 * reps * nl)
     peak, peak_kind = _peaks()
     achieved = bytes_per_launch / kern_ms / 1e6
+    traffic, traffic_note = recorded_traffic()
 
     # ---- end to end through the Python API with host buffers ----
     from turboquant_b200 import KVCaptureEngine, compute_hybrid_attention
@@ -576,8 +664,17 @@ def run_ours(args):
     two_tokens, two_s = run_e2e(e2e_step_two_calls, 0)
     fused_tokens, fused_s = run_e2e(e2e_step, nl + e2e_steps)
     e2e_tokens, e2e_s = run_e2e(e2e_step_host, 2 * (nl + e2e_steps))
+    # the same call with the stream synchronised after every step: what a caller sees who needs the
+    # output of step i before it can issue step i+1
+    sync_n = min(e2e_steps, 64)
+    t0 = time.perf_counter()
+    for s in range(3 * (nl + e2e_steps), 3 * (nl + e2e_steps) + sync_n):
+        e2e_step_host(s)
+        torch.cuda.synchronize()
+    synced_ms = (time.perf_counter() - t0) / sync_n * 1e3
     clocks = sampler.stop()
 
+    sharded = measure_sharded(dev, dist, rank, world) if not args.no_large else None   # every rank takes part
     store = measure_store(dev) if rank == 0 else None
     large = measure_decode_large(dev) if (rank == 0 and not args.no_large) else None
     paged = measure_decode_paged(dev) if (rank == 0 and not args.no_large) else None
@@ -596,10 +693,9 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "kernel": "tq_decode_mma_kernel", "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_kind": f"of {peak_kind}",
                          "frac_of_nominal_8TBs": achieved / 8000.0, "us_per_launch": kern_ms * 1e3,
-                         "bytes_per_launch": bytes_per_launch, "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
-                         "traffic_source": "ncu capture of one launch, profiles/tq_decode_mma_kernel.md"},
+                         "bytes_per_launch": bytes_per_launch, "traffic": traffic, "traffic_source": traffic_note},
             "e2e": {"value": e2e_tokens / e2e_s, "unit": UNIT, "steps": e2e_steps,
-                    "ms_per_step": e2e_s / e2e_steps * 1e3,
+                    "ms_per_step": e2e_s / e2e_steps * 1e3, "synced_ms_per_step": synced_ms,
                     "call": "KVCaptureEngine.decode_step_host (pinned host buffers; H2D copy, ring append + attention, "
                             "D2H copy enqueued by one library call)",
                     "device_tensor_call_value": fused_tokens / fused_s,
@@ -610,7 +706,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": (2 * w["H"] + w["Qh"]) * w["D"] * 2,
                     "d2h_bytes_per_step": w["Qh"] * w["D"] * 2},
             "gpu_launches": launches, "device_status": status, "clocks": clocks, "store": store,
-            "decode_large": large, "decode_paged": paged,
+            "decode_large": large, "decode_paged": paged, "sharded": sharded,
         }
         if base is not None:
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -632,7 +728,7 @@ def main():
     ap.add_argument("--only-store", action="store_true", help="run only the store-path measurement (profiling)")
     ap.add_argument("--only-paged", action="store_true", help="run only the paged batched decode measurement (profiling)")
     ap.add_argument("--sharded", action="store_true",
-                    help="config-4 layer partitioned over the ranks with an all-gather of head outputs (strong scaling)")
+                    help="only the partitioned layer stack with its all-gather of head outputs (strong scaling)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.only_store:

@@ -210,9 +210,16 @@ int tq_decode(const tq_consts* consts, const tq_pool* pool, const tq_decode_args
  * (before it waits for the kernel ahead of it on the stream) and `dev_in` is not written at
  * all; otherwise a one-CTA kernel pulls `host_in` into `dev_in`.  The decode kernel writes the
  * result into `host_out` itself (args->out is then left untouched).  Anything else goes through
- * cudaMemcpyAsync.  `host_in` must stay unchanged until the step has completed. */
+ * cudaMemcpyAsync.  `host_in` must stay unchanged until the step has completed.  The answer of the
+ * page-locked check is remembered per device and pointer: a buffer must stay registered for as
+ * long as the library may be given it, and tq_host_buffer_forget must be called before it is
+ * unregistered or freed (a stale "mapped" answer would let a kernel touch unmapped memory). */
 int tq_decode_host_io(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* args, const void* host_in,
                       void* dev_in, size_t in_bytes, void* host_out, size_t out_bytes, void* stream);
+
+/* Drop what tq_decode_host_io remembers about `host_ptr` (NULL: about every buffer, on every
+ * device).  Host-only; call it before cudaHostUnregister / cudaFreeHost of a step buffer. */
+int tq_host_buffer_forget(const void* host_ptr);
 
 /* tq_decode without caller-provided scratch: `workspace` / `workspace_bytes` of
  * the arguments are ignored and a fixed array inside the library, resident on
@@ -224,14 +231,27 @@ int tq_decode_host_io(const tq_consts* consts, const tq_pool* pool, const tq_dec
  *   - the launch must fit tq_decode_static_scratch_bytes() (8 MiB); a larger
  *     batch x heads x splits is refused with TQ_ERR_WORKSPACE (lower num_splits
  *     or use tq_decode);
- *   - the first call on a device looks up the array's device address: make it
- *     with that device current and before any stream capture;
+ *   - the first call on a device (of this function or of
+ *     tq_decode_static_read_status) looks up the array's device address: make it
+ *     with that device current, before any stream capture, and BEFORE the host
+ *     application claims the rest of the device memory - the CUDA runtime loads
+ *     the library's device code lazily, and the array's 8 MiB are taken from the
+ *     device at that first use, not when the shared library is opened;
  *   - all calls on a device share the one array: calls that overlap on the GPU
  *     (different streams) race - serialise them;
- *   - `query_prepared` is ignored (the query is always prepared again).
+ *   - `query_prepared` is ignored (the query is always prepared again);
+ *   - arguments are checked before anything is enqueued; every call clears the
+ *     array's tickets but not its status word, which keeps the first device-side
+ *     error until tq_decode_static_read_status has returned it.
  * It calls no cudaMalloc / cudaFree or any other allocating routine. */
 int tq_decode_static(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* args, void* stream);
 size_t tq_decode_static_scratch_bytes(void);
+
+/* Device status word of the built-in array on the current device: 0, or the
+ * tq_status (TQ_ERR_TIMEOUT, TQ_ERR_RANGE) a tq_decode_static kernel left there.
+ * Synchronises `stream`, then clears a non-zero status.  No counterpart in the
+ * reference, like tq_decode_static itself; allocates nothing. */
+int tq_decode_static_read_status(void* stream, int32_t* out);
 
 /* Unscaled logits <q, k_hat> of every query vector against the first n_tokens
  * of one sequence: query (H, n_q, D) -> logits (H, n_q, n_tokens) fp32.
@@ -275,8 +295,12 @@ int tq_pack_stage(const tq_consts* consts, const float* y, const float* projecte
  * them zero again).  Call once after allocating it. */
 int tq_workspace_init(void* workspace, size_t bytes, void* stream);
 
-/* Device status word of a workspace: 0, or a tq_status written by a kernel
- * whose bounded wait ran out.  Synchronises the stream. */
+/* Device status word of a workspace: 0, or a tq_status written by a kernel:
+ * TQ_ERR_TIMEOUT when a bounded wait ran out (the output of that launch is then
+ * undefined; the workspace stays usable, its tickets are reset), TQ_ERR_RANGE
+ * when a block index was outside the pool or a device-side length exceeded the
+ * host bound (max_seq_len / max_ring_len; the length is clamped to the bound).
+ * Synchronises the stream. */
 int tq_read_status(const void* workspace, void* stream, int32_t* out);
 
 #ifdef __cplusplus

@@ -361,7 +361,7 @@ def test_legacy_kv_cache_object(dev):
 
 
 def test_full_size_properties_config1(dev):
-    """BASELINE config 1 shape (D=256, 4 kv heads, 32768 tokens): size-independent
+    """The long single-sequence shape (D=256, 4 kv heads, 32768 tokens): size-independent
     properties instead of an oracle run - chunking must not change a byte, the
     plane round trip is lossless, split count and block permutation do not
     change the attention output."""
@@ -700,3 +700,82 @@ def test_vllm_adapter_hybrid_decode(dev):
         assert adapter.get_stats(runner)["total_compressed_tokens"] == 200
     finally:
         adapter.set_mode(adapter.MODE_OFF)
+
+
+def test_host_io_paths_and_length_bounds(dev):
+    """tq_decode_host_io through its three input routes - arguments inside the staging buffer
+    (read straight from mapped host memory), a query outside it (the one-CTA stage-in kernel)
+    and pageable host memory (cudaMemcpyAsync) - must give the same bytes as tq_decode on
+    device tensors; a device-side length above the host bound is clamped and reported."""
+    import ctypes as C
+    from turboquant_b200 import _engine as E, _lib
+    d, h, qh, n, cap = 128, 2, 8, 700, 32
+    c = E.LayerConstants(d, 3, 2, dev, seed=42)
+    k, v = O.synth_kv(n + 4, h, d, seed=23, dtype=torch.bfloat16)
+    pool = E.BlockPool(c, h, E.blocks_for(n))
+    bt = E.identity_block_table(pool.num_blocks, dev)
+    E.store(c, pool, k[:n].to(dev), v[:n].to(dev), stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h,
+            block_table=bt, start_pos=0)
+    lens = torch.tensor([n], dtype=torch.int32, device=dev)
+    q = O.synth_query(1, qh, d, seed=24, dtype=torch.bfloat16)
+    nk, nq = h * d, qh * d
+    st = torch.cuda.current_stream(dev).cuda_stream
+
+    def run(route):
+        ring_k = torch.zeros(cap, h, d, dtype=torch.bfloat16, device=dev)
+        ring_v = torch.zeros_like(ring_k)
+        rl = torch.zeros(1, dtype=torch.int32, device=dev)
+        ws = E.Workspace(dev)
+        ws.ensure_decode(c, 1, qh, h, 4)
+        out = torch.empty(1, qh, d, dtype=torch.bfloat16, device=dev)
+        a = _lib.tq_decode_args()
+        a.q_dtype = a.ring_dtype = _lib.TQ_BF16
+        a.batch, a.num_q_heads = 1, qh
+        a.block_table, a.block_table_stride = bt.data_ptr(), bt.numel()
+        a.seq_lens, a.max_seq_len, a.min_history = lens.data_ptr(), n, 16
+        a.ring_k, a.ring_v, a.ring_lens = ring_k.data_ptr(), ring_v.data_ptr(), rl.data_ptr()
+        a.max_ring_len, a.ring_capacity = 1, cap
+        a.ring_stride_seq, a.ring_stride_token = 0, h * d
+        a.scale = 1.0 / math.sqrt(d)
+        a.out, a.workspace, a.workspace_bytes, a.num_splits = out.data_ptr(), ws.ptr, ws.nbytes, 4
+        packed = torch.cat([k[n:n + 1].reshape(-1), v[n:n + 1].reshape(-1), q.reshape(-1)])
+        if route == "device":
+            stage = packed.to(dev)
+            a.append_k, a.append_v = stage.data_ptr(), stage.data_ptr() + 2 * nk
+            a.query = stage.data_ptr() + 4 * nk
+            E.check(_lib.lib().tq_decode(C.byref(c.c), C.byref(pool.c), C.byref(a), st), "tq_decode")
+            torch.cuda.synchronize()
+            return out.cpu(), ring_k.cpu(), int(rl.item()), ws.status()
+        hout = torch.empty(nq, dtype=torch.bfloat16)
+        stage = torch.zeros(2 * nk + nq, dtype=torch.bfloat16, device=dev)
+        qdev = q.to(dev).contiguous()
+        if route == "pageable":
+            hin = packed.clone()                     # not pinned: both copies go through cudaMemcpyAsync
+        else:
+            hin, hout = packed.pin_memory(), hout.pin_memory()
+        a.append_k, a.append_v = stage.data_ptr(), stage.data_ptr() + 2 * nk
+        a.query = qdev.data_ptr() if route == "query_outside" else stage.data_ptr() + 4 * nk
+        in_bytes = (2 * nk if route == "query_outside" else 2 * nk + nq) * 2
+        E.check(_lib.lib().tq_decode_host_io(C.byref(c.c), C.byref(pool.c), C.byref(a), hin.data_ptr(), stage.data_ptr(),
+                                             in_bytes, hout.data_ptr(), nq * 2, st), "tq_decode_host_io")
+        torch.cuda.synchronize()
+        _lib.lib().tq_host_buffer_forget(hin.data_ptr())
+        _lib.lib().tq_host_buffer_forget(hout.data_ptr())
+        return hout.view(1, qh, d).clone(), ring_k.cpu(), int(rl.item()), ws.status()
+
+    ref = run("device")
+    assert ref[2] == 1 and ref[3] == 0
+    for route in ("inside", "query_outside", "pageable"):
+        got = run(route)
+        assert got[2] == 1 and got[3] == 0, route
+        assert torch.equal(got[1], ref[1]), route
+        assert torch.equal(got[0], ref[0]), route
+
+    # a sequence length above the bound the host passed: clamped to the bound, status TQ_ERR_RANGE
+    ws = E.Workspace(dev)
+    big = torch.tensor([n + 4000], dtype=torch.int32, device=dev)
+    o_big = E.decode(c, pool, ws, q.to(dev), bt.unsqueeze(0), big, n, num_splits=3)
+    assert ws.status() == -7
+    E.check(_lib.lib().tq_workspace_init(ws.ptr, ws.nbytes, st), "tq_workspace_init")
+    o_ok = E.decode(c, pool, ws, q.to(dev), bt.unsqueeze(0), lens, n, num_splits=3)
+    assert ws.status() == 0 and torch.equal(o_big, o_ok)

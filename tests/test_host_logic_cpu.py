@@ -62,3 +62,22 @@ def test_config1_split_is_five_record_rounds_per_warp():
     s = E.choose_splits(1, 4, 32768, 148, 128)
     assert s == 35                                    # 37 slots per head: 35 history + 2 ring CTAs
     assert -(-2048 // s) <= 5 * 12                    # at most five records per warp of a 12-warp CTA
+
+
+@pytest.mark.parametrize("d,bits", [(128, 2), (128, 3), (256, 2), (256, 3), (64, 4), (576, 3)])
+def test_own_lloyd_max_solver_reproduces_the_shipped_code_books(d, bits):
+    """The package's solver (closed-form cell integrals) against the JSON files the kernels use, which
+    came from the reference's quadrature-based solver (codebook.py:68-143): same starting point and
+    stopping rule, so the same centroids and boundaries to well below 1e-6."""
+    import json
+    import os
+    import numpy as np
+    from turboquant_b200 import codebook as CB
+    with open(os.path.join(CB._CODEBOOK_DIR, f"codebook_d{d}_b{bits}.json")) as fh:
+        shipped = json.load(fh)
+    own = CB.compute_lloyd_max_codebook(d, bits)
+    assert len(own["centroids"]) == 2 ** bits and len(own["boundaries"]) == 2 ** bits + 1
+    assert np.abs(np.array(own["centroids"]) - np.array(shipped["centroids"])).max() <= 1e-6
+    assert np.abs(np.array(own["boundaries"]) - np.array(shipped["boundaries"])).max() <= 1e-6
+    assert abs(own["mse_per_coord"] - shipped["mse_per_coord"]) <= 1e-9
+    assert own["boundaries"][0] == -1.0 and own["boundaries"][-1] == 1.0

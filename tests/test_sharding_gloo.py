@@ -9,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from turboquant_b200.sharding import gather_head_outputs, partition, reduce_timing
+from turboquant_b200.sharding import gather_head_outputs, output_slab, partition, reduce_timing
 
 
 @pytest.mark.parametrize("seqs,heads,world", [(256, 8, 1), (256, 8, 2), (256, 8, 4), (256, 8, 8), (64, 8, 16),
@@ -23,9 +23,22 @@ def test_partition_covers_every_pair_once(seqs, heads, world):
     assert bool((owner == 1).all())
 
 
+def test_partition_is_sequences_first():
+    """With enough sequences every rank owns whole output rows (all kv heads of a band of sequences);
+    heads are split only when the ranks outnumber the sequences."""
+    for world in (1, 2, 4, 8):
+        for r in range(world):
+            s = partition(256, 8, world, r)
+            assert (s.head0, s.head1) == (0, 8) and (s.seq0, s.seq1) == (256 * r // world, 256 * (r + 1) // world)
+    s = partition(1, 4, 4, 2)
+    assert (s.seq0, s.seq1, s.head0, s.head1) == (0, 1, 2, 3)
+    s = partition(2, 8, 8, 5)      # 2 sequence bands x 4 head slots
+    assert (s.seq0, s.seq1, s.head0, s.head1) == (1, 2, 2, 4)
+
+
 def test_partition_rejects_bad_worlds():
     with pytest.raises(ValueError):
-        partition(8, 8, 3, 0)
+        partition(1, 8, 3, 0)      # three head slots do not divide eight heads
     with pytest.raises(ValueError):
         partition(8, 8, 2, 2)
 
@@ -48,6 +61,16 @@ def _worker(rank, world, port, seqs, heads, g, d, result):
         full = gather_head_outputs(local, shard, seqs, heads)
         want = (torch.arange(seqs).view(-1, 1, 1) * 1000 + torch.arange(heads * g).view(1, -1, 1)).float().expand(-1, -1, d)
         ok = torch.equal(full, want)
+        # in place: the rank writes its band of the full tensor, the gather fills in the others
+        buf = torch.full((seqs, heads * g, d), -1.0)
+        slab = output_slab(buf, shard, heads)
+        if seqs % world == 0 and shard.num_heads == heads:
+            slab.copy_(local)
+            full2, work = gather_head_outputs(slab, shard, seqs, heads, out=buf, async_op=True)
+            work.wait()
+            ok = ok and full2.data_ptr() == buf.data_ptr() and torch.equal(buf, want)
+        else:
+            ok = ok and slab is None
         ms, units = reduce_timing(10.0 + rank, 100.0 * (rank + 1), "cpu")
         ok = ok and ms == 10.0 + world - 1 and units == 100.0 * world * (world + 1) / 2
         result[rank] = bool(ok)
@@ -55,7 +78,7 @@ def _worker(rank, world, port, seqs, heads, g, d, result):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("seqs,heads", [(6, 2), (5, 1)])
+@pytest.mark.parametrize("seqs,heads", [(6, 2), (5, 1), (1, 2)])
 def test_two_gloo_ranks_gather_and_time(seqs, heads):
     world = 2
     with mp.Manager() as mgr:

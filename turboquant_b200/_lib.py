@@ -79,6 +79,8 @@ SIGNATURES = {
                                     C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p]),
     "tq_decode_static": (C.c_int, [C.POINTER(tq_consts), C.POINTER(tq_pool), C.POINTER(tq_decode_args), C.c_void_p]),
     "tq_decode_static_scratch_bytes": (C.c_size_t, []),
+    "tq_decode_static_read_status": (C.c_int, [C.c_void_p, C.POINTER(C.c_int32)]),
+    "tq_host_buffer_forget": (C.c_int, [C.c_void_p]),
     "tq_scores": (C.c_int, [C.POINTER(tq_consts), C.POINTER(tq_pool), C.c_void_p, C.c_int64, C.c_void_p, C.c_int,
                             C.c_int32, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "tq_pool_to_planes": (C.c_int, [C.POINTER(tq_config), C.POINTER(tq_pool), C.c_void_p, C.c_int64,
@@ -102,7 +104,7 @@ def lib() -> C.CDLL:
     """The loaded library; raises if it has not been built."""
     global _lib
     if _lib is None:
-        path = os.environ.get("TQ_B200_LIB", LIB_PATH)   # a differently built library, for A/B measurements
+        path = LIB_PATH
         if not os.path.exists(path):
             raise RuntimeError(
                 f"{path} is missing: build it with `python -m turboquant_b200.build` "

@@ -10,6 +10,23 @@ int tq_check_config(const tq_config* cfg) {
     return TQ_OK;
 }
 
+int tq_current_device() {
+    int dev = -1;
+    return cudaGetDevice(&dev) == cudaSuccess ? dev : -1;
+}
+
+int tq_sm_count() {
+    static int sms[TQ_MAX_DEVICES] = {};
+    const int dev = tq_current_device();
+    if (dev < 0 || dev >= TQ_MAX_DEVICES) return 148;
+    if (sms[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        sms[dev] = n;
+    }
+    return sms[dev];
+}
+
 extern "C" int tq_get_layout(const tq_config* cfg, tq_layout* out) {
     if (!cfg || !out) return TQ_ERR_NULL;
     int rc = tq_check_config(cfg);

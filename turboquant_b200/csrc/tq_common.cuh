@@ -212,3 +212,29 @@ struct TqCodebook {
 #define TQ_WS_HEADER_BYTES 256
 
 int tq_check_config(const tq_config* cfg);
+
+// ---------------------------------------------------------------------------
+// per-device host bookkeeping: kernel attributes and SM counts belong to a
+// device, not to the process
+// ---------------------------------------------------------------------------
+constexpr int TQ_MAX_DEVICES = 64;
+int tq_current_device();   // ordinal of the calling thread's current device, -1 on error
+int tq_sm_count();         // multiprocessors of the current device (148 when the query fails)
+
+// Largest dynamic shared-memory size a kernel has been opted in for, per device.
+struct TqSmemOptIn {
+    size_t bytes[TQ_MAX_DEVICES] = {};
+};
+// Raises the kernel's dynamic shared-memory limit on the current device when `smem`
+// exceeds what was set there before; steady-state calls issue nothing but the launch.
+template <class Kern>
+inline int tq_opt_in_smem(Kern kern, size_t smem, TqSmemOptIn& state) {
+    const int dev = tq_current_device();
+    if (dev < 0 || dev >= TQ_MAX_DEVICES) return TQ_ERR_CUDA;
+    if (smem > state.bytes[dev]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return TQ_ERR_CUDA;
+        state.bytes[dev] = smem;
+    }
+    return TQ_OK;
+}

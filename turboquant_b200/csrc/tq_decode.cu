@@ -36,7 +36,6 @@ struct RingAppend {
     int32_t* ring_lens;    // position of the new token; incremented
     int elem_bytes, B, H, capacity;
     int64_t stride_seq, stride_token;   // in elements
-    int trace_slot;
     int early_inputs;   // query and new token come from host memory that no earlier kernel writes:
                         // read them before waiting for the kernel ahead (their latency hides under it)
 };
@@ -51,12 +50,6 @@ __global__ void __launch_bounds__(256, OCC) tq_qprep_kernel(const void* __restri
                                                        const RingAppend ap) {
     // the decode kernel may start its set-up now; it waits for this grid before it reads our output
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-#ifdef TQ_TRACE
-#define TQ_QSTAMP(i) do { if (threadIdx.x == 0) { const int c = blockIdx.x + gridDim.x * blockIdx.y; if (c < 256) g_tq_trace_q[((ap.trace_slot & 1) * 256 + c) * 4 + (i)] = tq_now(); } } while (0)
-#else
-#define TQ_QSTAMP(i)
-#endif
-    TQ_QSTAMP(0);
     __shared__ float qsm[VPC * D];          // queries
     __shared__ float red[8 * VPC * 32];     // partial sums
     __shared__ float qn2[VPC];              // squared norms
@@ -105,7 +98,6 @@ __global__ void __launch_bounds__(256, OCC) tq_qprep_kernel(const void* __restri
     const bool live = pass == 1;
     if (live) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        TQ_QSTAMP(1);
     }
     if (do_append && live) {
         for (int i = threadIdx.x; i < n_app; i += 256) {
@@ -128,9 +120,10 @@ __global__ void __launch_bounds__(256, OCC) tq_qprep_kernel(const void* __restri
 #pragma unroll
         for (int u = 0; u < VPC * D / 256; ++u) qsm[threadIdx.x + u * 256] = qv[u];
     } else {
+        // before the wait the query still belongs to the kernel ahead: the rehearsal computes on zeros
         for (int i = threadIdx.x; i < VPC * D; i += 256) {
             const int v = i / D;
-            qsm[i] = v < nv ? tq_load_any(q, (v0 + v) * D + (i % D), dt) : 0.f;
+            qsm[i] = (live && v < nv) ? tq_load_any(q, (v0 + v) * D + (i % D), dt) : 0.f;
         }
     }
     __syncthreads();
@@ -187,7 +180,6 @@ __global__ void __launch_bounds__(256, OCC) tq_qprep_kernel(const void* __restri
     }
     __syncthreads();   // shared memory is reused by the second pass
     }
-    TQ_QSTAMP(2);
 }
 
 int launch_qprep(const void* q, int dt, int64_t nvec, int D, const float* pi_t, const float* s_t, float* out,
@@ -256,6 +248,10 @@ __global__ void __launch_bounds__(DEC_THREADS) tq_decode_kernel(const DecodePara
     if (x < p.num_splits) {
         // ------------------------- compressed history -------------------------
         int n = p.seq_lens[b];
+        if (n > p.max_seq_len) {   // the host bound sized the grid and the block-table check
+            if (tid == 0) atomicCAS(p.status, 0, (int)TQ_ERR_RANGE);
+            n = p.max_seq_len;
+        }
         if (n < p.min_history) n = 0;
         const int nblk = (n + TQ_BLOCK_TOKENS - 1) / TQ_BLOCK_TOKENS;
         const int ntile = (nblk + TILE_BLOCKS - 1) / TILE_BLOCKS;
@@ -464,14 +460,8 @@ int launch_decode(const DecodeParams& p, int B, int block_bytes, cudaStream_t st
     const int nslot = p.num_splits + p.ring_splits;
     const size_t smem = decode_smem_bytes<D, GP>(block_bytes, nslot);
     auto kern = tq_decode_kernel<D, MSE_BITS, VAL_BITS, GP>;
-    // raised once per kernel (and again only if a larger launch needs it), so
-    // that steady-state calls issue nothing but the launch (graph capture)
-    static size_t smem_set = 0;
-    if (smem > smem_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return TQ_ERR_CUDA;
-        smem_set = smem;
-    }
+    static TqSmemOptIn opt_in;
+    if (tq_opt_in_smem(kern, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;
     dim3 grid((unsigned)nslot, (unsigned)p.H, (unsigned)B);
     kern<<<grid, DEC_THREADS, smem, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
@@ -501,22 +491,12 @@ WsLayout decode_ws_layout(int D, int B, int Qh, int H, int max_slots) {
 
 int ring_splits_for(int max_ring_len, int ring_tok) { return (max_ring_len + ring_tok - 1) / ring_tok; }
 
-int sm_count_of_current_device() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0, n = 148;
-        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        sms = n > 0 ? n : 148;
-    }
-    return sms;
-}
-
 // Ring tokens per ring CTA: 64 when the whole launch then fits one wave (fewer ring CTAs leave more
 // SMs to the history), else 32.  A pure function of the launch shape, so that callers can plan with it.
 int ring_tok_for(int max_ring_len, int64_t pairs, int splits) {
     if (max_ring_len <= RING_TOK) return RING_TOK;
     const int r64 = (max_ring_len + 2 * RING_TOK - 1) / (2 * RING_TOK);
-    return pairs * (splits + r64) <= sm_count_of_current_device() ? 2 * RING_TOK : RING_TOK;
+    return pairs * (splits + r64) <= tq_sm_count() ? 2 * RING_TOK : RING_TOK;
 }
 
 }  // namespace
@@ -543,7 +523,7 @@ extern "C" int tq_scores_workspace_bytes(const tq_config* cfg, int64_t n_vectors
 }
 
 static int decode_impl(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* a, void* stream,
-                       int early_inputs) {
+                       int early_inputs, int validate_only = 0) {
     if (!consts || !pool || !a) return TQ_ERR_NULL;
     if (!pool->base || !a->query || !a->out || !a->workspace || !a->block_table || !a->seq_lens) return TQ_ERR_NULL;
     if (!consts->pi_t || !consts->s_t) return TQ_ERR_NULL;
@@ -567,8 +547,7 @@ static int decode_impl(const tq_consts* consts, const tq_pool* pool, const tq_de
     int splits = a->num_splits;
     if (splits <= 0) {
         // about two CTAs per SM over the whole launch, at least 2 tiles per split
-        int dev = 0, sms = 148;
-        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        const int sms = tq_sm_count();
         const int want = (2 * sms + a->batch * H - 1) / (a->batch * H);
         splits = want < 1 ? 1 : want;
         const int cap = (ntile + 1) / 2;
@@ -590,10 +569,6 @@ static int decode_impl(const tq_consts* consts, const tq_pool* pool, const tq_de
     uint32_t* qfrag = (uint32_t*)(ws + w.off_qfrag);
     RingAppend ap = {};
     ap.early_inputs = early_inputs;
-#ifdef TQ_TRACE
-    static int trace_launch_q = 0;
-    ap.trace_slot = trace_launch_q++;
-#endif
     if (a->append_k != nullptr) {
         if (!has_ring || !a->append_v || a->query_prepared) return TQ_ERR_NULL;
         if (a->ring_capacity < a->max_ring_len) return TQ_ERR_SHAPE;
@@ -613,6 +588,7 @@ static int decode_impl(const tq_consts* consts, const tq_pool* pool, const tq_de
         ap.stride_seq = a->ring_stride_seq;
         ap.stride_token = a->ring_stride_token;
     }
+    if (validate_only) return TQ_OK;   // every host-side check has passed; nothing was enqueued
     if (!a->query_prepared) {
         const int64_t nvec = (int64_t)a->batch * a->num_q_heads;
         if (launch_qprep(a->query, a->q_dtype, nvec, D, consts->pi_t, consts->s_t, qprep, qfrag, G, a->num_q_heads,
@@ -639,6 +615,7 @@ static int decode_impl(const tq_consts* consts, const tq_pool* pool, const tq_de
     p.ring_v = has_ring ? a->ring_v : nullptr;
     p.ring_dtype = a->ring_dtype;
     p.ring_lens = has_ring ? a->ring_lens : nullptr;
+    p.max_ring_len = has_ring ? a->max_ring_len : 0;
     p.ring_stride_seq = a->ring_stride_seq;
     p.ring_stride_token = a->ring_stride_token;
     p.scale = a->scale;
@@ -655,11 +632,6 @@ static int decode_impl(const tq_consts* consts, const tq_pool* pool, const tq_de
     p.ring_splits = rsplits;
     p.ring_tok = ring_tok;
     p.land_bytes = 0;
-    p.frags_ready = a->query_prepared ? 1 : 0;
-#ifdef TQ_TRACE
-    static int trace_launch = 0;
-    p.trace_slot = trace_launch++;
-#endif
 
     const int mse_bits = consts->cfg.key_bits - 1, vb = consts->cfg.value_bits;
     if (a->kernel != 1) {   // tensor-core kernel where it applies
@@ -728,13 +700,8 @@ extern "C" int tq_scores(const tq_consts* consts, const tq_pool* pool, const int
     const int mse_bits = consts->cfg.key_bits - 1;
 #define TQ_SC(DD, MB)                                                                                          \
     do {                                                                                                       \
-        static size_t smem_set = 0;                                                                            \
-        if (smem > smem_set) {                                                                                 \
-            if (cudaFuncSetAttribute(tq_scores_kernel<DD, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
-                                     (int)smem) != cudaSuccess)                                                \
-                return TQ_ERR_CUDA;                                                                            \
-            smem_set = smem;                                                                                   \
-        }                                                                                                      \
+        static TqSmemOptIn opt_in;                                                                             \
+        if (tq_opt_in_smem(tq_scores_kernel<DD, MB>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;               \
         tq_scores_kernel<DD, MB><<<grid, DEC_THREADS, smem, st>>>(p, consts->cfg.key_bits, consts->cfg.value_bits); \
     } while (0)
     if (D == 128 && mse_bits == 2) TQ_SC(128, 2);
@@ -759,8 +726,7 @@ extern "C" int tq_scores(const tq_consts* consts, const tq_pool* pool, const int
 static __device__ __align__(256) unsigned char g_tq_static_scratch[TQ_STATIC_SCRATCH_BYTES];
 
 namespace {
-constexpr int kMaxDevices = 64;
-void* g_static_scratch_ptr[kMaxDevices];   // device address of the array, per device ordinal
+void* g_static_scratch_ptr[TQ_MAX_DEVICES];   // device address of the array, per device ordinal
 }  // namespace
 
 extern "C" size_t tq_decode_static_scratch_bytes(void) { return (size_t)TQ_STATIC_SCRATCH_BYTES; }
@@ -791,15 +757,23 @@ __global__ void __launch_bounds__(1024) tq_stage_in_kernel(const uint4* __restri
 constexpr size_t HOST_IO_DIRECT_MAX = 64 * 1024;
 
 // true when the GPU may dereference `ptr` itself: page-locked (pinned or registered) host memory
-// under unified addressing.  The last answers are remembered: step buffers are reused.
+// under unified addressing.  Step buffers are reused, so the last few answers are remembered per
+// device; tq_host_buffer_forget drops them when a buffer is unregistered or freed.
+struct HostPtrCache {
+    const void* ptr[4] = {nullptr, nullptr, nullptr, nullptr};
+    size_t bytes[4] = {0, 0, 0, 0};
+    int next = 0;
+};
+HostPtrCache g_host_ptr_cache[TQ_MAX_DEVICES];
+std::mutex g_host_ptr_mu;   // callers may come from several host threads
+
 bool host_ptr_is_mapped(const void* ptr, size_t bytes) {
-    static const void* ok_ptr[4] = {nullptr, nullptr, nullptr, nullptr};
-    static size_t ok_bytes[4] = {0, 0, 0, 0};
-    static int next = 0;
-    static std::mutex mu;                 // callers may come from several host threads
-    std::lock_guard<std::mutex> lock(mu);
+    const int dev = tq_current_device();
+    if (dev < 0 || dev >= TQ_MAX_DEVICES) return false;
+    std::lock_guard<std::mutex> lock(g_host_ptr_mu);
+    HostPtrCache& c = g_host_ptr_cache[dev];
     for (int i = 0; i < 4; ++i)
-        if (ok_ptr[i] == ptr && ok_bytes[i] >= bytes) return true;
+        if (c.ptr[i] == ptr && c.bytes[i] >= bytes) return true;
     cudaPointerAttributes at;
     if (cudaPointerGetAttributes(&at, ptr) != cudaSuccess) {
         cudaGetLastError();
@@ -811,13 +785,24 @@ bool host_ptr_is_mapped(const void* ptr, size_t bytes) {
         cudaGetLastError();
         return false;
     }
-    ok_ptr[next] = ptr;
-    ok_bytes[next] = bytes;
-    next = (next + 1) & 3;
+    c.ptr[c.next] = ptr;
+    c.bytes[c.next] = bytes;
+    c.next = (c.next + 1) & 3;
     return true;
 }
 
 }  // namespace
+
+extern "C" int tq_host_buffer_forget(const void* host_ptr) {
+    std::lock_guard<std::mutex> lock(g_host_ptr_mu);
+    for (int d = 0; d < TQ_MAX_DEVICES; ++d)
+        for (int i = 0; i < 4; ++i)
+            if (host_ptr == nullptr || g_host_ptr_cache[d].ptr[i] == host_ptr) {
+                g_host_ptr_cache[d].ptr[i] = nullptr;
+                g_host_ptr_cache[d].bytes[i] = 0;
+            }
+    return TQ_OK;
+}
 
 extern "C" int tq_decode_host_io(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* a,
                                  const void* host_in, void* dev_in, size_t in_bytes, void* host_out, size_t out_bytes,
@@ -875,11 +860,10 @@ extern "C" int tq_decode_host_io(const tq_consts* consts, const tq_pool* pool, c
 }
 
 
-extern "C" int tq_decode_static(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* a, void* stream) {
-    if (!consts || !pool || !a) return TQ_ERR_NULL;
-    if (a->batch <= 0 || pool->num_kv_heads <= 0) return TQ_ERR_SHAPE;
-    int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TQ_ERR_CUDA;
+// Device address of the built-in array on the current device, looked up on first use.
+static int static_scratch_address(void** out) {
+    const int dev = tq_current_device();
+    if (dev < 0 || dev >= TQ_MAX_DEVICES) return TQ_ERR_CUDA;
     if (g_static_scratch_ptr[dev] == nullptr) {
         // In host code the array's name is only a handle; the kernels need the
         // address the symbol has on THIS device.  Looked up once per device, on
@@ -888,21 +872,44 @@ extern "C" int tq_decode_static(const tq_consts* consts, const tq_pool* pool, co
         if (cudaGetSymbolAddress(&ptr, g_tq_static_scratch) != cudaSuccess || ptr == nullptr) return TQ_ERR_CUDA;
         g_static_scratch_ptr[dev] = ptr;
     }
-    void* scratch = g_static_scratch_ptr[dev];
-    // The array keeps whatever the previous call left: the status word and the
-    // per-(sequence, head) tickets must start at zero.
-    const size_t head = TQ_WS_HEADER_BYTES + (((size_t)a->batch * pool->num_kv_heads * sizeof(int32_t) + 255) / 256) * 256;
-    if (head > TQ_STATIC_SCRATCH_BYTES) return TQ_ERR_WORKSPACE;
-    if (cudaMemsetAsync(scratch, 0, head, (cudaStream_t)stream) != cudaSuccess) return TQ_ERR_CUDA;
+    *out = g_static_scratch_ptr[dev];
+    return TQ_OK;
+}
+
+extern "C" int tq_decode_static(const tq_consts* consts, const tq_pool* pool, const tq_decode_args* a, void* stream) {
+    if (!consts || !pool || !a) return TQ_ERR_NULL;
+    if (a->batch <= 0 || pool->num_kv_heads <= 0) return TQ_ERR_SHAPE;
+    void* scratch = nullptr;
+    int rc = static_scratch_address(&scratch);
+    if (rc != TQ_OK) return rc;
     tq_decode_args b = *a;
     b.workspace = scratch;
     b.workspace_bytes = TQ_STATIC_SCRATCH_BYTES;
     b.query_prepared = 0;   // the prepared query of an earlier call may have been overwritten by another caller
-    return tq_decode(consts, pool, &b, stream);   // answers TQ_ERR_WORKSPACE when the launch needs more than the array
+    // Everything the host can check is checked before anything is enqueued (a refused call leaves the
+    // array as it was); TQ_ERR_WORKSPACE when the launch needs more than the array.
+    rc = decode_impl(consts, pool, &b, stream, 0, /*validate_only=*/1);
+    if (rc != TQ_OK) return rc;
+    // The array keeps whatever the previous call left.  The per-(sequence, head) tickets must start at
+    // zero: a call that was cut short (or overlapped another one) may have left them counting.  The
+    // status word in front of them is NOT cleared: an error stays until tq_decode_static_read_status
+    // has reported it.
+    const size_t tickets = (((size_t)a->batch * pool->num_kv_heads * sizeof(int32_t) + 255) / 256) * 256;
+    if (cudaMemsetAsync((char*)scratch + TQ_WS_HEADER_BYTES, 0, tickets, (cudaStream_t)stream) != cudaSuccess)
+        return TQ_ERR_CUDA;
+    return decode_impl(consts, pool, &b, stream, 0, 0);
 }
 
-#ifdef TQ_TRACE
-extern "C" int tq_debug_read_trace_q(unsigned long long* out, int n) {
-    return cudaMemcpyFromSymbol(out, tqdec::g_tq_trace_q, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -5;
+extern "C" int tq_decode_static_read_status(void* stream, int32_t* out) {
+    if (!out) return TQ_ERR_NULL;
+    void* scratch = nullptr;
+    const int rc = static_scratch_address(&scratch);
+    if (rc != TQ_OK) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    int32_t v = 0;
+    if (cudaMemcpyAsync(&v, scratch, sizeof(int32_t), cudaMemcpyDeviceToHost, st) != cudaSuccess) return TQ_ERR_CUDA;
+    if (cudaStreamSynchronize(st) != cudaSuccess) return TQ_ERR_CUDA;
+    if (v != 0 && cudaMemsetAsync(scratch, 0, sizeof(int32_t), st) != cudaSuccess) return TQ_ERR_CUDA;   // reported: clear
+    *out = v;
+    return TQ_OK;
 }
-#endif

@@ -12,25 +12,6 @@ constexpr int TILE_TOK = TILE_BLOCKS * TQ_BLOCK_TOKENS;  // 64
 constexpr int NSTAGE = 3;
 constexpr int RING_TOK = 32;  // ring tokens a ring CTA stages at a time
 
-#ifdef TQ_TRACE
-// Debug build only: per-CTA phase time stamps (ns) for latency analysis.
-static __device__ unsigned long long g_tq_trace[4096 * 16];   // two launches of up to 2048 CTAs, alternating
-static __device__ unsigned long long g_tq_trace_q[2 * 256 * 4];    // query-prep launches, same alternation
-__device__ __forceinline__ unsigned long long tq_now() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#define TQ_STAMP(i)                                                                                       \
-    do {                                                                                                  \
-        if (threadIdx.x == 0) {                                                                           \
-            const int cta = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);               \
-            if (cta < 2048) g_tq_trace[((p.trace_slot & 1) * 2048 + cta) * 16 + (i)] = tq_now();          \
-        }                                                                                                 \
-    } while (0)
-#else
-#define TQ_STAMP(i)
-#endif
 
 struct DecodeParams {
     const uint8_t* pool;
@@ -49,6 +30,7 @@ struct DecodeParams {
     const void* ring_v;
     int ring_dtype;
     const int32_t* ring_lens;
+    int max_ring_len;    // host upper bound of ring_lens (sizes the ring CTAs)
     int64_t ring_stride_seq, ring_stride_token;
     float scale, qjl_scale;
     TqCodebook cb;
@@ -58,10 +40,6 @@ struct DecodeParams {
     int32_t* status;
     int num_splits, ring_splits;
     int ring_tok;          // ring tokens per ring CTA, a multiple of RING_TOK
-#ifdef TQ_TRACE
-    int trace_slot;
-#endif
-    int frags_ready;       // the query fragments were written before this launch was enqueued (no query-prep grid ahead)
     uint32_t land_bytes;   // tensor-core kernel: shared memory in front of its barriers, reusable by the merge
 };
 
@@ -216,7 +194,6 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
     }
     __syncthreads();
     if (!s_last) return;
-    TQ_STAMP(7);
 
     const float* base = p.partials + (int64_t)(b * p.H + h) * nslot * PS;
     const uint32_t total = (uint32_t)nslot * PS * 4u;
@@ -233,10 +210,12 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
         __syncthreads();
         bool ok = tq_mbar_wait_bounded(&s_bar, 0u);
         if (!__syncthreads_and(ok)) {   // never arrived: report; the kernel must not touch `land` again
-            if (tid == 0) atomicCAS(p.status, 0, (int)TQ_ERR_TIMEOUT);
+            if (tid == 0) {
+                atomicCAS(p.status, 0, (int)TQ_ERR_TIMEOUT);
+                p.tickets[b * p.H + h] = 0;   // the output of this launch is lost, the workspace stays usable
+            }
             return;
         }
-        TQ_STAMP(13);
         // Out of shared memory: a thread owns four channels of one head; the head is the same for a whole
         // warp, so the warp works out the slots' weights once into its own row of `wsm` (padded with
         // zeros to a multiple of eight) and then takes the slots eight at a time, all loads first.
@@ -251,7 +230,6 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
             float mx = -INFINITY;
             for (int s = lane; s < nslot; s += 32) mx = fmaxf(mx, sb[s * PS + g]);
             mx = tq_warp_max(mx);
-            TQ_STAMP(14);
             float l = 0.f;
             for (int s = lane; s < wstride; s += 32) {
                 float wm = 0.f;
@@ -283,7 +261,6 @@ __device__ __forceinline__ void ticket_and_merge(const DecodeParams& p, int b, i
                 }
             }
             __syncwarp();   // the row of weights is rewritten by the warp's next pass
-            TQ_STAMP(15);
             const float inv = l > 0.f ? 1.f / l : 0.f;
             const int64_t dst = ((int64_t)b * p.Qh + h * p.G + g) * D + d;
             tq_store4_any(p.out, dst, o.x * inv, o.y * inv, o.z * inv, o.w * inv, p.q_dtype);
@@ -358,7 +335,11 @@ __device__ __forceinline__ void ring_part(const DecodeParams& p, int b, int h, i
     constexpr int MAX_OWN = (GP * D + 127) / 128;   // outputs per thread with at least 128 threads
     const int tid = threadIdx.x, nt = blockDim.x, warp = tid >> 5, lane = tid & 31;
     const int rs = slot_idx - p.num_splits;
-    const int R = p.ring_lens ? p.ring_lens[b] : 0;
+    int R = p.ring_lens ? p.ring_lens[b] : 0;
+    if (R > p.max_ring_len) {   // more than the host promised: the ring CTAs only cover max_ring_len tokens
+        if (tid == 0) atomicCAS(p.status, 0, (int)TQ_ERR_RANGE);
+        R = p.max_ring_len;
+    }
     float* mine = partial_ptr<D, GP>(p, b, h, slot_idx);
     // running state: ml[0..GP) max, ml[GP..2GP) sum (shared), acc of this thread's outputs (registers)
     float acc[MAX_OWN];

@@ -110,7 +110,6 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
     // order.  When this grid starts under the tail of the previous kernels, the CTAs that find their SM still
     // taken by the query preparation are then ring CTAs, which are off the critical path.
     const int b = blockIdx.z, h = blockIdx.x, x = blockIdx.y;
-    TQ_STAMP(0);
     // a kernel launched behind this one with programmatic stream serialisation may be scheduled as soon
     // as every CTA of this grid is running; whatever it reads of ours it reads after its own wait
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -123,25 +122,18 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
         uint8_t* kst = reinterpret_cast<uint8_t*>(scratch + D * GP + 2 * GP * RING_TOK);   // 16-byte aligned
         ring_part<D, GP>(p, b, h, x, scratch, scratch + D * GP, scratch + D * GP + GP * RING_TOK, ml, kst,
                          kst + RING_TOK * D * 4);
-        TQ_STAMP(5);
         ticket_and_merge<D, GP>(p, b, h, wsm, smem, p.land_bytes);
-        TQ_STAMP(6);
         return;
     }
 
     // ------------------------------ this CTA's share of the history ------------------------------
-    // Fragments that exist already are fetched ahead of everything else: behind the first burst of
-    // record copies they would arrive last and hold up every warp.
     constexpr uint32_t QF_BYTES = qf_words(D, SPLITB ? 8 : 4) * 4u;
-    if (p.frags_ready && tid == 0) {
-        tq_mbar_init(bars + NW * NSTW, 1);
-        tq_mbar_fence_init();
-        tq_mbar_expect_tx(bars + NW * NSTW, QF_BYTES);
-        tq_bulk_g2s(qf_s, p.qfrag + (int64_t)(b * p.H + h) * qf_words(D, SPLITB ? 8 : 4), QF_BYTES, bars + NW * NSTW);
-    }
     int n = p.seq_lens[b];
+    if (n > p.max_seq_len) {   // the host bound sized the grid, the block table and this CTA's table slice
+        if (tid == 0) atomicCAS(p.status, 0, (int)TQ_ERR_RANGE);
+        n = p.max_seq_len;
+    }
     if (n < p.min_history) n = 0;
-    TQ_STAMP(8);
     const uint32_t nblk = (uint32_t)(n + TQ_BLOCK_TOKENS - 1) / TQ_BLOCK_TOKENS;
     // 32-bit arithmetic: the launcher keeps num_splits * nblk below 2^31
     const int blk0 = (int)((uint32_t)x * nblk / (uint32_t)p.num_splits);
@@ -159,19 +151,20 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
         }
         bt_s[i] = phys;
     }
-    TQ_STAMP(9);
-    if (tid < NW * NSTW + (p.frags_ready ? 0 : 1)) {   // one barrier per thread
+    if (tid < NW * NSTW + 1) {   // one barrier per thread
         tq_mbar_init(bars + tid, 1);
         tq_mbar_fence_init();
     }
     __syncthreads();
-    TQ_STAMP(10);
     uint8_t* my_stage = stages + warp * NSTW * BB;
     uint64_t* my_bar = bars + warp * NSTW;
-    // The fragments of a query-prep grid still running ahead of this launch: thread 0 waits for that
-    // grid and asks for them before its own warp's records, so that they queue behind as few record
-    // copies as possible; the other warps start their copies at once.
-    if (!p.frags_ready && tid == 0) {
+    // The query fragments belong to the kernels ahead of this launch until they have completed: the
+    // query-prep grid of this call, or - when the caller says the query is already prepared - whatever
+    // earlier call prepared it, which may still be running when this grid starts (every kernel of the
+    // library lets its dependents start early).  Thread 0 waits for them and asks for the fragments
+    // before its own warp's records, so that they queue behind as few record copies as possible; the
+    // other warps start their copies at once.
+    if (tid == 0) {
         asm volatile("griddepcontrol.wait;" ::: "memory");
         tq_mbar_expect_tx(bars + NW * NSTW, QF_BYTES);
         tq_bulk_g2s(qf_s, p.qfrag + (int64_t)(b * p.H + h) * qf_words(D, SPLITB ? 8 : 4), QF_BYTES, bars + NW * NSTW);
@@ -185,11 +178,8 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
 
     // ---- query fragments, prepared once per (sequence, kv head) by the query-prep kernel ----
     // (launched with programmatic stream serialisation: everything above overlapped that kernel)
-    TQ_STAMP(1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    TQ_STAMP(2);
     bool failed = !__all_sync(0xffffffffu, tq_mbar_wait_bounded(bars + NW * NSTW, 0u));   // then no record is processed
-    TQ_STAMP(12);
     // Head_dim 256 with separate rotated / sketched sets: two sets of 32 fragment registers do not fit beside
     // the 64 value accumulators, so the fragments stay in shared memory and are read where they are used.
     constexpr bool BSM = (D == 256) && SPLITB;
@@ -214,7 +204,6 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
                 if (SPLITB) bsk[(SPLITB && !BSM) ? r : 0] = col_live ? qf[QF_HDR + (2 * KS + r) * 32 + lane] : 0u;
             }
         }
-        TQ_STAMP(11);
         // Sums of the fp16-rounded query over all dims (the constant terms of the bit-plane form), taken
         // with the score MMAs themselves: an A operand with every code (sign) bit set multiplies each
         // fragment entry by the power of two its position stands for, so the accumulator of column g is
@@ -289,7 +278,6 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
             t_hi1 |= (c >> 8) << (8 * i);
         }
     }
-    TQ_STAMP(3);
 
     for (int it = 0; it < cnt && !failed; ++it) {
         const int st = it % NSTW;
@@ -550,7 +538,6 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
         }
     }
     if (failed && lane == 0) atomicCAS(p.status, 0, (int)TQ_ERR_TIMEOUT);
-    if (warp == 0) TQ_STAMP(4);
 
     // ------------------------------ combine the warps of the CTA ------------------------------
 #pragma unroll
@@ -640,14 +627,11 @@ __global__ void __launch_bounds__(NW * 32, NW == NW_MULTI ? 2 : 1) tq_decode_mma
             }
         }
         if (single) {
-            TQ_STAMP(6);
             return;
         }
     }
     __syncthreads();   // wsm is reused by the merge
-    TQ_STAMP(5);
     ticket_and_merge<D, GP>(p, b, h, wsm, smem, p.land_bytes);
-    TQ_STAMP(6);
 }
 
 // Bytes in front of the barriers: stages, ml, bt_s, grown (one CTA per SM only) until the merge
@@ -670,16 +654,6 @@ size_t mma_smem_bytes(int block_bytes, int nslot) {
     return s;
 }
 
-int sm_count_cached() {
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0, n = 148;
-        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        sms = n;
-    }
-    return sms;
-}
-
 template <int D, int MSE_BITS, int VAL_BITS, bool SPLITB, int NW>
 int launch_mma_nw(const DecodeParams& p_in, int batch, cudaStream_t st) {
     DecodeParams p = p_in;
@@ -689,12 +663,8 @@ int launch_mma_nw(const DecodeParams& p_in, int batch, cudaStream_t st) {
     const size_t smem = mma_smem_bytes<D, SPLITB, NW>(L.block_bytes, nslot);
     p.land_bytes = (uint32_t)mma_land_bytes<D, SPLITB, NW>(L.block_bytes, nslot);
     auto kern = tq_decode_mma_kernel<D, MSE_BITS, VAL_BITS, SPLITB, NW>;
-    static size_t smem_set = 0;
-    if (smem > smem_set) {
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
-            return TQ_ERR_CUDA;
-        smem_set = smem;
-    }
+    static TqSmemOptIn opt_in;
+    if (tq_opt_in_smem(kern, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)p.H, (unsigned)nslot, (unsigned)batch);
     cfg.blockDim = dim3(NT);
@@ -720,7 +690,7 @@ int launch_mma(const DecodeParams& p, int batch, cudaStream_t st, int* handled) 
     const bool fits_multi = mma_smem_bytes<D, SPLITB, NW_MULTI>(L.block_bytes, nslot) <= SMEM_PER_CTA_MAX;
     *handled = 1;
     // two 8-warp CTAs per SM need two merge scratch areas in shared memory: only with few slots
-    if (fits_multi && ((ctas > sm_count_cached() && nslot <= 128) || !fits_wave))
+    if (fits_multi && ((ctas > tq_sm_count() && nslot <= 128) || !fits_wave))
         return launch_mma_nw<D, MSE_BITS, VAL_BITS, SPLITB, NW_MULTI>(p, batch, st);
     if (fits_wave) return launch_mma_nw<D, MSE_BITS, VAL_BITS, SPLITB, NW_WAVE>(p, batch, st);
     *handled = 0;
@@ -729,11 +699,6 @@ int launch_mma(const DecodeParams& p, int batch, cudaStream_t st, int* handled) 
 
 }  // namespace
 
-#ifdef TQ_TRACE
-extern "C" int tq_debug_read_trace(unsigned long long* out, int n) {
-    return cudaMemcpyFromSymbol(out, g_tq_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -5;
-}
-#endif
 
 namespace tqdec {
 

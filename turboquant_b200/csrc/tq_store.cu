@@ -274,13 +274,8 @@ __global__ void __launch_bounds__(NTHREADS) tq_store_f32_kernel(const StoreParam
 template <int D, int DT>
 int launch_f32(const StoreParams& p, int64_t n_tokens, int n_heads, cudaStream_t st) {
     const size_t smem = (size_t)(3 * D * LDT + 8 * TM + 4 * TM) * sizeof(float) + TM * sizeof(int64_t);
-    static bool smem_set = false;
-    if (!smem_set) {
-        if (cudaFuncSetAttribute(tq_store_f32_kernel<D, DT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)smem) != cudaSuccess)
-            return TQ_ERR_CUDA;
-        smem_set = true;
-    }
+    static TqSmemOptIn opt_in;
+    if (tq_opt_in_smem(tq_store_f32_kernel<D, DT>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;
     dim3 grid((unsigned)((n_tokens + TM - 1) / TM), (unsigned)n_heads);
     tq_store_f32_kernel<D, DT><<<grid, NTHREADS, smem, st>>>(p);
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;

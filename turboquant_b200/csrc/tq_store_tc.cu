@@ -50,20 +50,6 @@ struct TcParams {
 
 __device__ int g_tq_store_status;   // 0 or a tq_status left by a bounded wait that ran out
 
-#ifdef TQ_TRACE
-// Debug build only: phase time stamps (ns) of the first tiles of every CTA.
-__device__ unsigned long long g_tq_store_trace[256 * 4 * 8];
-#define TQ_SSTAMP(i)                                                                                              \
-    do {                                                                                                          \
-        if (threadIdx.x == 0 && blockIdx.x < 256 && tile_no < 4) {                                                \
-            unsigned long long t_;                                                                                \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                                                \
-            g_tq_store_trace[(blockIdx.x * 4 + tile_no) * 8 + (i)] = t_;                                          \
-        }                                                                                                         \
-    } while (0)
-#else
-#define TQ_SSTAMP(i)
-#endif
 
 __device__ __forceinline__ int core_off(int row, int k8) { return (row >> 3) * SBO + k8 * LBO + (row & 7) * 16; }
 
@@ -256,7 +242,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
 #pragma unroll 1
     for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
         ++tile_no;
-        TQ_SSTAMP(0);
         const int h = (int)(tile % p.H);
         const int64_t t0 = (tile / p.H) * TC_TOK;
         const int64_t tok = t0 + row;
@@ -307,7 +292,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
         tq_fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        TQ_SSTAMP(1);
         if (tid == 0) {
             tc_fence_after();
 #pragma unroll
@@ -324,7 +308,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
 
         // ---------------- values (group q of the row), while the tensor core works ----------------
         quantize_value_group<VAL_BITS>(vraw, rec, L, tl, q);
-        TQ_SSTAMP(2);
 
         {
             const bool ok = tq_mbar_wait_bounded(bars + 0, ph0);
@@ -335,7 +318,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
             }
         }
         tc_fence_after();
-        TQ_SSTAMP(3);
 
         // ---------------- codes and rotated-space residual of channels [32q, 32q+32) ----------------
         {
@@ -381,7 +363,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
         tq_fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        TQ_SSTAMP(4);
         if (tid == 0) {
             tc_fence_after();
 #pragma unroll
@@ -410,7 +391,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
             }
         }
         tc_fence_after();
-        TQ_SSTAMP(5);
 
         // ---------------- sign bits of channels [32q, 32q+32) (quantizer.py:214-222) ----------------
         {
@@ -424,7 +404,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
         tq_fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        TQ_SSTAMP(6);
 
         // ---------------- the tile's block records leave with one bulk store each ----------------
         if (tid < 8 && t0 + tid * TQ_BLOCK_TOKENS < p.n_tokens) {
@@ -439,7 +418,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
         }
         __syncthreads();
         tc_fence_after();
-        TQ_SSTAMP(7);
     }
     if (failed && tid == 0) atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_TIMEOUT);
     if (tid < 8) tq_bulk_wait_all();   // the records must have landed before the CTA retires
@@ -521,11 +499,6 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 
-#ifdef TQ_TRACE
-extern "C" int tq_debug_read_trace_store(unsigned long long* out, int n) {
-    return cudaMemcpyFromSymbol(out, g_tq_store_trace, sizeof(unsigned long long) * n) == cudaSuccess ? 0 : -5;
-}
-#endif
 
 // Status left by the tensor-core store kernel (0, or a tq_status if a bounded
 // wait ran out or a block index was out of range).  Synchronises the device.
