@@ -259,8 +259,8 @@ def test_paged_equals_flat_and_split_invariance(dev):
     """Random block tables and slot mappings; split count must not change the result."""
     from turboquant_b200 import _engine as E
     d, h, qh, n_seq = 128, 4, 16, 5
-    # one store kernel for both layouts (slot mappings always take the fp32 kernel), so bytes must be equal
-    c = E.LayerConstants(d, 3, 2, dev, seed=42, tensor_core_store=False)
+    # the tensor-core store kernel takes slot mappings and block tables alike, so bytes must be equal
+    c = E.LayerConstants(d, 3, 2, dev, seed=42, tensor_core_store=True)
     g = torch.Generator().manual_seed(3)
     lens = torch.randint(100, 900, (n_seq,), generator=g)
     nblk = [(int(x) + 15) // 16 for x in lens]
@@ -779,3 +779,74 @@ def test_host_io_paths_and_length_bounds(dev):
     E.check(_lib.lib().tq_workspace_init(ws.ptr, ws.nbytes, st), "tq_workspace_init")
     o_ok = E.decode(c, pool, ws, q.to(dev), bt.unsqueeze(0), lens, n, num_splits=3)
     assert ws.status() == 0 and torch.equal(o_big, o_ok)
+
+
+@pytest.mark.parametrize("kb,vb", [(3, 2), (4, 4), (3, 4)])
+def test_tensor_core_store_destinations(kb, vb, dev):
+    """The tcgen05 store kernel with every kind of destination: appends that start in the middle of a
+    block (the block's earlier tokens must survive), single-token appends, slot mappings (whole blocks
+    in order, shuffled slots, skipped tokens) and a head-major input layout.  Whatever the route, a
+    token's record bytes are the same as in one aligned whole-sequence call."""
+    from turboquant_b200 import _engine as E
+    d, h, n = 128, 4, 1000
+    c = E.LayerConstants(d, kb, vb, dev, seed=49)
+    k, v = O.synth_kv(n, h, d, seed=91, dtype=torch.bfloat16)
+    kd, vd = k.to(dev), v.to(dev)
+    nb = E.blocks_for(n)
+    g = torch.Generator().manual_seed(7)
+    bt = torch.randperm(nb + 5, generator=g)[:nb].int().to(dev)
+
+    def planes_of(pool, table):
+        ps = E.pool_to_planes(c, pool, table, n)
+        return [getattr(ps, f) for f in ("mse_indices", "qjl_signs", "norms", "residual_norms", "v_data", "v_scales", "v_zeros")]
+
+    base = E.BlockPool(c, h, nb + 5)
+    E.store(c, base, kd, vd, stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h, block_table=bt, start_pos=0)
+    want = planes_of(base, bt)
+    assert E.store_status() == 0
+
+    # ragged appends: every start offset inside a block occurs, chunks smaller and larger than a tile
+    pool = E.BlockPool(c, h, nb + 5)
+    pos = 0
+    for m in (5, 1, 10, 130, 1, 1, 17, 300, 128, 33, 64, 7, 1000):
+        m = min(m, n - pos)
+        if m <= 0:
+            break
+        E.store(c, pool, kd[pos:pos + m], vd[pos:pos + m], stride_token=h * d, stride_head=d, n_tokens=m, n_heads=h,
+                block_table=bt, start_pos=pos)
+        pos += m
+    assert pos == n and E.store_status() == 0
+    for a, b in zip(planes_of(pool, bt), want):
+        assert torch.equal(a, b)
+
+    # slot mapping in sequence order (whole blocks leave as records), in two calls split mid-block
+    pool = E.BlockPool(c, h, nb + 5)
+    p_ = torch.arange(n)
+    slots = (bt.cpu()[p_ // 16].long() * 16 + p_ % 16).to(dev)
+    for a, b in ((0, 391), (391, n)):
+        E.store(c, pool, kd[a:b], vd[a:b], stride_token=h * d, stride_head=d, n_tokens=b - a, n_heads=h,
+                slot_mapping=slots[a:b])
+    for a, b in zip(planes_of(pool, bt), want):
+        assert torch.equal(a, b)
+
+    # shuffled token order with some tokens skipped (slot -1): every stored token lands in its own slot
+    pool = E.BlockPool(c, h, nb + 5)
+    order = torch.randperm(n, generator=g)
+    skipped = order[:50]
+    sl = slots.cpu()[order].clone()
+    sl[:50] = -1
+    E.store(c, pool, kd[order.to(dev)], vd[order.to(dev)], stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h,
+            slot_mapping=sl.to(dev))
+    keep = torch.ones(n, dtype=torch.bool)
+    keep[skipped] = False
+    for a, b in zip(planes_of(pool, bt), want):
+        assert torch.equal(a[:, keep.to(dev)], b[:, keep.to(dev)])
+    assert E.store_status() == 0
+
+    # head-major input (heads, tokens, channels): token stride smaller than head stride
+    pool = E.BlockPool(c, h, nb + 5)
+    kh, vh = kd.transpose(0, 1).contiguous(), vd.transpose(0, 1).contiguous()
+    E.store(c, pool, kh, vh, stride_token=d, stride_head=n * d, n_tokens=n, n_heads=h, block_table=bt, start_pos=0)
+    for a, b in zip(planes_of(pool, bt), want):
+        assert torch.equal(a, b)
+    assert E.store_status() == 0

@@ -1,24 +1,34 @@
 // Store path on the 5th-generation tensor cores (tcgen05 + TMEM), head_dim 128,
-// bf16 input.  One persistent 512-thread CTA per SM; a tile is 128 tokens of one
-// kv head; four threads share a token row, each owning 32 channels from load to
-// packed output:
+// bf16 input.  One persistent 512-thread CTA per SM; a tile is 128 token
+// positions of one kv head; four threads share a token row, each owning 32
+// channels from load to packed output.
 //
-//   load row -> norm, normalise (bf16, as torch does) -> operand tiles in shared memory
-//   MMA 1 : Y = x_unit * Pi^T   (Pi as two bf16 limbs: exact-enough fp32 rotation)
-//           E = e * Pi_hi^T     (e = x - norm*x_unit, the normalisation's rounding error)
-//   read Y, E from TMEM -> bucket search + code packing; residual IN ROTATED SPACE
-//           r = norm*(Y - centroid[code]) + E   (the reference's x - x_hat, rotated: no
-//           un-rotation product); |r| is the residual norm; r as bf16 hi + lo limbs
-//   MMA 2 : P = r * M^T, M = S * Pi^T as two bf16 limbs (hi*hi + hi*lo + lo*hi)
-//   read P from TMEM -> sign bits
-//   values: per-group min/max quantisation by the same thread while MMA 1 runs
-//   the tile's eight 16-token block records are assembled in shared memory and
-//   leave with one bulk (TMA) store each.
+//   TMA (2 swizzled boxes)   : key rows and value rows of the tile -> shared memory
+//   N  norm, normalise       : u = bf16(x / |x|) exactly as torch does, e' = x/|x| - u (what the bf16
+//                              rounding lost); both written to TENSOR MEMORY as MMA A operands
+//   MMA 1 (A from TMEM)      : Y = u * Pi^T (Pi as two bf16 limbs), E = e' * Pi_hi^T
+//   V  values                : per-group min/max quantisation in packed bf16 arithmetic (under MMA 1)
+//   C  codes                 : bucket search on Y, code packing; residual IN ROTATED SPACE
+//                              r' = (Y - centroid[code]) + E  (the reference's x - x_hat, rotated and
+//                              divided by |x|: no un-rotation product); r' as bf16 hi + lo limbs -> TMEM
+//   MMA 2 (A from TMEM)      : P = r' * M^T, M = S * Pi^T as two bf16 limbs (hi*hi + hi*lo + lo*hi)
+//   S  sign bits of P; the tile's eight 16-token block records, assembled in shared memory, leave
+//      with one bulk (TMA) store each.
 //
-// Reference arithmetic: quantizer.py:129-149,231-257 and kv_cache.py:45-98.
-// Operand tiles use the no-swizzle K-major core-matrix layout (8 rows x 16 bytes
-// contiguous; LBO between the two K halves of an MMA step, SBO between 8-row
-// groups).  All waits on the MMA-completion mbarriers are bounded.
+// Two tiles are in flight: MMA 2 of tile t runs under the normalisation of tile t+1, MMA 1 of tile
+// t+1 under its value quantisation; the key / value boxes of the tile after that are already on
+// their way.  The constant operands (Pi_hi, Pi_lo, M_hi, M_lo: 128 KB) stay in shared memory; no A
+// operand ever touches it.  Tensor memory (512 columns): Y 128 | E, later P 128 | u 64 | e' 64 |
+// r'_hi 64 | r'_lo 64.
+//
+// Destinations: a block table with any start position (tiles are laid on the 16-token block grid;
+// a first block that already holds earlier tokens is read, completed and written back) or a slot
+// mapping (whole records where sixteen rows fill one block in order, byte scatter otherwise).
+//
+// Reference arithmetic: quantizer.py:129-149,231-257 and kv_cache.py:45-98.  Every wait on an
+// mbarrier is bounded; a timeout frees tensor memory and returns with a status.
+#include <cuda.h>
+
 #include "tq_common.cuh"
 
 namespace {
@@ -26,46 +36,62 @@ namespace {
 constexpr int TC_D = 128;
 constexpr int TC_TOK = 128;
 constexpr int TC_THREADS = 512;
-constexpr int TILE_BYTES = TC_TOK * TC_D * 2;   // one bf16 operand tile
-constexpr int LBO = 128;                        // bytes between core matrices along K
-constexpr int SBO = (TC_D / 8) * 128;           // bytes between 8-row groups
+constexpr int BOX_BYTES = TC_TOK * 128;          // one swizzled box: 128 rows x 128 bytes (64 bf16)
+constexpr int MAT_BYTES = 2 * BOX_BYTES;         // a 128 x 128 bf16 operand: two boxes (k 0-63, 64-127)
 constexpr int TMEM_COLS = 512;
-constexpr int REC_MAX = 2624;                   // largest block record at head_dim 128 (4-bit keys and values)
+constexpr size_t SMEM_LIMIT = 227 * 1024;
+
+// tensor-memory columns
+constexpr uint32_t COL_Y = 0, COL_E = 128, COL_U = 256, COL_EP = 320, COL_RH = 384, COL_RL = 448;
 
 struct TcParams {
-    const __nv_bfloat16* key;
-    const __nv_bfloat16* value;
-    int64_t n_tokens, stride_token, stride_head;
-    const int32_t* block_table;
-    int64_t start_block;   // start_pos / 16
+    int64_t n_tokens;
+    const int64_t* slot_mapping;   // destination of token i when given (negative: skip) ...
+    const int32_t* block_table;    // ... else position start_pos + i of this sequence
+    int64_t start_pos;
+    int lead;                      // start_pos & 15: rows of the first tile that precede token 0
     uint8_t* pool;
     int64_t num_blocks;
     int H;
-    const __nv_bfloat16* b_mat[4];   // Pi_hi, Pi_lo, M_hi, M_lo, each (128,128) row-major [n][k]
     TqCodebook cb;
-    int key_bits, val_bits;
     int64_t n_tiles;
-    int* status;
+    int n_rec_buf;                 // record images in shared memory (2 when they fit)
+    int tok_outer;                 // tensor-map dimension order: 1 = (channel, head, token), 0 = (channel, token, head)
 };
 
 __device__ int g_tq_store_status;   // 0 or a tq_status left by a bounded wait that ran out
 
+// ---------------------------------------------------------------------------
+// PTX wrappers
+// ---------------------------------------------------------------------------
 
-__device__ __forceinline__ int core_off(int row, int k8) { return (row >> 3) * SBO + k8 * LBO + (row & 7) * 16; }
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(tq_smem_u32(dst)), "l"(tm), "r"(x), "r"(y), "r"(tq_smem_u32(bar))
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* tm, int x, int y, int z, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+        ::"r"(tq_smem_u32(dst)), "l"(tm), "r"(x), "r"(y), "r"(z), "r"(tq_smem_u32(bar))
+        : "memory");
+}
 
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
-    // start address, leading/stride byte offsets in 16-byte units, descriptor version 1, no swizzle
-    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(LBO >> 4) << 16) | ((uint64_t)(SBO >> 4) << 32) |
-           (1ull << 46);
+// K-major operand tile written by a 128-byte-swizzled TMA box: rows of 128 bytes, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) |
+           (2ull << 61);
 }
 // kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, N = 128, M = 128
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a, uint64_t b, uint32_t accumulate) {
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(a), "l"(b), "r"(IDESC), "r"(accumulate)
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(IDESC), "r"(accumulate)
         : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
@@ -91,115 +117,140 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// 16 consecutive 32-bit columns (32 packed bf16 = one thread's channels of an A operand) of this thread's lane
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
 }
-// a / b for a caller that rounds the result to bf16 next: the product with the
-// reciprocal is within 2 ulp of the quotient, which can change the bf16 rounding
-// only next to a rounding tie (low half-word 0x8000); only there the exact
-// division runs.  Bit-identical to rounding __fdiv_rn(a, b), at a tenth of the cost.
-__device__ __forceinline__ float div_then_bf16(float a, float b, float rb) {
-    float q = a * rb;
-    if (((__float_as_uint(q) + 0x8004u) & 0xFFFFu) < 9u) q = __fdiv_rn(a, b);
-    return q;
-}
-// round two floats to bf16 with one conversion; returns the packed pair and the rounded values
-__device__ __forceinline__ uint32_t round_pair(float a, float b, float& ra, float& rb) {
-    const uint32_t pk = pack_bf16(a, b);
-    ra = __uint_as_float(pk << 16);
-    rb = __uint_as_float(pk & 0xffff0000u);
-    return pk;
-}
-__device__ __forceinline__ void unpack_bf16x8(const uint4& q, float (&f)[8]) {
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        f[2 * i] = __uint_as_float(w[i] << 16);
-        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-    }
+__device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t w) { return *reinterpret_cast<const __nv_bfloat162*>(&w); }
+__device__ __forceinline__ uint32_t as_u32(__nv_bfloat162 v) { return *reinterpret_cast<const uint32_t*>(&v); }
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// 16 bytes of row `row`, 16-byte chunk `chunk` (0..7) of a 128-byte-swizzled box
+__device__ __forceinline__ uint4 lds_sw128(const uint8_t* box, int row, int chunk) {
+    return *reinterpret_cast<const uint4*>(box + row * 128 + ((chunk ^ (row & 7)) << 4));
 }
 
-}  // namespace
+// Offset inside a block record of byte `cb` of token `tl`'s share (a token owns bytes_per_token bytes:
+// codes, signs, norm, residual norm, value codes, group scales, group zero points - in that order).
+__device__ __forceinline__ int rec_byte_offset(const TqLayout& L, int tl, int cb) {
+    if (cb < L.kcode_row) return L.off_kcodes + tl * L.kcode_row + cb;
+    cb -= L.kcode_row;
+    if (cb < L.ksign_row) return L.off_ksigns + tl * L.ksign_row + cb;
+    cb -= L.ksign_row;
+    if (cb < 2) return L.off_knorm + tl * 2 + cb;
+    cb -= 2;
+    if (cb < 2) return L.off_krnorm + tl * 2 + cb;
+    cb -= 2;
+    if (cb < L.vcode_row) return L.off_vcodes + tq_vcode_native(L.D, L.val_bits, tl, cb);
+    cb -= L.vcode_row;
+    if (cb < 2 * L.ngroups) return L.off_vscale + ((cb >> 1) * TQ_BLOCK_TOKENS + tl) * 2 + (cb & 1);
+    cb -= 2 * L.ngroups;
+    return L.off_vzero + ((cb >> 1) * TQ_BLOCK_TOKENS + tl) * 2 + (cb & 1);
+}
 
-namespace {
-
-// Asymmetric min/max quantisation of ONE 32-channel group of one value row in
-// bf16 arithmetic (kv_cache.py:64-90), from the four preloaded 16-byte pieces;
-// codes go to the record image in the decode kernel's byte order, scale / zero
-// point group-major.
+// ---------------------------------------------------------------------------
+// Values: asymmetric min/max quantisation of ONE 32-channel group of one row in
+// bf16 arithmetic (kv_cache.py:64-90), on packed pairs.
+//   v - zero        : one packed bf16 subtraction per pair (a single rounding, as torch's)
+//   (.) / scale     : both operands are bf16 numbers, so the quotient is either exactly representable
+//                     or at least 2^-17 (relative) away from every bf16 rounding boundary: the
+//                     product with the fp32 reciprocal rounds to the same bf16 as the division
+//   round, clamp    : adding 128 in bf16 (unit in the last place: 1) IS round-half-to-even of a value
+//                     in [0, 128); the code sits in the low mantissa bits
+// Codes go to the record image in the decode kernel's byte order, scale / zero point group-major.
+// ---------------------------------------------------------------------------
 template <int VAL_BITS>
 __device__ __forceinline__ void quantize_value_group(const uint4 (&raw)[4], uint8_t* rec, const TqLayout& L, int tl,
-                                                     int grp) {
+                                                     int grp, bool wr) {
     constexpr uint32_t N_LEVELS = (1u << VAL_BITS) - 1u;
-    const float min_scale = bf16r(1e-10f);
-    float v[32];
+    constexpr uint32_t FIELD = VAL_BITS == 2 ? 0x00030003u : 0x000f000fu;
+    const uint32_t w[16] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w,
+                            raw[2].x, raw[2].y, raw[2].z, raw[2].w, raw[3].x, raw[3].y, raw[3].z, raw[3].w};
+    __nv_bfloat162 mn = as_bf162(w[0]), mx = mn;
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-        float f[8];
-        unpack_bf16x8(raw[c], f);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[c * 8 + i] = f[i];
+    for (int i = 1; i < 16; ++i) {
+        mn = __hmin2(mn, as_bf162(w[i]));
+        mx = __hmax2(mx, as_bf162(w[i]));
     }
-    float vmin = v[0], vmax = v[0];
-#pragma unroll
-    for (int i = 1; i < 32; ++i) {
-        vmin = fminf(vmin, v[i]);
-        vmax = fmaxf(vmax, v[i]);
-    }
+    const float vmin = fminf(bf_lo(as_u32(mn)), bf_hi(as_u32(mn)));
+    const float vmax = fmaxf(bf_lo(as_u32(mx)), bf_hi(as_u32(mx)));
     float scale = bf16r(__fdiv_rn(bf16r(vmax - vmin), (float)N_LEVELS));
-    scale = fmaxf(scale, min_scale);
+    scale = fmaxf(scale, bf16r(1e-10f));
     const float rscale = __frcp_rn(scale);
+    const __nv_bfloat162 zero2 = __floats2bfloat162_rn(vmin, vmin);
+    const __nv_bfloat162 magic = __floats2bfloat162_rn(128.f, 128.f);
+    const __nv_bfloat162 top = __floats2bfloat162_rn((float)N_LEVELS, (float)N_LEVELS);
+    uint32_t code[16];   // code of the pair's elements in bits 0.. and 16..
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const uint32_t d = as_u32(__hsub2(as_bf162(w[i]), zero2));
+        const __nv_bfloat162 z = __hmin2(as_bf162(pack_bf16(bf_lo(d) * rscale, bf_hi(d) * rscale)), top);
+        code[i] = as_u32(__hadd2(z, magic)) & FIELD;
+    }
+    if (!wr) return;
     reinterpret_cast<__half*>(rec + L.off_vscale)[grp * TQ_BLOCK_TOKENS + tl] = __float2half_rn(scale);
     reinterpret_cast<__half*>(rec + L.off_vzero)[grp * TQ_BLOCK_TOKENS + tl] = __float2half_rn(vmin);
-    constexpr int PER_BYTE = 8 / VAL_BITS;
+    uint8_t* vc = rec + L.off_vcodes;
+    if (VAL_BITS == 2) {
 #pragma unroll
-    for (int bt = 0; bt < 32 / PER_BYTE; ++bt) {
-        uint32_t byte = 0;
-#pragma unroll
-        for (int e = 0; e < PER_BYTE; e += 2) {
-            float d0, d1, t0, t1;
-            round_pair(v[bt * PER_BYTE + e] - vmin, v[bt * PER_BYTE + e + 1] - vmin, d0, d1);   // (v - zero) in bf16
-            round_pair(div_then_bf16(d0, scale, rscale), div_then_bf16(d1, scale, rscale), t0, t1);   // / scale in bf16
-            // round half to even, clamp to [0, levels]; t >= 0 because zero = min
-            byte |= min(__float2uint_rn(t0), N_LEVELS) << (e * VAL_BITS);
-            byte |= min(__float2uint_rn(t1), N_LEVELS) << ((e + 1) * VAL_BITS);
+        for (int bt = 0; bt < 8; ++bt) {   // byte = four codes, LSB first (kv_cache.py:80-84)
+            const uint32_t t = code[2 * bt] | (code[2 * bt + 1] << 4);
+            vc[tq_vcode_native(TC_D, 2, tl, grp * 8 + bt)] = (uint8_t)(t | (t >> 14));
         }
-        rec[L.off_vcodes + tq_vcode_native(TC_D, VAL_BITS, tl, grp * (32 / PER_BYTE) + bt)] = (uint8_t)byte;
+    } else {
+#pragma unroll
+        for (int bt = 0; bt < 16; ++bt) {  // byte = two codes (kv_cache.py:86-90)
+            const uint32_t t = code[bt];
+            vc[tq_vcode_native(TC_D, 4, tl, grp * 16 + bt)] = (uint8_t)(t | (t >> 12));
+        }
     }
 }
 
-// 512 threads: thread (row = tid % 128, q = tid / 128) owns channels [32q, 32q+32) of
-// token row `row` - one TMEM chunk, one value group.  Warp w reads TMEM lanes of
-// quarter w % 4 = row / 32, as the hardware requires.
+// 512 threads: thread (row = tid % 128, q = tid / 128) owns channels [32q, 32q+32) of token row `row` -
+// one value group, 16 packed columns of an A operand, 32 accumulator columns.  Warp w reads and writes
+// TMEM lanes of quarter w % 4 = row / 32, as the hardware requires.
 template <int MSE_BITS, int VAL_BITS>
-__global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcParams p) {
+__global__ void __launch_bounds__(TC_THREADS, 1)
+tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                   const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
+                   const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_b3,
+                   const TcParams p) {
     const TqLayout L = tq_make_layout(TC_D, MSE_BITS + 1, VAL_BITS);
     const int BB = L.block_bytes;
+    const int IMG = 8 * BB;                           // one record image: the tile's 8 block records
     constexpr int N_CENT = 1 << MSE_BITS;
 
-    extern __shared__ __align__(1024) uint8_t smem[];
-    uint8_t* sB = smem;                               // Pi_hi, Pi_lo, M_hi, M_lo operand tiles
-    uint8_t* sA0 = smem + 4 * TILE_BYTES;             // x_unit, later r_hi
-    uint8_t* sA1 = sA0 + TILE_BYTES;                  // e, later r_lo
-    uint8_t* sRec = sA1 + TILE_BYTES;                 // image of the tile's 8 block records
-    float* s_part = reinterpret_cast<float*>(sRec + 8 * REC_MAX);   // [4][128] partial sums of squares
+    extern __shared__ uint8_t smem_raw[];
+    // swizzled boxes need a 1024-byte aligned base in the shared window
+    uint8_t* smem = smem_raw + ((1024u - (tq_smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* sB = smem;                               // Pi_hi, Pi_lo, M_hi, M_lo: 4 x (2 boxes)
+    uint8_t* sX = sB + 4 * MAT_BYTES;                 // key rows of the tile (2 boxes)
+    uint8_t* sV = sX + MAT_BYTES;                     // value rows of the tile (2 boxes)
+    uint8_t* sRec = sV + MAT_BYTES;                   // n_rec_buf record images
+    float* s_part = reinterpret_cast<float*>(sRec + p.n_rec_buf * IMG);   // [4][128] partial sums of squares
     uint64_t* bars = reinterpret_cast<uint64_t*>(s_part + 4 * TC_TOK);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2);
+    uint64_t *bar_b = bars, *bar_k = bars + 1, *bar_v = bars + 2, *bar_m1 = bars + 3, *bar_m2 = bars + 4,
+             *bar_r = bars + 5;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
 
-    const int tid = threadIdx.x, warp = tid >> 5;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int row = tid & (TC_TOK - 1), q = tid >> 7;
+    const int blk_l = row >> 4, tl = row & 15;
+    const bool slot_mode = p.slot_mapping != nullptr;
 
-    // constant operands, once per CTA, into the core-matrix layout
-#pragma unroll 1
-    for (int m = 0; m < 4; ++m)
-        for (int c = tid; c < TC_D * TC_D / 8; c += TC_THREADS) {
-            const int n = c >> 4, k8 = c & 15;
-            *reinterpret_cast<uint4*>(sB + m * TILE_BYTES + core_off(n, k8)) =
-                __ldg(reinterpret_cast<const uint4*>(p.b_mat[m] + n * TC_D + k8 * 8));
-        }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tq_smem_u32(tmem_slot)),
                      "r"(TMEM_COLS)
@@ -207,126 +258,192 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     if (tid == 0) {
-        tq_mbar_init(bars + 0, 1);
-        tq_mbar_init(bars + 1, 1);
+#pragma unroll
+        for (int i = 0; i < 6; ++i) tq_mbar_init(bars + i, 1);
         tq_mbar_fence_init();
     }
-    tq_fence_proxy_async();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_y = tmem, tmem_e = tmem + 128, tmem_p = tmem + 256;
     const uint32_t lane_base = (uint32_t)(row & ~31) << 16;   // this warp's quarter of the 128 TMEM lanes
-    const uint32_t aA0 = tq_smem_u32(sA0), aA1 = tq_smem_u32(sA1), aB = tq_smem_u32(sB);
 
-    uint32_t ph0 = 0, ph1 = 0;
-    bool failed = false;
-    const int blk_l = row >> 4, tl = row & 15;
-    uint8_t* rec = sRec + blk_l * BB;
-
-    // this thread's 32 key channels of the NEXT tile, fetched while the current tile finishes
-    uint4 knext[4];
-    auto fetch_keys = [&](int64_t tile_idx) {
-        const int hh = (int)(tile_idx % p.H);
-        const int64_t tk = (tile_idx / p.H) * TC_TOK + row;
-        const bool ok = tile_idx < p.n_tiles && tk < p.n_tokens;
-        const __nv_bfloat16* src = p.key + tk * p.stride_token + (int64_t)hh * p.stride_head + q * 32;
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-            knext[c] = ok ? __ldg(reinterpret_cast<const uint4*>(src + c * 8)) : make_uint4(0u, 0u, 0u, 0u);
+    // tile -> (kv head, first row's token index).  Tiles lie on the block grid of the destination
+    // sequence: row r of token tile tt is token i = 128 * tt + r - lead (lead > 0: the first block already
+    // holds `lead` earlier tokens); the boxes of rows outside [0, n_tokens) arrive as zeros.
+    auto tile_head = [&](int64_t tile) { return (int)(tile % p.H); };
+    auto tile_tok0 = [&](int64_t tile) { return (tile / p.H) * TC_TOK - p.lead; };
+    auto issue_kv = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int64_t tile) {
+        const int hh = tile_head(tile), t0 = (int)tile_tok0(tile);
+        tq_mbar_expect_tx(bar, 2 * BOX_BYTES);
+        tma_load_3d(dst, tm, 0, p.tok_outer ? hh : t0, p.tok_outer ? t0 : hh, bar);
+        tma_load_3d(dst + BOX_BYTES, tm, 64, p.tok_outer ? hh : t0, p.tok_outer ? t0 : hh, bar);
     };
-    fetch_keys(blockIdx.x);
 
-    int tile_no = -1;
-#pragma unroll 1
-    for (int64_t tile = blockIdx.x; tile < p.n_tiles; tile += gridDim.x) {
-        ++tile_no;
-        const int h = (int)(tile % p.H);
-        const int64_t t0 = (tile / p.H) * TC_TOK;
-        const int64_t tok = t0 + row;
-        const bool valid = tok < p.n_tokens;
+    const int64_t tile0 = blockIdx.x;   // the grid never exceeds the tile count
+    if (tid == 0) {
+        tq_mbar_expect_tx(bar_b, 4 * MAT_BYTES);
+        const CUtensorMap* tb[4] = {&tm_b0, &tm_b1, &tm_b2, &tm_b3};
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+            tma_load_2d(sB + m * MAT_BYTES, tb[m], 0, 0, bar_b);
+            tma_load_2d(sB + m * MAT_BYTES + BOX_BYTES, tb[m], 64, 0, bar_b);
+        }
+        issue_kv(sX, &tm_k, bar_k, tile0);
+        issue_kv(sV, &tm_v, bar_v, tile0);
+    }
 
-        // value channels of this tile: in flight while the keys are normalised
+    const uint32_t aB = tq_smem_u32(sB);
+    uint32_t ph_k = 0, ph_v = 0, ph_m1 = 0, ph_m2 = 0;
+    bool failed = false;
+    float nd = 0.f;        // |x| of this thread's row in the input dtype, from N to S of the same tile
+    float nd_next = 0.f;
+
+    // ---- N: key rows of a tile -> norm, u and e' in tensor memory (uniform result: false = timeout) ----
+    auto phase_n = [&](float& nd_out) -> bool {
+        const bool ok = tq_mbar_wait_bounded(bar_k, ph_k);
+        ph_k ^= 1;
+        uint32_t xw[16];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const uint4 v = lds_sw128(sX + (q >> 1) * BOX_BYTES, row, (q & 1) * 4 + c);
+            xw[4 * c] = v.x; xw[4 * c + 1] = v.y; xw[4 * c + 2] = v.z; xw[4 * c + 3] = v.w;
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float a = bf_lo(xw[i]), b = bf_hi(xw[i]);
+            ss = fmaf(a, a, ss);
+            ss = fmaf(b, b, ss);
+        }
+        s_part[q * TC_TOK + row] = ss;
+        if (__syncthreads_or(!ok)) return false;      // partial sums published; every thread has read its key row
+        ss = (s_part[row] + s_part[TC_TOK + row]) + (s_part[2 * TC_TOK + row] + s_part[3 * TC_TOK + row]);
+        const float n_d = bf16r(__fsqrt_rn(ss));               // quantizer.py:136, in the input dtype
+        const float den = bf16r(n_d + 1e-10f);                 // quantizer.py:138
+        const float rden = __frcp_rn(den);
+        uint32_t up[16], ep[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            // numerator and denominator are bf16 numbers: the product with the reciprocal rounds to
+            // the same bf16 as the division (see quantize_value_group)
+            const float q0 = bf_lo(xw[i]) * rden, q1 = bf_hi(xw[i]) * rden;
+            const uint32_t u = pack_bf16(q0, q1);
+            up[i] = u;
+            ep[i] = pack_bf16(q0 - bf_lo(u), q1 - bf_hi(u));   // what the bf16 normalisation lost
+        }
+        tmem_st16(tmem + lane_base + COL_U + q * 16, up);
+        tmem_st16(tmem + lane_base + COL_EP + q * 16, ep);
+        tmem_st_wait();
+        nd_out = n_d;
+        return true;
+    };
+    // issued by one thread once every thread's u / e' are in tensor memory
+    auto issue_mma1 = [&]() {
+        tc_fence_after();
+#pragma unroll
+        for (int m = 0; m < 2; ++m)
+#pragma unroll
+            for (int ks = 0; ks < TC_D / 16; ++ks)
+                umma_ts(tmem + COL_Y, tmem + COL_U + ks * 8,
+                        smem_desc_sw128(aB + m * MAT_BYTES + (ks >> 2) * BOX_BYTES + (ks & 3) * 32), (m | ks) != 0);
+#pragma unroll
+        for (int ks = 0; ks < TC_D / 16; ++ks)
+            umma_ts(tmem + COL_E, tmem + COL_EP + ks * 8,
+                    smem_desc_sw128(aB + (ks >> 2) * BOX_BYTES + (ks & 3) * 32), ks != 0);
+        umma_commit(bar_m1);
+    };
+    auto issue_mma2 = [&]() {
+        tc_fence_after();
+#pragma unroll
+        for (int m = 0; m < 3; ++m) {   // r_hi * M_hi + r_hi * M_lo + r_lo * M_hi
+            const uint32_t a_col = m == 2 ? COL_RL : COL_RH;
+            const uint32_t b_mat = m == 1 ? 3 : 2;
+#pragma unroll
+            for (int ks = 0; ks < TC_D / 16; ++ks)
+                umma_ts(tmem + COL_E, tmem + a_col + ks * 8,
+                        smem_desc_sw128(aB + b_mat * MAT_BYTES + (ks >> 2) * BOX_BYTES + (ks & 3) * 32), (m | ks) != 0);
+        }
+        umma_commit(bar_m2);
+    };
+    // V: value rows in shared memory -> codes, scales, zero points of one tile's record image
+    auto phase_v = [&](uint8_t* image, int64_t tok_first) -> bool {
+        const bool ok = tq_mbar_wait_bounded(bar_v, ph_v);
+        ph_v ^= 1;
         uint4 vraw[4];
-        {
-            const __nv_bfloat16* vseg = p.value + tok * p.stride_token + (int64_t)h * p.stride_head + q * 32;
 #pragma unroll
-            for (int c = 0; c < 4; ++c)
-                vraw[c] = valid ? __ldg(reinterpret_cast<const uint4*>(vseg + c * 8)) : make_uint4(0u, 0u, 0u, 0u);
-        }
+        for (int c = 0; c < 4; ++c) vraw[c] = lds_sw128(sV + (q >> 1) * BOX_BYTES, row, (q & 1) * 4 + c);
+        quantize_value_group<VAL_BITS>(vraw, image + blk_l * BB, L, tl, q, tok_first + row >= 0);
+        return !__syncthreads_or(!ok);                // every thread has read its value row
+    };
 
-        // ---------------- key row: norm, normalise, operand tiles ----------------
-        float nd;
-        {
-            float ss = 0.f;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float f[8];
-                unpack_bf16x8(knext[c], f);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) ss = fmaf(f[i], f[i], ss);
+    // ---- prologue: first tile's keys normalised ----
+    if (!phase_n(nd)) failed = true;
+
+    int tile_no = 0;
+#pragma unroll 1
+    for (int64_t tile = tile0; tile < p.n_tiles && !failed; tile += gridDim.x, ++tile_no) {
+        const int64_t next = tile + gridDim.x;
+        const bool has_next = next < p.n_tiles;
+        const int h = tile_head(tile);
+        const int64_t tok0 = tile_tok0(tile);
+        const bool wr = tok0 + row >= 0;                 // rows before token 0 belong to an earlier append
+        uint8_t* img = sRec + (p.n_rec_buf == 2 ? (tile_no & 1) : 0) * IMG;
+        uint8_t* rec = img + blk_l * BB;
+
+        if (tile_no == 0) {
+            // first tile of this CTA: its u / e' are in tensor memory; publish them, start MMA 1 and the
+            // next key load, fetch the block this append continues (if any), quantise its values
+            const bool b_ok = tid != 0 || tq_mbar_wait_bounded(bar_b, 0);   // constant operands (needed by the issuer)
+            tc_fence_before();
+            if (__syncthreads_or(!b_ok)) {
+                failed = true;
+                break;
             }
-            s_part[q * TC_TOK + row] = ss;
-            __syncthreads();
-            ss = (s_part[row] + s_part[TC_TOK + row]) + (s_part[2 * TC_TOK + row] + s_part[3 * TC_TOK + row]);
-            nd = bf16r(__fsqrt_rn(ss));              // quantizer.py:136, in the input dtype
-            const float den = bf16r(nd + 1e-10f);    // quantizer.py:138
-            const float rden = __frcp_rn(den);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                float f[8];
-                unpack_bf16x8(knext[c], f);
-                uint32_t up[4], ep[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    float u0, u1;
-                    up[i] = round_pair(div_then_bf16(f[2 * i], den, rden), div_then_bf16(f[2 * i + 1], den, rden), u0, u1);
-                    // what the bf16 normalisation lost, exact in fp32
-                    ep[i] = pack_bf16(fmaf(-nd, u0, f[2 * i]), fmaf(-nd, u1, f[2 * i + 1]));
+            if (tid == 0) {
+                issue_mma1();
+                if (has_next) issue_kv(sX, &tm_k, bar_k, next);
+            }
+            if (!slot_mode && p.lead != 0 && tile < p.H) {
+                // the first block of this append already holds `lead` tokens of the sequence: complete it
+                if (tid == 0) {
+                    const int64_t phys = p.block_table[p.start_pos >> 4];
+                    if (phys >= 0 && phys < p.num_blocks) {
+                        tq_mbar_expect_tx(bar_r, (uint32_t)BB);
+                        tq_bulk_g2s(img, p.pool + (phys * p.H + h) * (int64_t)BB, (uint32_t)BB, bar_r);
+                    } else {
+                        atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_RANGE);
+                        tq_mbar_expect_tx(bar_r, 0);   // completes the phase: nobody waits for bytes
+                    }
                 }
-                *reinterpret_cast<uint4*>(sA0 + core_off(row, q * 4 + c)) = make_uint4(up[0], up[1], up[2], up[3]);
-                *reinterpret_cast<uint4*>(sA1 + core_off(row, q * 4 + c)) = make_uint4(ep[0], ep[1], ep[2], ep[3]);
+                const bool ok = tq_mbar_wait_bounded(bar_r, 0);
+                if (__syncthreads_or(!ok)) {
+                    failed = true;
+                    break;
+                }
             }
-        }
-        tq_fence_proxy_async();
-        tc_fence_before();
-        __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < TC_D / 16; ++ks)
-                umma(tmem_y, smem_desc(aA0 + ks * 2 * LBO), smem_desc(aB + 0 * TILE_BYTES + ks * 2 * LBO), ks > 0);
-#pragma unroll
-            for (int ks = 0; ks < TC_D / 16; ++ks)
-                umma(tmem_y, smem_desc(aA0 + ks * 2 * LBO), smem_desc(aB + 1 * TILE_BYTES + ks * 2 * LBO), 1);
-#pragma unroll
-            for (int ks = 0; ks < TC_D / 16; ++ks)
-                umma(tmem_e, smem_desc(aA1 + ks * 2 * LBO), smem_desc(aB + 0 * TILE_BYTES + ks * 2 * LBO), ks > 0);
-            umma_commit(bars + 0);
+            if (!phase_v(img, tok0)) {
+                failed = true;
+                break;
+            }
+            if (tid == 0 && has_next) issue_kv(sV, &tm_v, bar_v, next);
         }
 
-        // ---------------- values (group q of the row), while the tensor core works ----------------
-        quantize_value_group<VAL_BITS>(vraw, rec, L, tl, q);
-
+        // ---------------- C: codes and rotated-space residual of channels [32q, 32q+32) ----------------
         {
-            const bool ok = tq_mbar_wait_bounded(bars + 0, ph0);
-            ph0 ^= 1;
+            const bool ok = tq_mbar_wait_bounded(bar_m1, ph_m1);
+            ph_m1 ^= 1;
             if (__syncthreads_or(!ok)) {
                 failed = true;
                 break;
             }
         }
         tc_fence_after();
-
-        // ---------------- codes and rotated-space residual of channels [32q, 32q+32) ----------------
         {
-            float y[32], er[32];
-            tmem_ld32(tmem_y + lane_base + q * 32, y);
-            tmem_ld32(tmem_e + lane_base + q * 32, er);
-            uint32_t* kc = reinterpret_cast<uint32_t*>(rec + L.off_kcodes + tl * L.kcode_row);
+            float y[32];
+            tmem_ld32(tmem + lane_base + COL_Y + q * 32, y);
             constexpr int WIDTH = MSE_BITS == 2 ? 2 : 4, PER_WORD = 32 / WIDTH;
-            float rn2 = 0.f;
+            uint32_t words[32 / PER_WORD];
 #pragma unroll
             for (int w = 0; w < 32 / PER_WORD; ++w) {
                 uint32_t word = 0;
@@ -334,93 +451,150 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
                 for (int jj = 0; jj < PER_WORD; ++jj) {
                     const int j = w * PER_WORD + jj;
                     uint32_t k = 0;
+                    float c = p.cb.centroids[0];
 #pragma unroll
-                    for (int bnd = 0; bnd < N_CENT - 1; ++bnd) k += (p.cb.boundaries[bnd] < y[j]) ? 1u : 0u;
-                    if (y[j] != y[j]) k = N_CENT - 1;
+                    for (int bnd = 0; bnd < N_CENT - 1; ++bnd) {
+                        const bool above = !(y[j] <= p.cb.boundaries[bnd]);   // searchsorted; NaN sorts last
+                        k += above ? 1u : 0u;
+                        c = above ? p.cb.centroids[bnd + 1] : c;
+                    }
                     word |= k << (WIDTH * jj);       // quantizer.py:50-68
-                    const float r = fmaf(nd, y[j] - p.cb.centroids[k], er[j]);
-                    rn2 = fmaf(r, r, rn2);
-                    y[j] = r;
+                    y[j] -= c;
                 }
-                kc[q * (32 / PER_WORD) + w] = word;
+                words[w] = word;
             }
+            if (wr) {
+                uint32_t* kc = reinterpret_cast<uint32_t*>(rec + L.off_kcodes + tl * L.kcode_row) + q * (32 / PER_WORD);
+#pragma unroll
+                for (int w = 0; w < 32 / PER_WORD; ++w) kc[w] = words[w];
+            }
+            float er[32];
+            tmem_ld32(tmem + lane_base + COL_E + q * 32, er);
+            float rn2 = 0.f;
+            uint32_t hi[16], lo[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const float a = y[2 * i] + er[2 * i], b = y[2 * i + 1] + er[2 * i + 1];   // r' = (Y - c) + E
+                rn2 = fmaf(a, a, rn2);
+                rn2 = fmaf(b, b, rn2);
+                const uint32_t hh = pack_bf16(a, b);
+                hi[i] = hh;
+                lo[i] = pack_bf16(a - bf_lo(hh), b - bf_hi(hh));
+            }
+            tmem_st16(tmem + lane_base + COL_RH + q * 16, hi);
+            tmem_st16(tmem + lane_base + COL_RL + q * 16, lo);
             s_part[q * TC_TOK + row] = rn2;
-            // residual as bf16 hi + lo limbs -> operand tiles of the QJL product
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t hi[4], lo[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float a = y[c * 8 + 2 * i], b = y[c * 8 + 2 * i + 1];
-                    float ah, bh;
-                    hi[i] = round_pair(a, b, ah, bh);
-                    lo[i] = pack_bf16(a - ah, b - bh);
-                }
-                *reinterpret_cast<uint4*>(sA0 + core_off(row, q * 4 + c)) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                *reinterpret_cast<uint4*>(sA1 + core_off(row, q * 4 + c)) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-            }
+            tmem_st_wait();
         }
-        tq_fence_proxy_async();
         tc_fence_before();
         __syncthreads();
-        if (tid == 0) {
-            tc_fence_after();
-#pragma unroll
-            for (int ks = 0; ks < TC_D / 16; ++ks)
-                umma(tmem_p, smem_desc(aA0 + ks * 2 * LBO), smem_desc(aB + 2 * TILE_BYTES + ks * 2 * LBO), ks > 0);
-#pragma unroll
-            for (int ks = 0; ks < TC_D / 16; ++ks)
-                umma(tmem_p, smem_desc(aA0 + ks * 2 * LBO), smem_desc(aB + 3 * TILE_BYTES + ks * 2 * LBO), 1);
-#pragma unroll
-            for (int ks = 0; ks < TC_D / 16; ++ks)
-                umma(tmem_p, smem_desc(aA1 + ks * 2 * LBO), smem_desc(aB + 2 * TILE_BYTES + ks * 2 * LBO), 1);
-            umma_commit(bars + 1);
-        }
-        fetch_keys(tile + gridDim.x);
-        if (q == 0) {   // norms of the row (partials were published before the barrier above)
+        if (tid == 0) issue_mma2();
+        if (q == 0 && wr) {   // norms of the row (partials were published before the barrier above)
             const float rn2 = (s_part[row] + s_part[TC_TOK + row]) + (s_part[2 * TC_TOK + row] + s_part[3 * TC_TOK + row]);
             reinterpret_cast<__half*>(rec + L.off_knorm)[tl] = __float2half_rn(nd);
-            reinterpret_cast<__half*>(rec + L.off_krnorm)[tl] = __float2half_rn(__fsqrt_rn(rn2));
+            // |r| = |x| * |r'| (the reference's residual x - x_hat, quantizer.py:244-245)
+            reinterpret_cast<__half*>(rec + L.off_krnorm)[tl] = __float2half_rn(nd * __fsqrt_rn(rn2));
         }
+        // the other record image is written next (values of the following tile): the records it held must have left
+        if (lane == 0 && warp < 8 && p.n_rec_buf == 2) tq_bulk_wait_all_read();
+        __syncthreads();   // also: s_part is reused by N below
+
+        // ---------------- N of the next tile, under MMA 2 ----------------
+        if (has_next && !phase_n(nd_next)) {
+            failed = true;
+            break;
+        }
+
+        // ---------------- S: sign bits of channels [32q, 32q+32) (quantizer.py:214-222) ----------------
         {
-            const bool ok = tq_mbar_wait_bounded(bars + 1, ph1);
-            ph1 ^= 1;
+            const bool ok = tq_mbar_wait_bounded(bar_m2, ph_m2);
+            ph_m2 ^= 1;
             if (__syncthreads_or(!ok)) {
                 failed = true;
                 break;
             }
         }
         tc_fence_after();
-
-        // ---------------- sign bits of channels [32q, 32q+32) (quantizer.py:214-222) ----------------
         {
             float pr[32];
-            tmem_ld32(tmem_p + lane_base + q * 32, pr);
+            tmem_ld32(tmem + lane_base + COL_E + q * 32, pr);
             uint32_t w = 0;
 #pragma unroll
             for (int j = 0; j < 32; ++j) w |= (pr[j] > 0.f ? 1u : 0u) << j;
-            reinterpret_cast<uint32_t*>(rec + L.off_ksigns + tl * L.ksign_row)[q] = w;
+            if (nd == 0.f) w = 0;   // x = 0: the reference's residual is exactly 0, r' is not
+            if (wr) reinterpret_cast<uint32_t*>(rec + L.off_ksigns + tl * L.ksign_row)[q] = w;
         }
         tq_fence_proxy_async();
         tc_fence_before();
-        __syncthreads();
+        __syncthreads();   // record image complete; P has been read: its columns may take the next E
 
-        // ---------------- the tile's block records leave with one bulk store each ----------------
-        if (tid < 8 && t0 + tid * TQ_BLOCK_TOKENS < p.n_tokens) {
-            const int64_t phys = p.block_table[p.start_block + (t0 >> 4) + tid];
-            if (phys >= 0 && phys < p.num_blocks) {
-                tq_bulk_s2g(p.pool + (phys * p.H + h) * (int64_t)BB, sRec + tid * BB, (uint32_t)BB);
-                tq_bulk_commit();
-                tq_bulk_wait_all_read();
-            } else {
-                atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_RANGE);
-            }
+        if (tid == 0 && has_next) {
+            issue_mma1();
+            if (next + gridDim.x < p.n_tiles) issue_kv(sX, &tm_k, bar_k, next + gridDim.x);
         }
-        __syncthreads();
-        tc_fence_after();
+
+        // ---------------- the tile's block records leave ----------------
+        if (warp < 8) {
+            const int j = warp;                                   // image block
+            if (!slot_mode) {
+                if (lane == 0) {
+                    const int64_t first = tok0 + j * TQ_BLOCK_TOKENS;     // token index of the block's first row
+                    if (first < p.n_tokens && first + TQ_BLOCK_TOKENS > 0) {
+                        const int64_t phys = p.block_table[(p.start_pos + first) >> 4];
+                        if (phys >= 0 && phys < p.num_blocks) {
+                            tq_bulk_s2g(p.pool + (phys * p.H + h) * (int64_t)BB, img + j * BB, (uint32_t)BB);
+                            tq_bulk_commit();
+                        } else {
+                            atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_RANGE);
+                        }
+                    }
+                }
+            } else {
+                // slot mapping: sixteen rows that fill one block in order leave as a whole record, anything
+                // else is scattered byte by byte to each token's own slot
+                const int64_t i = tok0 + j * TQ_BLOCK_TOKENS + (lane & 15);
+                int64_t slot = (i >= 0 && i < p.n_tokens) ? p.slot_mapping[i] : -1;
+                if (slot >= 0 && (slot >> 4) >= p.num_blocks) {
+                    atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_RANGE);
+                    slot = -1;
+                }
+                const int64_t slot0 = __shfl_sync(0xffffffffu, slot, 0);
+                const bool whole =
+                    __all_sync(0xffffffffu, slot0 >= 0 && (slot0 & 15) == 0 && slot == slot0 + (lane & 15));
+                if (whole) {
+                    if (lane == 0) {
+                        tq_bulk_s2g(p.pool + ((slot0 >> 4) * p.H + h) * (int64_t)BB, img + j * BB, (uint32_t)BB);
+                        tq_bulk_commit();
+                    }
+                } else {
+                    const int per_tok = BB / TQ_BLOCK_TOKENS;
+                    const uint8_t* src = img + j * BB;
+                    for (int t = 0; t < TQ_BLOCK_TOKENS; ++t) {
+                        const int64_t s = __shfl_sync(0xffffffffu, slot, t);
+                        if (s < 0) continue;
+                        uint8_t* dst = p.pool + ((s >> 4) * p.H + h) * (int64_t)BB;
+                        for (int cb = lane; cb < per_tok; cb += 32)
+                            dst[rec_byte_offset(L, (int)(s & 15), cb)] = src[rec_byte_offset(L, t, cb)];
+                    }
+                }
+            }
+            if (lane == 0 && p.n_rec_buf == 1) tq_bulk_wait_all_read();
+        }
+        if (p.n_rec_buf == 1) __syncthreads();   // the single image is rewritten by the values below
+
+        // ---------------- V of the next tile, under MMA 1 ----------------
+        if (has_next) {
+            uint8_t* nimg = sRec + (p.n_rec_buf == 2 ? ((tile_no + 1) & 1) : 0) * IMG;
+            if (!phase_v(nimg, tile_tok0(next))) {
+                failed = true;
+                break;
+            }
+            if (tid == 0 && next + gridDim.x < p.n_tiles) issue_kv(sV, &tm_v, bar_v, next + gridDim.x);
+        }
+        nd = nd_next;
     }
     if (failed && tid == 0) atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_TIMEOUT);
-    if (tid < 8) tq_bulk_wait_all();   // the records must have landed before the CTA retires
+    if (lane == 0 && warp < 8) tq_bulk_wait_all();   // the records must have landed before the CTA retires
 
     tc_fence_before();
     __syncthreads();
@@ -428,68 +602,111 @@ __global__ void __launch_bounds__(TC_THREADS, 1) tq_store_tc_kernel(const TcPara
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
 }
 
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+    return fn;
+}
+
+// (128 x 128) bf16 matrix, row pitch 256 bytes: boxes of 64 columns x 128 rows, 128-byte swizzle
+bool make_matrix_map(CUtensorMap* tm, const void* base) {
+    const cuuint64_t dims[2] = {TC_D, TC_D};
+    const cuuint64_t strides[1] = {TC_D * 2};
+    const cuuint32_t box[2] = {64, TC_TOK};
+    const cuuint32_t estr[2] = {1, 1};
+    return encode_tiled_fn()(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// (tokens, heads, 128) bf16 with element strides: boxes of 64 channels x 128 tokens of one head; the
+// dimension with the larger stride goes last
+bool make_rows_map(CUtensorMap* tm, const void* base, int64_t n_tokens, int n_heads, int64_t stride_token,
+                   int64_t stride_head, bool tok_outer) {
+    cuuint64_t dims[3] = {TC_D, (cuuint64_t)n_heads, (cuuint64_t)n_tokens};
+    cuuint64_t strides[2] = {(cuuint64_t)stride_head * 2, (cuuint64_t)stride_token * 2};
+    cuuint32_t box[3] = {64, 1, TC_TOK};
+    if (!tok_outer) {
+        dims[1] = (cuuint64_t)n_tokens; dims[2] = (cuuint64_t)n_heads;
+        strides[0] = (cuuint64_t)stride_token * 2; strides[1] = (cuuint64_t)stride_head * 2;
+        box[1] = TC_TOK; box[2] = 1;
+    }
+    const cuuint32_t estr[3] = {1, 1, 1};
+    return encode_tiled_fn()(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
-// Launches the tensor-core kernel when the call fits it: head_dim 128, bf16,
-// destination given as (block table, start position) with the start on a block
-// boundary, 16-byte aligned rows, and the split operands present.  Otherwise
-// *handled stays 0 and tq_store runs its fp32 kernel.
+// Launches the tensor-core kernel when the call fits it: head_dim 128, bf16, 16-byte aligned rows, the
+// split operands present.  Otherwise *handled stays 0 and tq_store runs its fp32 kernel.
 int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* value, tq_dtype dtype, int64_t n_tokens,
                        int32_t n_heads, int64_t stride_token, int64_t stride_head, const int64_t* slot_mapping,
                        const int32_t* block_table, int64_t start_pos, const tq_pool* pool, cudaStream_t st,
                        int* handled) {
     *handled = 0;
     const tq_config& cfg = consts->cfg;
-    if (cfg.head_dim != TC_D || dtype != TQ_BF16 || slot_mapping != nullptr || block_table == nullptr) return TQ_OK;
-    if ((start_pos & 15) != 0) return TQ_OK;
+    if (cfg.head_dim != TC_D || dtype != TQ_BF16) return TQ_OK;
     if (!consts->pi_limbs[0] || !consts->pi_limbs[1] || !consts->m_limbs[0] || !consts->m_limbs[1]) return TQ_OK;
     if (((uintptr_t)key & 15) || ((uintptr_t)value & 15) || (stride_token & 7) || (stride_head & 7)) return TQ_OK;
-    *handled = 1;
+    if (stride_token < TC_D || (n_heads > 1 && stride_head < TC_D)) return TQ_OK;
+    if (n_heads == 1) stride_head = stride_token > TC_D ? TC_D : stride_token;   // never dereferenced; keep the map well formed
+    for (int i = 0; i < 2; ++i)
+        if (((uintptr_t)consts->pi_limbs[i] & 15) || ((uintptr_t)consts->m_limbs[i] & 15)) return TQ_OK;
+    if (n_tokens >= ((int64_t)1 << 31) - 256) return TQ_OK;   // 32-bit box coordinates
+    if (encode_tiled_fn() == nullptr) return TQ_OK;
 
     TcParams p;
-    p.key = (const __nv_bfloat16*)key;
-    p.value = (const __nv_bfloat16*)value;
     p.n_tokens = n_tokens;
-    p.stride_token = stride_token;
-    p.stride_head = stride_head;
+    p.slot_mapping = slot_mapping;
     p.block_table = block_table;
-    p.start_block = start_pos >> 4;
+    p.start_pos = slot_mapping ? 0 : start_pos;
+    p.lead = slot_mapping ? 0 : (int)(start_pos & 15);
     p.pool = (uint8_t*)pool->base;
     p.num_blocks = pool->num_blocks;
     p.H = n_heads;
-    p.b_mat[0] = (const __nv_bfloat16*)consts->pi_limbs[0];
-    p.b_mat[1] = (const __nv_bfloat16*)consts->pi_limbs[1];
-    p.b_mat[2] = (const __nv_bfloat16*)consts->m_limbs[0];
-    p.b_mat[3] = (const __nv_bfloat16*)consts->m_limbs[1];
+    p.tok_outer = stride_token >= stride_head ? 1 : 0;
     for (int i = 0; i < TQ_MAX_CENTROIDS; ++i) {
         p.cb.centroids[i] = consts->centroids[i];
         p.cb.boundaries[i] = consts->boundaries[i];
     }
-    p.key_bits = cfg.key_bits;
-    p.val_bits = cfg.value_bits;
-    p.n_tiles = ((n_tokens + TC_TOK - 1) / TC_TOK) * n_heads;
-    p.status = nullptr;
+    p.n_tiles = ((p.lead + n_tokens + TC_TOK - 1) / TC_TOK) * n_heads;
 
-    static int sms = 0;
-    if (sms == 0) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-            sms = 148;
-    }
-    const size_t smem = (size_t)6 * TILE_BYTES + 8 * REC_MAX + 4 * TC_TOK * sizeof(float) + 2 * sizeof(uint64_t) + 16;
-    const unsigned grid = (unsigned)(p.n_tiles < sms ? p.n_tiles : sms);
+    CUtensorMap tm_k, tm_v, tm_b[4];
+    if (!make_rows_map(&tm_k, key, n_tokens, n_heads, stride_token, stride_head, p.tok_outer != 0) ||
+        !make_rows_map(&tm_v, value, n_tokens, n_heads, stride_token, stride_head, p.tok_outer != 0) ||
+        !make_matrix_map(&tm_b[0], consts->pi_limbs[0]) || !make_matrix_map(&tm_b[1], consts->pi_limbs[1]) ||
+        !make_matrix_map(&tm_b[2], consts->m_limbs[0]) || !make_matrix_map(&tm_b[3], consts->m_limbs[1]))
+        return TQ_OK;   // a stride pattern the tensor map cannot express: the fp32 kernel takes the call
+    *handled = 1;
+
     const int mse_bits = cfg.key_bits - 1;
+    const TqLayout L = tq_make_layout(TC_D, cfg.key_bits, cfg.value_bits);
+    const size_t img = (size_t)8 * L.block_bytes;
+    const size_t fixed = (size_t)6 * MAT_BYTES + 4 * TC_TOK * sizeof(float) + 6 * sizeof(uint64_t) + 16 + 1024;
+    p.n_rec_buf = fixed + 2 * img <= SMEM_LIMIT ? 2 : 1;
+    const size_t smem = fixed + (size_t)p.n_rec_buf * img;
+    const int sms = tq_sm_count();
+    const unsigned grid = (unsigned)(p.n_tiles < sms ? p.n_tiles : sms);
 #define TQ_TC(MB, VB)                                                                                            \
     do {                                                                                                         \
-        static bool attr_set = false;                                                                            \
-        if (!attr_set) {                                                                                         \
-            if (cudaFuncSetAttribute(tq_store_tc_kernel<MB, VB>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
-                                     (int)smem) != cudaSuccess)                                                  \
-                return TQ_ERR_CUDA;                                                                              \
-            attr_set = true;                                                                                     \
-        }                                                                                                        \
-        tq_store_tc_kernel<MB, VB><<<grid, TC_THREADS, smem, st>>>(p);                                           \
+        static TqSmemOptIn opt_in;                                                                               \
+        if (tq_opt_in_smem(tq_store_tc_kernel<MB, VB>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;               \
+        tq_store_tc_kernel<MB, VB><<<grid, TC_THREADS, smem, st>>>(tm_k, tm_v, tm_b[0], tm_b[1], tm_b[2], tm_b[3], p); \
     } while (0)
     if (mse_bits == 2 && cfg.value_bits == 2) TQ_TC(2, 2);
     else if (mse_bits == 2) TQ_TC(2, 4);
@@ -498,7 +715,6 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
 #undef TQ_TC
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
-
 
 // Status left by the tensor-core store kernel (0, or a tq_status if a bounded
 // wait ran out or a block index was out of range).  Synchronises the device.
