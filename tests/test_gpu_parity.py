@@ -850,3 +850,42 @@ def test_tensor_core_store_destinations(kb, vb, dev):
     for a, b in zip(planes_of(pool, bt), want):
         assert torch.equal(a, b)
     assert E.store_status() == 0
+
+
+@pytest.mark.parametrize("d,h,qh,kb,vb", [(128, 8, 32, 4, 4), (128, 8, 32, 3, 2), (256, 2, 2, 4, 2), (256, 4, 24, 3, 2),
+                                          (128, 2, 16, 4, 2)])
+def test_decode_stays_inside_its_workspace(d, h, qh, kb, vb, dev):
+    """tq_decode given EXACTLY the bytes tq_decode_workspace_bytes asks for, with a guard pattern behind
+    them: both kernels, with and without a ring, must leave the guard alone (3-bit codes make the
+    tensor-core kernel pad a kv head's query heads to eight, which the size has to cover)."""
+    import ctypes as C
+    from turboquant_b200 import _engine as E, _lib
+    n, ring, splits = 1500, 100, 9
+    c = E.LayerConstants(d, kb, vb, dev, seed=3)
+    k, v = O.synth_kv(n + ring, h, d, seed=77, dtype=torch.bfloat16)
+    pool = E.BlockPool(c, h, E.blocks_for(n))
+    bt = E.identity_block_table(pool.num_blocks, dev)
+    E.store(c, pool, k[:n].to(dev), v[:n].to(dev), stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h,
+            block_table=bt, start_pos=0)
+    need = C.c_size_t(0)
+    E.check(_lib.lib().tq_decode_workspace_bytes(C.byref(c.cfg), 2, qh, h, splits, C.byref(need)), "ws bytes")
+    guard = 1 << 16
+    buf = torch.zeros(need.value + guard, dtype=torch.uint8, device=dev)
+    buf[need.value:] = 0xA5
+    ws = E.Workspace(dev)
+    ws.buf = buf[: need.value]                       # the library sees only what it asked for
+    q = O.synth_query(2, qh, d, seed=6, dtype=torch.bfloat16).to(dev)
+    lens = torch.tensor([n, n - 333], dtype=torch.int32, device=dev)
+    bt2 = bt.unsqueeze(0).expand(2, -1).contiguous()
+    rk, rv = k[n:].to(dev).contiguous(), v[n:].to(dev).contiguous()
+    rl = torch.tensor([ring, 40], dtype=torch.int32, device=dev)
+    outs = []
+    for kernel in (0, 1):
+        for with_ring in (False, True):
+            kw = dict(ring_k=rk, ring_v=rv, ring_lens=rl, max_ring_len=ring, ring_stride_seq=0,
+                      ring_stride_token=h * d) if with_ring else {}
+            outs.append(E.decode(c, pool, ws, q, bt2, lens, n, num_splits=splits, kernel=kernel, **kw).float())
+            torch.cuda.synchronize()
+            assert bool((buf[need.value:] == 0xA5).all()), (kernel, with_ring)
+            assert ws.status() == 0
+    assert _cos(outs[0], outs[2]) >= 0.9999 and _cos(outs[1], outs[3]) >= 0.9999

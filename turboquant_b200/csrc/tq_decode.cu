@@ -477,10 +477,13 @@ struct WsLayout {
     size_t off_tickets, off_qprep, off_qfrag, off_partials, total;
 };
 
-WsLayout decode_ws_layout(int D, int B, int Qh, int H, int max_slots) {
+// Partial results are GP x (D + 2) floats per slot.  The tensor-core kernel pads the query heads of a
+// kv head to 8 whenever it keeps separate rotated / sketched fragment sets (more than four heads, or
+// 3-bit codes), the CUDA-core kernel only with more than four heads: size for the larger of the two.
+WsLayout decode_ws_layout(int D, int B, int Qh, int H, int max_slots, int mse_bits) {
     WsLayout w;
     const int G = Qh / H;
-    const int GP = G <= 4 ? 4 : 8;
+    const int GP = (G <= 4 && mse_bits != 3) ? 4 : 8;
     w.off_tickets = TQ_WS_HEADER_BYTES;
     w.off_qprep = w.off_tickets + (((size_t)B * H * sizeof(int32_t) + 255) / 256) * 256;
     w.off_qfrag = w.off_qprep + (((size_t)B * Qh * 2 * D * sizeof(float) + 255) / 256) * 256;
@@ -509,7 +512,7 @@ extern "C" int tq_decode_workspace_bytes(const tq_config* cfg, int32_t batch, in
     if (batch <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || max_splits <= 0) return TQ_ERR_SHAPE;
     if (num_q_heads % num_kv_heads != 0 || num_q_heads / num_kv_heads > TQ_MAX_GROUP_HEADS) return TQ_ERR_UNSUPPORTED;
     // ring CTAs need partial slots too: reserve for a ring of up to 256 tokens
-    *out = decode_ws_layout(cfg->head_dim, batch, num_q_heads, num_kv_heads, max_splits + 8).total;
+    *out = decode_ws_layout(cfg->head_dim, batch, num_q_heads, num_kv_heads, max_splits + 8, cfg->key_bits - 1).total;
     return TQ_OK;
 }
 
@@ -561,7 +564,7 @@ static int decode_impl(const tq_consts* consts, const tq_pool* pool, const tq_de
     if (splits > ntile && ntile > 0) splits = ntile;
     const int ring_tok = has_ring ? ring_tok_for(a->max_ring_len, (int64_t)a->batch * H, splits) : RING_TOK;
     const int rsplits = has_ring ? ring_splits_for(a->max_ring_len, ring_tok) : 0;
-    const WsLayout w = decode_ws_layout(D, a->batch, a->num_q_heads, H, splits + rsplits);
+    const WsLayout w = decode_ws_layout(D, a->batch, a->num_q_heads, H, splits + rsplits, consts->cfg.key_bits - 1);
     if (w.total > a->workspace_bytes) return TQ_ERR_WORKSPACE;
 
     uint8_t* ws = (uint8_t*)a->workspace;

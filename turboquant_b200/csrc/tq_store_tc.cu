@@ -1,7 +1,8 @@
 // Store path on the 5th-generation tensor cores (tcgen05 + TMEM), head_dim 128,
-// bf16 input.  One persistent 512-thread CTA per SM; a tile is 128 token
-// positions of one kv head; four threads share a token row, each owning 32
-// channels from load to packed output.
+// bf16 input.  One persistent CTA per SM: 16 compute warps plus one warp whose
+// single elected thread issues every TMA load and every MMA.  A tile is 128
+// token positions of one kv head; four compute threads share a token row, each
+// owning 32 channels from load to packed output.
 //
 //   TMA (2 swizzled boxes)   : key rows and value rows of the tile -> shared memory
 //   N  norm, normalise       : u = bf16(x / |x|) exactly as torch does, e' = x/|x| - u (what the bf16
@@ -17,7 +18,9 @@
 //
 // Two tiles are in flight: MMA 2 of tile t runs under the normalisation of tile t+1, MMA 1 of tile
 // t+1 under its value quantisation; the key / value boxes of the tile after that are already on
-// their way.  The constant operands (Pi_hi, Pi_lo, M_hi, M_lo: 128 KB) stay in shared memory; no A
+// their way.  The compute warps hand work to the issuing thread through mbarriers they only arrive
+// on, and meet one another at two CTA barriers per tile (norm exchange, record image complete), so
+// they drift apart and fill each other's stalls.  The constant operands (Pi_hi, Pi_lo, M_hi, M_lo: 128 KB) stay in shared memory; no A
 // operand ever touches it.  Tensor memory (512 columns): Y 128 | E, later P 128 | u 64 | e' 64 |
 // r'_hi 64 | r'_lo 64.
 //
@@ -35,7 +38,8 @@ namespace {
 
 constexpr int TC_D = 128;
 constexpr int TC_TOK = 128;
-constexpr int TC_THREADS = 512;
+constexpr int TC_THREADS = 512;                 // compute threads
+constexpr int TC_LAUNCH = TC_THREADS + 32;      // plus the issuing warp
 constexpr int BOX_BYTES = TC_TOK * 128;          // one swizzled box: 128 rows x 128 bytes (64 bf16)
 constexpr int MAT_BYTES = 2 * BOX_BYTES;         // a 128 x 128 bf16 operand: two boxes (k 0-63, 64-127)
 constexpr int TMEM_COLS = 512;
@@ -54,7 +58,7 @@ struct TcParams {
     int64_t num_blocks;
     int H;
     TqCodebook cb;
-    int64_t n_tiles;
+    int n_tiles;                   // token tiles x heads (the launcher keeps it below 2^31)
     int n_rec_buf;                 // record images in shared memory (2 when they fit)
     int tok_outer;                 // tensor-map dimension order: 1 = (channel, head, token), 0 = (channel, token, head)
 };
@@ -192,12 +196,12 @@ __device__ __forceinline__ void quantize_value_group(const uint4 (&raw)[4], uint
     const float rscale = __frcp_rn(scale);
     const __nv_bfloat162 zero2 = __floats2bfloat162_rn(vmin, vmin);
     const __nv_bfloat162 magic = __floats2bfloat162_rn(128.f, 128.f);
-    const __nv_bfloat162 top = __floats2bfloat162_rn((float)N_LEVELS, (float)N_LEVELS);
     uint32_t code[16];   // code of the pair's elements in bits 0.. and 16..
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
         const uint32_t d = as_u32(__hsub2(as_bf162(w[i]), zero2));
-        const __nv_bfloat162 z = __hmin2(as_bf162(pack_bf16(bf_lo(d) * rscale, bf_hi(d) * rscale)), top);
+        // z <= levels * (1 + 2^-7) < levels + 1/2: the rounding below cannot leave the field
+        const __nv_bfloat162 z = as_bf162(pack_bf16(bf_lo(d) * rscale, bf_hi(d) * rscale));
         code[i] = as_u32(__hadd2(z, magic)) & FIELD;
     }
     if (!wr) return;
@@ -219,11 +223,68 @@ __device__ __forceinline__ void quantize_value_group(const uint4 (&raw)[4], uint
     }
 }
 
-// 512 threads: thread (row = tid % 128, q = tid / 128) owns channels [32q, 32q+32) of token row `row` -
-// one value group, 16 packed columns of an A operand, 32 accumulator columns.  Warp w reads and writes
-// TMEM lanes of quarter w % 4 = row / 32, as the hardware requires.
+// Comparisons as arithmetic.  The fp32 pipes are the only full-rate ones of an SM; compares, selects and
+// bit logic run at half rate and would bound this kernel.  For finite a:
+//     step_gt(a, BIG, -b * BIG) = saturate((a - b) * 2^126)  is exactly 1 when a > b and exactly 0 when
+// a <= b, as long as |a - b| is either 0 or at least 2^-126 - true for every boundary that is not itself
+// tiny; the second saturating multiply of step_gt2 extends that to every float (2^-149 * 2^252 >= 1).
+// NaN saturates to 0.
+constexpr float BIG = 8.507059173023462e37f;   // 2^126
+__device__ __forceinline__ float fma_sat(float a, float b, float c) {
+    float d;
+    asm("fma.rn.sat.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float mul_sat(float a, float b) {
+    float d;
+    asm("mul.rn.sat.f32 %0, %1, %2;" : "=f"(d) : "f"(a), "f"(b));
+    return d;
+}
+
+// The code book prepared for that arithmetic (registers): nb[i] = -boundary[i] * 2^126, c0 = centroid[0],
+// step[i] = centroid[i+1] - centroid[i].
+template <int MSE_BITS>
+struct BookRegs {
+    float nb[(1 << MSE_BITS) - 1], step[(1 << MSE_BITS) - 1], c0;
+};
+
+// Bucket search of one rotated coordinate y (torch.searchsorted on the interior boundaries, left: the
+// code is the number of boundaries below y) and y minus its centroid.  `code` comes back as a float.
+template <int MSE_BITS>
+__device__ __forceinline__ void bucket(const BookRegs<MSE_BITS>& bk, float y, float& code, float& y_minus_c) {
+    constexpr int NB = (1 << MSE_BITS) - 1, MID = NB / 2;   // the middle boundary is (next to) zero
+    float k = 0.f, r = y - bk.c0;
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+        float t = fma_sat(y, BIG, bk.nb[i]);
+        if (i == MID) t = mul_sat(t, BIG);
+        k += t;
+        r = fmaf(-t, bk.step[i], r);
+    }
+    code = k;
+    y_minus_c = r;
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tq_smem_u32(bar)) : "memory");
+}
+// Barrier of the 512 compute threads (the issuing warp is not part of it); true if any thread passes true.
+__device__ __forceinline__ bool compute_barrier_or(bool flag) {
+    uint32_t out;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.or.pred p, 1, 512, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(out)
+        : "r"((uint32_t)flag)
+        : "memory");
+    return out != 0;
+}
+
+// Compute thread (row = tid % 128, q = tid / 128), tid < 512, owns channels [32q, 32q+32) of token row
+// `row` - one value group, 16 packed columns of an A operand, 32 accumulator columns.  Warp w reads
+// and writes TMEM lanes of quarter w % 4 = row / 32, as the hardware requires.  Warp 16 only issues.
 template <int MSE_BITS, int VAL_BITS>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_LAUNCH, 1)
 tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
                    const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_b3,
@@ -231,7 +292,6 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     const TqLayout L = tq_make_layout(TC_D, MSE_BITS + 1, VAL_BITS);
     const int BB = L.block_bytes;
     const int IMG = 8 * BB;                           // one record image: the tile's 8 block records
-    constexpr int N_CENT = 1 << MSE_BITS;
 
     extern __shared__ uint8_t smem_raw[];
     // swizzled boxes need a 1024-byte aligned base in the shared window
@@ -240,15 +300,21 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     uint8_t* sX = sB + 4 * MAT_BYTES;                 // key rows of the tile (2 boxes)
     uint8_t* sV = sX + MAT_BYTES;                     // value rows of the tile (2 boxes)
     uint8_t* sRec = sV + MAT_BYTES;                   // n_rec_buf record images
-    float* s_part = reinterpret_cast<float*>(sRec + p.n_rec_buf * IMG);   // [4][128] partial sums of squares
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_part + 4 * TC_TOK);
-    uint64_t *bar_b = bars, *bar_k = bars + 1, *bar_v = bars + 2, *bar_m1 = bars + 3, *bar_m2 = bars + 4,
-             *bar_r = bars + 5;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 6);
+    float* s_ss = reinterpret_cast<float*>(sRec + p.n_rec_buf * IMG);   // [4][128] partial sums of squares of x
+    float* s_rn = s_ss + 4 * TC_TOK;                                    // [4][128] ... of r'
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_rn + 4 * TC_TOK);
+    // completed by TMA bytes / MMA commits (count 1) ...
+    uint64_t *bar_b = bars, *bar_k = bars + 1, *bar_v = bars + 2, *bar_y = bars + 3, *bar_e = bars + 4,
+             *bar_p = bars + 5, *bar_r = bars + 6;
+    // ... and by the 512 compute threads, waited for by the issuing thread:
+    uint64_t* bar_n = bars + 7;    // u / e' of a tile written (Y was read before), its key rows consumed
+    uint64_t* bar_a = bars + 8;    // P of the tile before read: E's columns are free
+    uint64_t* bar_c = bars + 9;    // r' limbs written, Y and E read
+    uint64_t* bar_vf = bars + 10;  // value rows consumed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+    volatile int* s_fail = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int row = tid & (TC_TOK - 1), q = tid >> 7;
-    const int blk_l = row >> 4, tl = row & 15;
     const bool slot_mode = p.slot_mapping != nullptr;
 
     if (warp == 0) {
@@ -259,342 +325,436 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     }
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 6; ++i) tq_mbar_init(bars + i, 1);
+        for (int i = 0; i < 7; ++i) tq_mbar_init(bars + i, 1);
+#pragma unroll
+        for (int i = 7; i < 11; ++i) tq_mbar_init(bars + i, TC_THREADS);
+        *s_fail = 0;
         tq_mbar_fence_init();
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t lane_base = (uint32_t)(row & ~31) << 16;   // this warp's quarter of the 128 TMEM lanes
 
     // tile -> (kv head, first row's token index).  Tiles lie on the block grid of the destination
     // sequence: row r of token tile tt is token i = 128 * tt + r - lead (lead > 0: the first block already
     // holds `lead` earlier tokens); the boxes of rows outside [0, n_tokens) arrive as zeros.
-    auto tile_head = [&](int64_t tile) { return (int)(tile % p.H); };
-    auto tile_tok0 = [&](int64_t tile) { return (tile / p.H) * TC_TOK - p.lead; };
-    auto issue_kv = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int64_t tile) {
-        const int hh = tile_head(tile), t0 = (int)tile_tok0(tile);
-        tq_mbar_expect_tx(bar, 2 * BOX_BYTES);
-        tma_load_3d(dst, tm, 0, p.tok_outer ? hh : t0, p.tok_outer ? t0 : hh, bar);
-        tma_load_3d(dst + BOX_BYTES, tm, 64, p.tok_outer ? hh : t0, p.tok_outer ? t0 : hh, bar);
-    };
+    // (32-bit unsigned arithmetic: 64-bit division is a long instruction sequence)
+    auto tile_head = [&](int tile) { return (int)((uint32_t)tile % (uint32_t)p.H); };
+    auto tile_tok0 = [&](int tile) { return (int64_t)((uint32_t)tile / (uint32_t)p.H) * TC_TOK - p.lead; };
+    const int tile0 = blockIdx.x;   // the grid never exceeds the tile count
+    const bool rmw = !slot_mode && p.lead != 0 && tile0 < p.H;   // this CTA's first tile completes a begun block
 
-    const int64_t tile0 = blockIdx.x;   // the grid never exceeds the tile count
-    if (tid == 0) {
-        tq_mbar_expect_tx(bar_b, 4 * MAT_BYTES);
-        const CUtensorMap* tb[4] = {&tm_b0, &tm_b1, &tm_b2, &tm_b3};
-#pragma unroll
-        for (int m = 0; m < 4; ++m) {
-            tma_load_2d(sB + m * MAT_BYTES, tb[m], 0, 0, bar_b);
-            tma_load_2d(sB + m * MAT_BYTES + BOX_BYTES, tb[m], 64, 0, bar_b);
-        }
-        issue_kv(sX, &tm_k, bar_k, tile0);
-        issue_kv(sV, &tm_v, bar_v, tile0);
-    }
-
-    const uint32_t aB = tq_smem_u32(sB);
-    uint32_t ph_k = 0, ph_v = 0, ph_m1 = 0, ph_m2 = 0;
-    bool failed = false;
-    float nd = 0.f;        // |x| of this thread's row in the input dtype, from N to S of the same tile
-    float nd_next = 0.f;
-
-    // ---- N: key rows of a tile -> norm, u and e' in tensor memory (uniform result: false = timeout) ----
-    auto phase_n = [&](float& nd_out) -> bool {
-        const bool ok = tq_mbar_wait_bounded(bar_k, ph_k);
-        ph_k ^= 1;
-        uint32_t xw[16];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-            const uint4 v = lds_sw128(sX + (q >> 1) * BOX_BYTES, row, (q & 1) * 4 + c);
-            xw[4 * c] = v.x; xw[4 * c + 1] = v.y; xw[4 * c + 2] = v.z; xw[4 * c + 3] = v.w;
-        }
-        float ss = 0.f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const float a = bf_lo(xw[i]), b = bf_hi(xw[i]);
-            ss = fmaf(a, a, ss);
-            ss = fmaf(b, b, ss);
-        }
-        s_part[q * TC_TOK + row] = ss;
-        if (__syncthreads_or(!ok)) return false;      // partial sums published; every thread has read its key row
-        ss = (s_part[row] + s_part[TC_TOK + row]) + (s_part[2 * TC_TOK + row] + s_part[3 * TC_TOK + row]);
-        const float n_d = bf16r(__fsqrt_rn(ss));               // quantizer.py:136, in the input dtype
-        const float den = bf16r(n_d + 1e-10f);                 // quantizer.py:138
-        const float rden = __frcp_rn(den);
-        uint32_t up[16], ep[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            // numerator and denominator are bf16 numbers: the product with the reciprocal rounds to
-            // the same bf16 as the division (see quantize_value_group)
-            const float q0 = bf_lo(xw[i]) * rden, q1 = bf_hi(xw[i]) * rden;
-            const uint32_t u = pack_bf16(q0, q1);
-            up[i] = u;
-            ep[i] = pack_bf16(q0 - bf_lo(u), q1 - bf_hi(u));   // what the bf16 normalisation lost
-        }
-        tmem_st16(tmem + lane_base + COL_U + q * 16, up);
-        tmem_st16(tmem + lane_base + COL_EP + q * 16, ep);
-        tmem_st_wait();
-        nd_out = n_d;
-        return true;
-    };
-    // issued by one thread once every thread's u / e' are in tensor memory
-    auto issue_mma1 = [&]() {
-        tc_fence_after();
-#pragma unroll
-        for (int m = 0; m < 2; ++m)
-#pragma unroll
-            for (int ks = 0; ks < TC_D / 16; ++ks)
-                umma_ts(tmem + COL_Y, tmem + COL_U + ks * 8,
-                        smem_desc_sw128(aB + m * MAT_BYTES + (ks >> 2) * BOX_BYTES + (ks & 3) * 32), (m | ks) != 0);
-#pragma unroll
-        for (int ks = 0; ks < TC_D / 16; ++ks)
-            umma_ts(tmem + COL_E, tmem + COL_EP + ks * 8,
-                    smem_desc_sw128(aB + (ks >> 2) * BOX_BYTES + (ks & 3) * 32), ks != 0);
-        umma_commit(bar_m1);
-    };
-    auto issue_mma2 = [&]() {
-        tc_fence_after();
-#pragma unroll
-        for (int m = 0; m < 3; ++m) {   // r_hi * M_hi + r_hi * M_lo + r_lo * M_hi
-            const uint32_t a_col = m == 2 ? COL_RL : COL_RH;
-            const uint32_t b_mat = m == 1 ? 3 : 2;
-#pragma unroll
-            for (int ks = 0; ks < TC_D / 16; ++ks)
-                umma_ts(tmem + COL_E, tmem + a_col + ks * 8,
-                        smem_desc_sw128(aB + b_mat * MAT_BYTES + (ks >> 2) * BOX_BYTES + (ks & 3) * 32), (m | ks) != 0);
-        }
-        umma_commit(bar_m2);
-    };
-    // V: value rows in shared memory -> codes, scales, zero points of one tile's record image
-    auto phase_v = [&](uint8_t* image, int64_t tok_first) -> bool {
-        const bool ok = tq_mbar_wait_bounded(bar_v, ph_v);
-        ph_v ^= 1;
-        uint4 vraw[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) vraw[c] = lds_sw128(sV + (q >> 1) * BOX_BYTES, row, (q & 1) * 4 + c);
-        quantize_value_group<VAL_BITS>(vraw, image + blk_l * BB, L, tl, q, tok_first + row >= 0);
-        return !__syncthreads_or(!ok);                // every thread has read its value row
-    };
-
-    // ---- prologue: first tile's keys normalised ----
-    if (!phase_n(nd)) failed = true;
-
-    int tile_no = 0;
-#pragma unroll 1
-    for (int64_t tile = tile0; tile < p.n_tiles && !failed; tile += gridDim.x, ++tile_no) {
-        const int64_t next = tile + gridDim.x;
-        const bool has_next = next < p.n_tiles;
-        const int h = tile_head(tile);
-        const int64_t tok0 = tile_tok0(tile);
-        const bool wr = tok0 + row >= 0;                 // rows before token 0 belong to an earlier append
-        uint8_t* img = sRec + (p.n_rec_buf == 2 ? (tile_no & 1) : 0) * IMG;
-        uint8_t* rec = img + blk_l * BB;
-
-        if (tile_no == 0) {
-            // first tile of this CTA: its u / e' are in tensor memory; publish them, start MMA 1 and the
-            // next key load, fetch the block this append continues (if any), quantise its values
-            const bool b_ok = tid != 0 || tq_mbar_wait_bounded(bar_b, 0);   // constant operands (needed by the issuer)
-            tc_fence_before();
-            if (__syncthreads_or(!b_ok)) {
-                failed = true;
-                break;
+    // One poller per warp; gives up after `limit` polls or as soon as somebody has flagged a failure.
+    auto wait_warp = [&](uint64_t* bar, uint32_t parity) -> bool {
+        uint32_t ok = 1;
+        if (lane == 0) {
+            ok = 0;
+            for (int i = 0; i < (1 << 21); ++i) {
+                if (tq_mbar_try_wait(bar, parity)) {
+                    ok = 1;
+                    break;
+                }
+                if (i >= 4) __nanosleep(20);
+                if ((i & 255) == 255 && *s_fail) break;
             }
-            if (tid == 0) {
-                issue_mma1();
-                if (has_next) issue_kv(sX, &tm_k, bar_k, next);
+            if (!ok) *s_fail = 1;
+        }
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        __syncwarp();   // the poller's acquire covers the whole warp
+        return ok != 0;
+    };
+
+    if (warp == TC_THREADS / 32) {
+        // =============================== issuing warp ===============================
+        // The whole warp runs this code with identical values, so that addresses and descriptors stay
+        // in the uniform datapath the MMA and TMA instructions take their operands from; one elected
+        // lane issues.
+        {
+            const uint32_t aB = tq_smem_u32(sB);
+            const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
+            auto wait1 = [&](uint64_t* bar, uint32_t parity) -> bool {
+                uint32_t ok = 0;
+                for (int i = 0; i < (1 << 20); ++i) {
+                    if (tq_mbar_try_wait(bar, parity)) {
+                        ok = 1;
+                        break;
+                    }
+                    __nanosleep(40);   // a spinning warp takes issue slots from the compute warps of its scheduler
+                    if ((i & 255) == 255 && *s_fail) break;
+                }
+                ok = __all_sync(0xffffffffu, ok != 0);
+                if (!ok) *s_fail = 1;
+                return ok != 0;
+            };
+            auto elected = [&]() -> bool {
+                uint32_t pred;
+                asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+                return pred != 0;
+            };
+            auto issue_kv = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int tile) {
+                const int hh = tile_head(tile), t0 = (int)tile_tok0(tile);
+                if (elected()) {
+                    tq_mbar_expect_tx(bar, 2 * BOX_BYTES);
+                    tma_load_3d(dst, tm, 0, p.tok_outer ? hh : t0, p.tok_outer ? t0 : hh, bar);
+                    tma_load_3d(dst + BOX_BYTES, tm, 64, p.tok_outer ? hh : t0, p.tok_outer ? t0 : hh, bar);
+                }
+                __syncwarp();
+            };
+            // operand descriptors: the upper word is a constant, the lower one the address in 16-byte units
+            const uint32_t desc_lo = (uint32_t)(smem_desc_sw128(aB) & 0xffffffffu);
+            const uint32_t desc_hi = (uint32_t)(smem_desc_sw128(aB) >> 32);
+            auto b_desc = [&](int mat, int ks) {
+                const uint32_t lo = desc_lo + (uint32_t)((mat * MAT_BYTES + (ks >> 2) * BOX_BYTES + (ks & 3) * 32) >> 4);
+                return ((uint64_t)desc_hi << 32) | lo;
+            };
+            auto issue_mma_y = [&]() {   // Y = u Pi_hi^T + u Pi_lo^T
+                tc_fence_after();
+                if (elected()) {
+#pragma unroll
+                    for (int m = 0; m < 2; ++m)
+#pragma unroll
+                        for (int ks = 0; ks < TC_D / 16; ++ks)
+                            umma_ts(tmem + COL_Y, tmem + COL_U + ks * 8, b_desc(m, ks), (m | ks) != 0);
+                    umma_commit(bar_y);
+                }
+                __syncwarp();
+            };
+            auto issue_mma_e = [&]() {   // E = e' Pi_hi^T
+                tc_fence_after();
+                if (elected()) {
+#pragma unroll
+                    for (int ks = 0; ks < TC_D / 16; ++ks)
+                        umma_ts(tmem + COL_E, tmem + COL_EP + ks * 8, b_desc(0, ks), ks != 0);
+                    umma_commit(bar_e);
+                }
+                __syncwarp();
+            };
+            auto issue_mma_p = [&]() {   // P = r_hi M_hi^T + r_hi M_lo^T + r_lo M_hi^T, over E's columns
+                tc_fence_after();
+                if (elected()) {
+#pragma unroll
+                    for (int m = 0; m < 3; ++m)
+#pragma unroll
+                        for (int ks = 0; ks < TC_D / 16; ++ks)
+                            umma_ts(tmem + COL_E, tmem + (m == 2 ? COL_RL : COL_RH) + ks * 8, b_desc(m == 1 ? 3 : 2, ks),
+                                    (m | ks) != 0);
+                    umma_commit(bar_p);
+                }
+                __syncwarp();
+            };
+
+            if (elected()) {
+                tq_mbar_expect_tx(bar_b, 4 * MAT_BYTES);
+                const CUtensorMap* tb[4] = {&tm_b0, &tm_b1, &tm_b2, &tm_b3};
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    tma_load_2d(sB + m * MAT_BYTES, tb[m], 0, 0, bar_b);
+                    tma_load_2d(sB + m * MAT_BYTES + BOX_BYTES, tb[m], 64, 0, bar_b);
+                }
             }
-            if (!slot_mode && p.lead != 0 && tile < p.H) {
-                // the first block of this append already holds `lead` tokens of the sequence: complete it
-                if (tid == 0) {
+            __syncwarp();
+            issue_kv(sX, &tm_k, bar_k, tile0);
+            issue_kv(sV, &tm_v, bar_v, tile0);
+            if (rmw) {   // the block this append continues, into block 0 of the first record image
+                if (elected()) {
                     const int64_t phys = p.block_table[p.start_pos >> 4];
                     if (phys >= 0 && phys < p.num_blocks) {
                         tq_mbar_expect_tx(bar_r, (uint32_t)BB);
-                        tq_bulk_g2s(img, p.pool + (phys * p.H + h) * (int64_t)BB, (uint32_t)BB, bar_r);
+                        tq_bulk_g2s(sRec, p.pool + (phys * p.H + tile_head(tile0)) * (int64_t)BB, (uint32_t)BB, bar_r);
                     } else {
                         atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_RANGE);
                         tq_mbar_expect_tx(bar_r, 0);   // completes the phase: nobody waits for bytes
                     }
                 }
-                const bool ok = tq_mbar_wait_bounded(bar_r, 0);
-                if (__syncthreads_or(!ok)) {
-                    failed = true;
-                    break;
+                __syncwarp();
+            }
+            bool ok = wait1(bar_b, 0);
+            // per tile, in the order the compute threads arrive: [n] Y product, next key rows; [vf] next value
+            // rows; [a] E product; [c] P product
+            auto feed = [&](int i, int tile) -> bool {
+                const int next = tile + (int)gridDim.x;
+                if (!wait1(bar_n, i & 1)) return false;
+                issue_mma_y();
+                if (next < p.n_tiles) issue_kv(sX, &tm_k, bar_k, next);
+                if (p.n_rec_buf == 2) {
+                    if (!wait1(bar_vf, i & 1)) return false;
+                    if (next < p.n_tiles) issue_kv(sV, &tm_v, bar_v, next);
                 }
+                if (!wait1(bar_a, i & 1)) return false;
+                issue_mma_e();
+                if (p.n_rec_buf != 2) {   // with one record image the values follow the record store
+                    if (!wait1(bar_vf, i & 1)) return false;
+                    if (next < p.n_tiles) issue_kv(sV, &tm_v, bar_v, next);
+                }
+                return true;
+            };
+            int i = 0;
+            ok = ok && feed(0, tile0);
+#pragma unroll 1
+            for (int tile = tile0; tile < p.n_tiles && ok; tile += (int)gridDim.x, ++i) {
+                if (!(ok = wait1(bar_c, i & 1))) break;
+                issue_mma_p();
+                if (tile + (int)gridDim.x < p.n_tiles) ok = feed(i + 1, tile + (int)gridDim.x);
             }
-            if (!phase_v(img, tok0)) {
-                failed = true;
-                break;
-            }
-            if (tid == 0 && has_next) issue_kv(sV, &tm_v, bar_v, next);
         }
+    } else {
+        // =============================== compute warps ===============================
+        const int row = tid & (TC_TOK - 1), q = tid >> 7;
+        const int blk_l = row >> 4, tl = row & 15;
+        const uint32_t lane_base = (uint32_t)(row & ~31) << 16;   // this warp's quarter of the 128 TMEM lanes
+        BookRegs<MSE_BITS> bk;   // the code book, in registers
+        bk.c0 = p.cb.centroids[0];
+#pragma unroll
+        for (int i = 0; i < (1 << MSE_BITS) - 1; ++i) {
+            bk.nb[i] = -p.cb.boundaries[i] * BIG;
+            bk.step[i] = p.cb.centroids[i + 1] - p.cb.centroids[i];
+        }
+        bool bad = false;      // one of this warp's waits ran out; reported at the next compute barrier
+        float nd = 0.f;        // |x| of this thread's row in the input dtype, from N to S of the same tile
+        float nd_next = 0.f;
 
-        // ---------------- C: codes and rotated-space residual of channels [32q, 32q+32) ----------------
-        {
-            const bool ok = tq_mbar_wait_bounded(bar_m1, ph_m1);
-            ph_m1 ^= 1;
-            if (__syncthreads_or(!ok)) {
-                failed = true;
-                break;
+        // N: key rows of a tile -> norm, u and e' in tensor memory; false (uniform) = a wait ran out
+        auto phase_n = [&](uint32_t parity, float& nd_out) -> bool {
+            bad |= !wait_warp(bar_k, parity);
+            uint32_t xw[16];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const uint4 v = lds_sw128(sX + (q >> 1) * BOX_BYTES, row, (q & 1) * 4 + c);
+                xw[4 * c] = v.x; xw[4 * c + 1] = v.y; xw[4 * c + 2] = v.z; xw[4 * c + 3] = v.w;
             }
-        }
-        tc_fence_after();
-        {
-            float y[32];
-            tmem_ld32(tmem + lane_base + COL_Y + q * 32, y);
-            constexpr int WIDTH = MSE_BITS == 2 ? 2 : 4, PER_WORD = 32 / WIDTH;
-            uint32_t words[32 / PER_WORD];
-#pragma unroll
-            for (int w = 0; w < 32 / PER_WORD; ++w) {
-                uint32_t word = 0;
-#pragma unroll
-                for (int jj = 0; jj < PER_WORD; ++jj) {
-                    const int j = w * PER_WORD + jj;
-                    uint32_t k = 0;
-                    float c = p.cb.centroids[0];
-#pragma unroll
-                    for (int bnd = 0; bnd < N_CENT - 1; ++bnd) {
-                        const bool above = !(y[j] <= p.cb.boundaries[bnd]);   // searchsorted; NaN sorts last
-                        k += above ? 1u : 0u;
-                        c = above ? p.cb.centroids[bnd + 1] : c;
-                    }
-                    word |= k << (WIDTH * jj);       // quantizer.py:50-68
-                    y[j] -= c;
-                }
-                words[w] = word;
-            }
-            if (wr) {
-                uint32_t* kc = reinterpret_cast<uint32_t*>(rec + L.off_kcodes + tl * L.kcode_row) + q * (32 / PER_WORD);
-#pragma unroll
-                for (int w = 0; w < 32 / PER_WORD; ++w) kc[w] = words[w];
-            }
-            float er[32];
-            tmem_ld32(tmem + lane_base + COL_E + q * 32, er);
-            float rn2 = 0.f;
-            uint32_t hi[16], lo[16];
+            float ss = 0.f;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
-                const float a = y[2 * i] + er[2 * i], b = y[2 * i + 1] + er[2 * i + 1];   // r' = (Y - c) + E
-                rn2 = fmaf(a, a, rn2);
-                rn2 = fmaf(b, b, rn2);
-                const uint32_t hh = pack_bf16(a, b);
-                hi[i] = hh;
-                lo[i] = pack_bf16(a - bf_lo(hh), b - bf_hi(hh));
+                const float a = bf_lo(xw[i]), b = bf_hi(xw[i]);
+                ss = fmaf(a, a, ss);
+                ss = fmaf(b, b, ss);
             }
-            tmem_st16(tmem + lane_base + COL_RH + q * 16, hi);
-            tmem_st16(tmem + lane_base + COL_RL + q * 16, lo);
-            s_part[q * TC_TOK + row] = rn2;
+            s_ss[q * TC_TOK + row] = ss;
+            if (compute_barrier_or(bad)) return false;    // partial sums (of x, and of the r' before) published
+            ss = (s_ss[row] + s_ss[TC_TOK + row]) + (s_ss[2 * TC_TOK + row] + s_ss[3 * TC_TOK + row]);
+            const float n_d = bf16r(__fsqrt_rn(ss));               // quantizer.py:136, in the input dtype
+            const float den = bf16r(n_d + 1e-10f);                 // quantizer.py:138
+            const float rden = __frcp_rn(den);
+            uint32_t up[16], ep[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                // numerator and denominator are bf16 numbers: the product with the reciprocal rounds to
+                // the same bf16 as the division (see quantize_value_group)
+                const float q0 = bf_lo(xw[i]) * rden, q1 = bf_hi(xw[i]) * rden;
+                const uint32_t u = pack_bf16(q0, q1);
+                up[i] = u;
+                ep[i] = pack_bf16(q0 - bf_lo(u), q1 - bf_hi(u));   // what the bf16 normalisation lost
+            }
+            tmem_st16(tmem + lane_base + COL_U + q * 16, up);
+            tmem_st16(tmem + lane_base + COL_EP + q * 16, ep);
             tmem_st_wait();
-        }
-        tc_fence_before();
-        __syncthreads();
-        if (tid == 0) issue_mma2();
-        if (q == 0 && wr) {   // norms of the row (partials were published before the barrier above)
-            const float rn2 = (s_part[row] + s_part[TC_TOK + row]) + (s_part[2 * TC_TOK + row] + s_part[3 * TC_TOK + row]);
-            reinterpret_cast<__half*>(rec + L.off_knorm)[tl] = __float2half_rn(nd);
-            // |r| = |x| * |r'| (the reference's residual x - x_hat, quantizer.py:244-245)
-            reinterpret_cast<__half*>(rec + L.off_krnorm)[tl] = __float2half_rn(nd * __fsqrt_rn(rn2));
-        }
-        // the other record image is written next (values of the following tile): the records it held must have left
-        if (lane == 0 && warp < 8 && p.n_rec_buf == 2) tq_bulk_wait_all_read();
-        __syncthreads();   // also: s_part is reused by N below
+            nd_out = n_d;
+            return true;
+        };
+        // V: value rows in shared memory -> codes, scales, zero points of one tile's record image
+        auto phase_v = [&](uint32_t parity, uint8_t* image, int64_t tok_first) {
+            bad |= !wait_warp(bar_v, parity);
+            uint4 vraw[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) vraw[c] = lds_sw128(sV + (q >> 1) * BOX_BYTES, row, (q & 1) * 4 + c);
+            mbar_arrive(bar_vf);                          // this thread's value row is in registers
+            quantize_value_group<VAL_BITS>(vraw, image + blk_l * BB, L, tl, q, tok_first + row >= 0);
+        };
 
-        // ---------------- N of the next tile, under MMA 2 ----------------
-        if (has_next && !phase_n(nd_next)) {
-            failed = true;
-            break;
+        // N of a tile, then the hand-over to the issuing thread: its Y product may start (every thread
+        // passed the C phase of the tile before, so Y has been read), the key rows are consumed
+        auto phase_n_and_arrive = [&](uint32_t parity, float& nd_out) -> bool {
+            if (!phase_n(parity, nd_out)) return false;
+            tc_fence_before();
+            mbar_arrive(bar_n);
+            return true;
+        };
+
+        // ---- first tile: keys normalised, the begun block fetched, values quantised ----
+        bool ok = phase_n_and_arrive(0, nd);
+        if (ok) {
+            mbar_arrive(bar_a);                           // nothing occupies E's columns yet
+            if (rmw) bad |= !wait_warp(bar_r, 0);
+            phase_v(0, sRec, tile_tok0(tile0));
         }
 
-        // ---------------- S: sign bits of channels [32q, 32q+32) (quantizer.py:214-222) ----------------
-        {
-            const bool ok = tq_mbar_wait_bounded(bar_m2, ph_m2);
-            ph_m2 ^= 1;
-            if (__syncthreads_or(!ok)) {
-                failed = true;
+        int tile_no = 0;
+#pragma unroll 1
+        for (int tile = tile0; tile < p.n_tiles && ok; tile += (int)gridDim.x, ++tile_no) {
+            const int next = tile + (int)gridDim.x;
+            const bool has_next = next < p.n_tiles;
+            const uint32_t par = tile_no & 1;
+            const int h = tile_head(tile);
+            const int64_t tok0 = tile_tok0(tile);
+            const bool wr = tok0 + row >= 0;                 // rows before token 0 belong to an earlier append
+            uint8_t* img = sRec + (p.n_rec_buf == 2 ? (tile_no & 1) : 0) * IMG;
+            uint8_t* nimg = sRec + (p.n_rec_buf == 2 ? ((tile_no + 1) & 1) : 0) * IMG;
+            uint8_t* rec = img + blk_l * BB;
+
+            // destination of image block `warp` (warps 0-7): asked for now, looked at when the records leave
+            // (the loaded words are not touched before that - not even widened - so nobody waits for them here)
+            int32_t dest_blk = -1;    // block-table mode, lane 0: physical block
+            int64_t dest_slot = -1;   // slot mode: slot of row `lane & 15`
+            bool dest_asked = false;
+            if (warp < 8) {
+                if (!slot_mode) {
+                    const int64_t first = tok0 + warp * TQ_BLOCK_TOKENS;      // token index of the block's first row
+                    dest_asked = lane == 0 && first < p.n_tokens && first + TQ_BLOCK_TOKENS > 0;
+                    if (dest_asked) dest_blk = __ldg(p.block_table + ((p.start_pos + first) >> 4));
+                } else {
+                    const int64_t i = tok0 + warp * TQ_BLOCK_TOKENS + (lane & 15);
+                    if (i >= 0 && i < p.n_tokens) dest_slot = __ldg(p.slot_mapping + i);
+                }
+            }
+
+            // ---------------- C: codes and rotated-space residual of channels [32q, 32q+32) ----------------
+            bad |= !wait_warp(bar_y, par);
+            tc_fence_after();
+            {
+                float y[32];
+                tmem_ld32(tmem + lane_base + COL_Y + q * 32, y);
+                // codes of 16 bits' worth of coordinates are summed in one float (exact), LSB first
+                // (quantizer.py:50-68), and converted once
+                constexpr int WIDTH = MSE_BITS == 2 ? 2 : 4, PER_HALF = 16 / WIDTH;
+                uint32_t halves[32 / PER_HALF];
+#pragma unroll
+                for (int w = 0; w < 32 / PER_HALF; ++w) {
+                    float wf = 0.f;
+#pragma unroll
+                    for (int jj = 0; jj < PER_HALF; ++jj) {
+                        float code;
+                        bucket<MSE_BITS>(bk, y[w * PER_HALF + jj], code, y[w * PER_HALF + jj]);   // quantizer.py:144
+                        wf = fmaf(code, (float)(1u << (WIDTH * jj)), wf);
+                    }
+                    halves[w] = __float_as_uint(wf + 8388608.f) & 0xffffu;   // 2^23 + integer: the integer sits in the mantissa
+                }
+                if (wr) {
+                    uint32_t* kc = reinterpret_cast<uint32_t*>(rec + L.off_kcodes + tl * L.kcode_row) + q * (16 / PER_HALF);
+#pragma unroll
+                    for (int w = 0; w < 16 / PER_HALF; ++w) kc[w] = halves[2 * w] | (halves[2 * w + 1] << 16);
+                }
+                bad |= !wait_warp(bar_e, par);            // the E product was issued last: it lands under the search above
+                tc_fence_after();
+                float er[32];
+                tmem_ld32(tmem + lane_base + COL_E + q * 32, er);
+                float rn2 = 0.f;
+                uint32_t hi[16], lo[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const float a = y[2 * i] + er[2 * i], b = y[2 * i + 1] + er[2 * i + 1];   // r' = (Y - c) + E
+                    rn2 = fmaf(a, a, rn2);
+                    rn2 = fmaf(b, b, rn2);
+                    const uint32_t hh = pack_bf16(a, b);
+                    hi[i] = hh;
+                    lo[i] = pack_bf16(a - bf_lo(hh), b - bf_hi(hh));
+                }
+                tmem_st16(tmem + lane_base + COL_RH + q * 16, hi);
+                tmem_st16(tmem + lane_base + COL_RL + q * 16, lo);
+                s_rn[q * TC_TOK + row] = rn2;
+                tmem_st_wait();
+            }
+            tc_fence_before();
+            mbar_arrive(bar_c);                           // the P product may start once every thread is here
+
+            // the other record image is written next (values of the following tile): what it held must have left
+            if (lane == 0 && warp < 8) tq_bulk_wait_all_read();
+
+            // ---------------- N of the next tile, under the P product ----------------
+            if (has_next) {
+                if (!phase_n_and_arrive(par ^ 1, nd_next)) {
+                    ok = false;
+                    break;
+                }
+            } else if (compute_barrier_or(bad)) {         // same barrier: publishes the r' partial sums
+                ok = false;
                 break;
             }
-        }
-        tc_fence_after();
-        {
-            float pr[32];
-            tmem_ld32(tmem + lane_base + COL_E + q * 32, pr);
-            uint32_t w = 0;
+
+            // ---------------- V of the next tile (two record images: before this tile's records are complete) ----------------
+            if (has_next && p.n_rec_buf == 2) phase_v(par ^ 1, nimg, tile_tok0(next));
+
+            // ---------------- S: sign bits of channels [32q, 32q+32) (quantizer.py:214-222) ----------------
+            bad |= !wait_warp(bar_p, par);
+            tc_fence_after();
+            {
+                float pr[32];
+                tmem_ld32(tmem + lane_base + COL_E + q * 32, pr);
+                tc_fence_before();
+                if (has_next) mbar_arrive(bar_a);         // P is read: the next E product may use its columns
+                float w_lo = 0.f, w_hi = 0.f;   // bit j = (P_j > 0), sixteen bits per float
 #pragma unroll
-            for (int j = 0; j < 32; ++j) w |= (pr[j] > 0.f ? 1u : 0u) << j;
-            if (nd == 0.f) w = 0;   // x = 0: the reference's residual is exactly 0, r' is not
-            if (wr) reinterpret_cast<uint32_t*>(rec + L.off_ksigns + tl * L.ksign_row)[q] = w;
-        }
-        tq_fence_proxy_async();
-        tc_fence_before();
-        __syncthreads();   // record image complete; P has been read: its columns may take the next E
+                for (int j = 0; j < 16; ++j) {
+                    w_lo = fmaf(mul_sat(mul_sat(pr[j], BIG), BIG), (float)(1u << j), w_lo);
+                    w_hi = fmaf(mul_sat(mul_sat(pr[16 + j], BIG), BIG), (float)(1u << j), w_hi);
+                }
+                uint32_t w = (__float_as_uint(w_lo + 8388608.f) & 0xffffu) | (__float_as_uint(w_hi + 8388608.f) << 16);
+                if (nd == 0.f) w = 0;   // x = 0: the reference's residual is exactly 0, r' is not
+                if (wr) reinterpret_cast<uint32_t*>(rec + L.off_ksigns + tl * L.ksign_row)[q] = w;
+            }
+            if (q == 0 && wr) {   // norms of the row
+                const float rn2 = (s_rn[row] + s_rn[TC_TOK + row]) + (s_rn[2 * TC_TOK + row] + s_rn[3 * TC_TOK + row]);
+                reinterpret_cast<__half*>(rec + L.off_knorm)[tl] = __float2half_rn(nd);
+                // |r| = |x| * |r'| (the reference's residual x - x_hat, quantizer.py:244-245)
+                reinterpret_cast<__half*>(rec + L.off_krnorm)[tl] = __float2half_rn(nd * __fsqrt_rn(rn2));
+            }
+            tq_fence_proxy_async();
+            if (compute_barrier_or(bad)) {                // record image complete
+                ok = false;
+                break;
+            }
 
-        if (tid == 0 && has_next) {
-            issue_mma1();
-            if (next + gridDim.x < p.n_tiles) issue_kv(sX, &tm_k, bar_k, next + gridDim.x);
-        }
-
-        // ---------------- the tile's block records leave ----------------
-        if (warp < 8) {
-            const int j = warp;                                   // image block
-            if (!slot_mode) {
-                if (lane == 0) {
-                    const int64_t first = tok0 + j * TQ_BLOCK_TOKENS;     // token index of the block's first row
-                    if (first < p.n_tokens && first + TQ_BLOCK_TOKENS > 0) {
-                        const int64_t phys = p.block_table[(p.start_pos + first) >> 4];
-                        if (phys >= 0 && phys < p.num_blocks) {
-                            tq_bulk_s2g(p.pool + (phys * p.H + h) * (int64_t)BB, img + j * BB, (uint32_t)BB);
+            // ---------------- the tile's block records leave ----------------
+            if (warp < 8) {
+                const int j = warp;                                   // image block
+                if (!slot_mode) {
+                    if (dest_asked) {
+                        if (dest_blk >= 0 && dest_blk < p.num_blocks) {
+                            tq_bulk_s2g(p.pool + ((int64_t)dest_blk * p.H + h) * (int64_t)BB, img + j * BB, (uint32_t)BB);
                             tq_bulk_commit();
                         } else {
                             atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_RANGE);
                         }
                     }
-                }
-            } else {
-                // slot mapping: sixteen rows that fill one block in order leave as a whole record, anything
-                // else is scattered byte by byte to each token's own slot
-                const int64_t i = tok0 + j * TQ_BLOCK_TOKENS + (lane & 15);
-                int64_t slot = (i >= 0 && i < p.n_tokens) ? p.slot_mapping[i] : -1;
-                if (slot >= 0 && (slot >> 4) >= p.num_blocks) {
-                    atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_RANGE);
-                    slot = -1;
-                }
-                const int64_t slot0 = __shfl_sync(0xffffffffu, slot, 0);
-                const bool whole =
-                    __all_sync(0xffffffffu, slot0 >= 0 && (slot0 & 15) == 0 && slot == slot0 + (lane & 15));
-                if (whole) {
-                    if (lane == 0) {
-                        tq_bulk_s2g(p.pool + ((slot0 >> 4) * p.H + h) * (int64_t)BB, img + j * BB, (uint32_t)BB);
-                        tq_bulk_commit();
-                    }
                 } else {
-                    const int per_tok = BB / TQ_BLOCK_TOKENS;
-                    const uint8_t* src = img + j * BB;
-                    for (int t = 0; t < TQ_BLOCK_TOKENS; ++t) {
-                        const int64_t s = __shfl_sync(0xffffffffu, slot, t);
-                        if (s < 0) continue;
-                        uint8_t* dst = p.pool + ((s >> 4) * p.H + h) * (int64_t)BB;
-                        for (int cb = lane; cb < per_tok; cb += 32)
-                            dst[rec_byte_offset(L, (int)(s & 15), cb)] = src[rec_byte_offset(L, t, cb)];
+                    // slot mapping: sixteen rows that fill one block in order leave as a whole record,
+                    // anything else is scattered byte by byte to each token's own slot
+                    int64_t slot = dest_slot;
+                    if (slot >= 0 && (slot >> 4) >= p.num_blocks) {
+                        atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_RANGE);
+                        slot = -1;
+                    }
+                    const int64_t slot0 = __shfl_sync(0xffffffffu, slot, 0);
+                    const bool whole =
+                        __all_sync(0xffffffffu, slot0 >= 0 && (slot0 & 15) == 0 && slot == slot0 + (lane & 15));
+                    if (whole) {
+                        if (lane == 0) {
+                            tq_bulk_s2g(p.pool + ((slot0 >> 4) * p.H + h) * (int64_t)BB, img + j * BB, (uint32_t)BB);
+                            tq_bulk_commit();
+                        }
+                    } else {
+                        const int per_tok = BB / TQ_BLOCK_TOKENS;
+                        const uint8_t* src = img + j * BB;
+                        for (int t = 0; t < TQ_BLOCK_TOKENS; ++t) {
+                            const int64_t s = __shfl_sync(0xffffffffu, slot, t);
+                            if (s < 0) continue;
+                            uint8_t* dst = p.pool + ((s >> 4) * p.H + h) * (int64_t)BB;
+                            for (int cb = lane; cb < per_tok; cb += 32)
+                                dst[rec_byte_offset(L, (int)(s & 15), cb)] = src[rec_byte_offset(L, t, cb)];
+                        }
                     }
                 }
+                if (lane == 0 && p.n_rec_buf == 1) tq_bulk_wait_all_read();
             }
-            if (lane == 0 && p.n_rec_buf == 1) tq_bulk_wait_all_read();
-        }
-        if (p.n_rec_buf == 1) __syncthreads();   // the single image is rewritten by the values below
-
-        // ---------------- V of the next tile, under MMA 1 ----------------
-        if (has_next) {
-            uint8_t* nimg = sRec + (p.n_rec_buf == 2 ? ((tile_no + 1) & 1) : 0) * IMG;
-            if (!phase_v(nimg, tile_tok0(next))) {
-                failed = true;
-                break;
+            if (p.n_rec_buf == 1) {
+                compute_barrier_or(false);                // the single image is rewritten by the values below
+                if (has_next) phase_v(par ^ 1, nimg, tile_tok0(next));
             }
-            if (tid == 0 && next + gridDim.x < p.n_tiles) issue_kv(sV, &tm_v, bar_v, next + gridDim.x);
+            nd = nd_next;
         }
-        nd = nd_next;
+        if (!ok && tid == 0) atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_TIMEOUT);
+        if (lane == 0 && warp < 8) tq_bulk_wait_all();   // the records must have landed before the CTA retires
     }
-    if (failed && tid == 0) atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_TIMEOUT);
-    if (lane == 0 && warp < 8) tq_bulk_wait_all();   // the records must have landed before the CTA retires
 
     tc_fence_before();
     __syncthreads();
@@ -669,6 +829,12 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
         if (((uintptr_t)consts->pi_limbs[i] & 15) || ((uintptr_t)consts->m_limbs[i] & 15)) return TQ_OK;
     if (n_tokens >= ((int64_t)1 << 31) - 256) return TQ_OK;   // 32-bit box coordinates
     if (encode_tiled_fn() == nullptr) return TQ_OK;
+    {   // the kernel's comparison arithmetic treats only the middle boundary as possibly (next to) zero
+        const int nb = (1 << (cfg.key_bits - 1)) - 1;
+        for (int i = 0; i < nb; ++i)
+            if (i != nb / 2 && !(fabsf(consts->boundaries[i]) >= 1e-30f && fabsf(consts->boundaries[i]) < 2.f)) return TQ_OK;
+        if (!(fabsf(consts->boundaries[nb / 2]) < 2.f)) return TQ_OK;
+    }
 
     TcParams p;
     p.n_tokens = n_tokens;
@@ -684,7 +850,9 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
         p.cb.centroids[i] = consts->centroids[i];
         p.cb.boundaries[i] = consts->boundaries[i];
     }
-    p.n_tiles = ((p.lead + n_tokens + TC_TOK - 1) / TC_TOK) * n_heads;
+    const int64_t n_tiles = ((p.lead + n_tokens + TC_TOK - 1) / TC_TOK) * n_heads;
+    if (n_tiles >= ((int64_t)1 << 30)) return TQ_OK;
+    p.n_tiles = (int)n_tiles;
 
     CUtensorMap tm_k, tm_v, tm_b[4];
     if (!make_rows_map(&tm_k, key, n_tokens, n_heads, stride_token, stride_head, p.tok_outer != 0) ||
@@ -697,7 +865,7 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
     const int mse_bits = cfg.key_bits - 1;
     const TqLayout L = tq_make_layout(TC_D, cfg.key_bits, cfg.value_bits);
     const size_t img = (size_t)8 * L.block_bytes;
-    const size_t fixed = (size_t)6 * MAT_BYTES + 4 * TC_TOK * sizeof(float) + 6 * sizeof(uint64_t) + 16 + 1024;
+    const size_t fixed = (size_t)6 * MAT_BYTES + 8 * TC_TOK * sizeof(float) + 11 * sizeof(uint64_t) + 16 + 1024;
     p.n_rec_buf = fixed + 2 * img <= SMEM_LIMIT ? 2 : 1;
     const size_t smem = fixed + (size_t)p.n_rec_buf * img;
     const int sms = tq_sm_count();
@@ -706,7 +874,7 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
     do {                                                                                                         \
         static TqSmemOptIn opt_in;                                                                               \
         if (tq_opt_in_smem(tq_store_tc_kernel<MB, VB>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;               \
-        tq_store_tc_kernel<MB, VB><<<grid, TC_THREADS, smem, st>>>(tm_k, tm_v, tm_b[0], tm_b[1], tm_b[2], tm_b[3], p); \
+        tq_store_tc_kernel<MB, VB><<<grid, TC_LAUNCH, smem, st>>>(tm_k, tm_v, tm_b[0], tm_b[1], tm_b[2], tm_b[3], p); \
     } while (0)
     if (mse_bits == 2 && cfg.value_bits == 2) TQ_TC(2, 2);
     else if (mse_bits == 2) TQ_TC(2, 4);
