@@ -152,6 +152,26 @@ int tq_store(const tq_consts* consts, const void* key, const void* value, tq_dty
              const int64_t* slot_mapping, const int32_t* block_table, int64_t start_pos,
              const tq_pool* pool, void* stream);
 
+/* Compress the first `n_tokens` tokens of a sequence that lives in a PAGED
+ * bf16 cache - blocks of `src_block_size` tokens, element (b, t, h, :) of the
+ * key plane at key_cache + b*stride_block + t*stride_token + h*stride_head
+ * (in elements; the value plane likewise from value_cache), logical block j
+ * of the sequence at physical block src_block_table[j] (device memory) - and
+ * write them into the pool at positions start_pos.. of block_table, in one
+ * launch whose tile loader walks the table (nothing is gathered first).
+ * Replaces the gather loop of KVCaptureEngine.ingest_prefill_from_paged_cache
+ * (capture.py:187-217) followed by append_chunk; for vLLM's
+ * (2, num_blocks, block_size, H, D) tensor pass the two planes' bases.
+ * Needs the tensor-core store (bf16; head_dim 128, or 256 with 3-bit keys and
+ * 2-bit values; split operands in `consts`), a power-of-two src_block_size
+ * >= 16, start_pos a multiple of 16 and 16-byte aligned planes and strides:
+ * anything else returns TQ_ERR_UNSUPPORTED and nothing is launched.  Records
+ * are byte-identical to tq_store on the gathered rows. */
+int tq_store_paged(const tq_consts* consts, const void* key_cache, const void* value_cache, tq_dtype dtype,
+                   int64_t src_num_blocks, int32_t src_block_size, int32_t n_heads, int64_t stride_block,
+                   int64_t stride_token, int64_t stride_head, const int32_t* src_block_table, int64_t n_tokens,
+                   const int32_t* block_table, int64_t start_pos, const tq_pool* pool, void* stream);
+
 /* Status word of the tensor-core store kernel: 0, or TQ_ERR_TIMEOUT / TQ_ERR_RANGE
  * if one of its bounded waits ran out or a block index was out of range.
  * Synchronises the device. */

@@ -553,12 +553,12 @@ def test_random_shapes_tensor_core_vs_cuda_core(seed, dev):
     torch.testing.assert_close(a, b, rtol=3e-2, atol=3e-3)
 
 
-@pytest.mark.parametrize("kb,vb,h,n", [(3, 2, 8, 8192), (4, 4, 4, 3000), (3, 4, 2, 129), (4, 2, 1, 16), (3, 2, 3, 2047)])
-def test_tensor_core_store_matches_fp32_store_and_oracle(kb, vb, h, n, dev):
-    """tcgen05 store kernel (head_dim 128, bf16, block-aligned start) against the fp32 store
-    kernel and the oracle: values bit exact, codes / sign bits within the tie budget."""
+@pytest.mark.parametrize("d,kb,vb,h,n", [(128, 3, 2, 8, 8192), (128, 4, 4, 4, 3000), (128, 3, 4, 2, 129), (128, 4, 2, 1, 16),
+                                         (128, 3, 2, 3, 2047), (256, 3, 2, 4, 8192), (256, 3, 2, 1, 16), (256, 3, 2, 3, 1999)])
+def test_tensor_core_store_matches_fp32_store_and_oracle(d, kb, vb, h, n, dev):
+    """tcgen05 store kernels (head_dim 128: every bit width; head_dim 256: 3-bit keys, 2-bit values)
+    against the fp32 store kernel and the oracle: values bit exact, codes / sign bits within the tie budget."""
     from turboquant_b200 import _engine as E
-    d = 128
     k, v = O.synth_kv(n, h, d, seed=77 + n, dtype=torch.bfloat16)
     v[3 % n, 0, :32] = 0.25            # constant group
     k[5 % n, h - 1, :] = 0             # zero key
@@ -781,14 +781,14 @@ def test_host_io_paths_and_length_bounds(dev):
     assert ws.status() == 0 and torch.equal(o_big, o_ok)
 
 
-@pytest.mark.parametrize("kb,vb", [(3, 2), (4, 4), (3, 4)])
-def test_tensor_core_store_destinations(kb, vb, dev):
-    """The tcgen05 store kernel with every kind of destination: appends that start in the middle of a
+@pytest.mark.parametrize("d,kb,vb", [(128, 3, 2), (128, 4, 4), (128, 3, 4), (256, 3, 2)])
+def test_tensor_core_store_destinations(d, kb, vb, dev):
+    """The tcgen05 store kernels with every kind of destination: appends that start in the middle of a
     block (the block's earlier tokens must survive), single-token appends, slot mappings (whole blocks
     in order, shuffled slots, skipped tokens) and a head-major input layout.  Whatever the route, a
     token's record bytes are the same as in one aligned whole-sequence call."""
     from turboquant_b200 import _engine as E
-    d, h, n = 128, 4, 1000
+    h, n = 4, 1000
     c = E.LayerConstants(d, kb, vb, dev, seed=49)
     k, v = O.synth_kv(n, h, d, seed=91, dtype=torch.bfloat16)
     kd, vd = k.to(dev), v.to(dev)
@@ -889,3 +889,67 @@ def test_decode_stays_inside_its_workspace(d, h, qh, kb, vb, dev):
             assert bool((buf[need.value:] == 0xA5).all()), (kernel, with_ring)
             assert ws.status() == 0
     assert _cos(outs[0], outs[2]) >= 0.9999 and _cos(outs[1], outs[3]) >= 0.9999
+
+
+@pytest.mark.parametrize("d,kb,vb,bs,n,hnd", [(128, 3, 2, 16, 1000, False), (128, 4, 4, 32, 4096, False),
+                                              (128, 3, 2, 128, 1300, True), (128, 3, 4, 256, 1700, False),
+                                              (256, 3, 2, 16, 2049, False), (256, 3, 2, 64, 1777, True),
+                                              (128, 3, 2, 8, 1000, False), (256, 4, 4, 16, 1500, False)])
+def test_paged_cache_to_compressed_store(d, kb, vb, bs, n, hnd, dev):
+    """A sequence held in a vLLM-shaped paged bf16 cache (2, num_blocks, block_size, H, D) behind a
+    shuffled block table, compressed by the table-walking launch (capture.py:187-217 gathers the rows
+    first): pool records byte-identical to `append_chunk` on the gathered rows, and within the tie
+    budget of the oracle.  The last two cases do not fit the table-walking kernel (block size 8; a
+    record image too large for head_dim 256) and take the gathering route with the same results."""
+    from turboquant_b200 import CompressedKVStore, KVCaptureEngine, _engine as E
+    h = 4
+    k, v = O.synth_kv(n, h, d, seed=400 + n, dtype=torch.bfloat16)
+    g = torch.Generator().manual_seed(n)
+    nblk = (n + bs - 1) // bs
+    num_blocks = nblk + 7
+    table = torch.randperm(num_blocks, generator=g)[:nblk].int()
+    # every block of the cache starts as NaN: rows past the last token must not leak into the records
+    if hnd:
+        cache = torch.full((2, num_blocks, h, bs, d), float("nan"), dtype=torch.bfloat16).permute(0, 1, 3, 2, 4)
+    else:
+        cache = torch.full((2, num_blocks, bs, h, d), float("nan"), dtype=torch.bfloat16)
+    for j in range(nblk):
+        m = min(bs, n - j * bs)
+        cache[0, table[j], :m] = k[j * bs:j * bs + m]
+        cache[1, table[j], :m] = v[j * bs:j * bs + m]
+    cache_d = cache.to(dev) if not hnd else cache.permute(0, 1, 3, 2, 4).contiguous().to(dev).permute(0, 1, 3, 2, 4)
+    table_d = table.to(dev)
+
+    a = CompressedKVStore(d, h, kb, vb, device=dev, capacity_tokens=n)
+    a.append_from_paged(cache_d[0], cache_d[1], table_d, n)
+    b = CompressedKVStore(d, h, kb, vb, device=dev, capacity_tokens=n)
+    b.append_chunk(k.to(dev), v.to(dev))
+    assert E.store_status() == 0 and a.num_tokens == b.num_tokens == n
+    used = E.blocks_for(n)
+    nbytes = used * h * a.consts.block_bytes
+    assert torch.equal(a.pool.data[:nbytes], b.pool.data[:nbytes])
+    fits = bs >= 16 and (d == 128 or (kb, vb) == (3, 2))
+    direct = E.store_paged(a.consts, E.BlockPool(a.consts, h, used), cache_d[0], cache_d[1], src_block_table=table_d,
+                           n_tokens=n, block_table=E.identity_block_table(used, dev))
+    assert direct == fits and E.store_status() == 0
+
+    ost = O.OracleStore(d, h, kb, vb, a.consts.centroids_cpu, a.consts.boundaries_cpu, pi=a.consts.Pi.cpu(), s=a.consts.S.cpu())
+    ost.append_chunk(k, v)
+    of = ost.get_flat_cache()
+    pa = E.pool_to_planes(a.consts, a.pool, a.block_table, n)
+    assert _code_frac(pa.mse_indices.cpu(), torch.from_numpy(of.mse_indices), 2 if kb == 3 else 4) <= TIE_BUDGET
+    assert _bit_frac(pa.qjl_signs.cpu(), torch.from_numpy(of.qjl_signs)) <= TIE_BUDGET
+    assert torch.equal(pa.v_data.cpu(), torch.from_numpy(of.v_data))
+
+    # the engine's prefill entry: all but the ring's tokens compressed, the last ones exact in the ring
+    cap = 48
+    e1 = KVCaptureEngine(CompressedKVStore(d, h, kb, vb, device=dev, capacity_tokens=n), ring_capacity=cap, device=dev)
+    e1.ingest_prefill_from_paged_cache(cache_d, n, table_d, bs)
+    e2 = KVCaptureEngine(CompressedKVStore(d, h, kb, vb, device=dev, capacity_tokens=n), ring_capacity=cap, device=dev)
+    e2.ingest_prefill(k.to(dev), v.to(dev), n)
+    assert e1.total_compressed_tokens == e2.total_compressed_tokens == n - cap and e1.total_buffered_tokens == cap
+    u2 = E.blocks_for(n - cap) * h * e1.store.consts.block_bytes
+    assert torch.equal(e1.store.pool.data[:u2], e2.store.pool.data[:u2])
+    for x, y in zip(e1.ring.peek(), e2.ring.peek()):
+        assert torch.equal(x, y)
+    assert E.store_status() == 0

@@ -233,6 +233,35 @@ def store(consts: LayerConstants, pool: BlockPool, key: torch.Tensor, value: tor
                          start_pos, C.byref(pool.c), stream_ptr(consts.device)), "tq_store")
 
 
+def store_paged(consts: LayerConstants, pool: BlockPool, key_cache: torch.Tensor, value_cache: torch.Tensor, *,
+                src_block_table: torch.Tensor, n_tokens: int, block_table: torch.Tensor, start_pos: int = 0) -> bool:
+    """Compress the first n_tokens tokens of a sequence held in a paged cache.
+
+    key_cache / value_cache: (num_blocks, block_size, H, D) views (any block / token / head strides, D
+    contiguous, same strides for both); src_block_table: int32 device tensor, logical -> physical block.
+    Returns False, with nothing launched, when the call does not fit the table-walking tensor-core
+    kernel (the caller then gathers the rows and uses `store`).
+    """
+    require_cuda(key_cache, "key_cache")
+    require_cuda(value_cache, "value_cache")
+    if key_cache.dtype != value_cache.dtype or key_cache.shape != value_cache.shape or \
+            key_cache.stride() != value_cache.stride() or key_cache.dim() != 4 or key_cache.stride(3) != 1:
+        raise ValueError("key_cache and value_cache must be (num_blocks, block_size, H, D) views of one layout")
+    if src_block_table.dtype != torch.int32 or not src_block_table.is_cuda or not src_block_table.is_contiguous():
+        raise TypeError("src_block_table must be a contiguous int32 device tensor")
+    nb, bs, h, _ = key_cache.shape
+    if n_tokens > src_block_table.numel() * bs:
+        raise ValueError("src_block_table is shorter than n_tokens")
+    rc = lib().tq_store_paged(C.byref(consts.c), key_cache.data_ptr(), value_cache.data_ptr(), dtype_code(key_cache.dtype),
+                              nb, bs, h, key_cache.stride(0), key_cache.stride(1), key_cache.stride(2),
+                              src_block_table.data_ptr(), n_tokens, block_table.data_ptr(), start_pos,
+                              C.byref(pool.c), stream_ptr(consts.device))
+    if rc == _lib.TQ_ERR_UNSUPPORTED:
+        return False
+    check(rc, "tq_store_paged")
+    return True
+
+
 def decode(consts: LayerConstants, pool: BlockPool, ws: Workspace, query: torch.Tensor,
            block_table: torch.Tensor, seq_lens: torch.Tensor, max_seq_len: int, *,
            ring_k: Optional[torch.Tensor] = None, ring_v: Optional[torch.Tensor] = None,

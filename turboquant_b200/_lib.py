@@ -14,6 +14,7 @@ from .build import LIB_PATH
 TQ_BLOCK_TOKENS = 16
 TQ_MAX_CENTROIDS = 16
 TQ_F32, TQ_BF16, TQ_F16 = 0, 1, 2
+TQ_ERR_UNSUPPORTED = -4
 
 
 class TQError(RuntimeError):
@@ -73,6 +74,9 @@ SIGNATURES = {
     "tq_store": (C.c_int, [C.POINTER(tq_consts), C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int32,
                            C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64, C.POINTER(tq_pool),
                            C.c_void_p]),
+    "tq_store_paged": (C.c_int, [C.POINTER(tq_consts), C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int32, C.c_int32,
+                                 C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
+                                 C.POINTER(tq_pool), C.c_void_p]),
     "tq_store_read_status": (C.c_int, [C.POINTER(C.c_int32)]),
     "tq_decode": (C.c_int, [C.POINTER(tq_consts), C.POINTER(tq_pool), C.POINTER(tq_decode_args), C.c_void_p]),
     "tq_decode_host_io": (C.c_int, [C.POINTER(tq_consts), C.POINTER(tq_pool), C.POINTER(tq_decode_args), C.c_void_p,

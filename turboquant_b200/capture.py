@@ -140,12 +140,21 @@ class KVCaptureEngine:
 
     def ingest_prefill_from_paged_cache(self, kv_cache_tensor: torch.Tensor, num_tokens: int,
                                         block_table: torch.Tensor, block_size: int) -> None:
-        """kv_cache_tensor (2, num_blocks, block_size, H, D); block_table maps logical to physical blocks."""
-        n_blocks = (num_tokens + block_size - 1) // block_size
-        phys = block_table[:n_blocks].long()
-        k = kv_cache_tensor[0].index_select(0, phys).reshape(-1, *kv_cache_tensor.shape[3:])[:num_tokens]
-        v = kv_cache_tensor[1].index_select(0, phys).reshape(-1, *kv_cache_tensor.shape[3:])[:num_tokens]
-        self.ingest_prefill(k, v, num_tokens)
+        """kv_cache_tensor (2, num_blocks, block_size, H, D); block_table maps logical to physical blocks
+        (reference capture.py:187-217).  All but the last `capacity` tokens go from the paged cache into
+        the compressed store in one launch that walks the table; only the ring's tokens are gathered."""
+        if kv_cache_tensor.shape[2] != block_size:
+            raise ValueError(f"block_size {block_size} does not match the cache's {kv_cache_tensor.shape[2]}")
+        cap = self.ring.capacity
+        n = max(num_tokens - cap, 0)
+        self.store.append_from_paged(kv_cache_tensor[0], kv_cache_tensor[1], block_table, n)
+        b0, b1 = n // block_size, (num_tokens + block_size - 1) // block_size
+        phys = block_table[b0:b1].long()
+        lo = n - b0 * block_size
+        k = kv_cache_tensor[0].index_select(0, phys).flatten(0, 1)[lo:lo + num_tokens - n]
+        v = kv_cache_tensor[1].index_select(0, phys).flatten(0, 1)[lo:lo + num_tokens - n]
+        self.ring.write(k, v, num_tokens - n)
+        self._prefill_done = True
 
     def ingest_decode(self, key: torch.Tensor, value: torch.Tensor, num_tokens: int) -> None:
         overflow = self.ring.write(key[:num_tokens], value[:num_tokens], num_tokens)

@@ -222,6 +222,14 @@ int tq_current_device();   // ordinal of the calling thread's current device, -1
 int tq_sm_count();         // multiprocessors of the current device (148 when the query fails)
 
 // Largest dynamic shared-memory size a kernel has been opted in for, per device.
+// A paged bf16 cache as the source of a store call (see tq_store_paged).
+struct TqPagedSource {
+    const int32_t* table;    // device: logical block of the sequence -> physical block
+    int64_t num_blocks;      // physical blocks in the cache
+    int32_t block_size;      // tokens per block
+    int64_t stride_block;    // elements between blocks
+};
+
 struct TqSmemOptIn {
     size_t bytes[TQ_MAX_DEVICES] = {};
 };

@@ -47,14 +47,16 @@ __global__ void __launch_bounds__(256, OCC) tq_qprep_kernel(const void* __restri
                                                        const float* __restrict__ pi_t,
                                                        const float* __restrict__ s_t, float* __restrict__ out,
                                                        uint32_t* __restrict__ frag, int G, int Qh, int mse_bits,
-                                                       const RingAppend ap) {
+                                                       const RingAppend ap, int groups) {
     // the decode kernel may start its set-up now; it waits for this grid before it reads our output
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     __shared__ float qsm[VPC * D];          // queries
     __shared__ float red[8 * VPC * 32];     // partial sums
     __shared__ float qn2[VPC];              // squared norms
-    const int64_t v0 = (int64_t)blockIdx.y * VPC;
-    const int nv = (int)min((int64_t)VPC, nvec - v0);
+    // A CTA takes `groups` consecutive groups of VPC vectors against the matrix slice it holds in
+    // registers (large batches: the slice is fetched once per CTA, not once per four vectors).
+    int64_t v0 = (int64_t)blockIdx.y * groups * VPC;
+    int nv = (int)min((int64_t)VPC, nvec - v0);
     constexpr int chunks = D / 32;
     const int which = blockIdx.x / chunks;            // 0: Pi^T, 1: S^T
     const int chunk = blockIdx.x % chunks;
@@ -116,6 +118,8 @@ __global__ void __launch_bounds__(256, OCC) tq_qprep_kernel(const void* __restri
         for (int b = threadIdx.x; b < ap.B; b += 256)
             if (ap.ring_lens[b] >= 0 && ap.ring_lens[b] < ap.capacity) ap.ring_lens[b] += 1;
     }
+#pragma unroll 1
+    for (int gi = 0; gi < groups && v0 < nvec; ++gi, v0 += VPC, nv = (int)min((int64_t)VPC, nvec - v0)) {
     if (ap.early_inputs) {
 #pragma unroll
         for (int u = 0; u < VPC * D / 256; ++u) qsm[threadIdx.x + u * 256] = qv[u];
@@ -178,36 +182,185 @@ __global__ void __launch_bounds__(256, OCC) tq_qprep_kernel(const void* __restri
             }
         }
     }
-    __syncthreads();   // shared memory is reused by the second pass
+    __syncthreads();   // shared memory is reused by the next group / the second pass
+    }
+    v0 = (int64_t)blockIdx.y * groups * VPC;
+    nv = (int)min((int64_t)VPC, nvec - v0);
+    }
+}
+
+// One element of the query preparation's output: the fp32 value and, when asked for, its place in the
+// fp16 MMA fragments of the tensor-core decode kernel.  `which` 0: rotated (q Pi^T), 1: sketched (q S^T);
+// `qn2`: squared norm of the query vector (the fragment's power-of-two scale is derived from it alone).
+template <int D>
+__device__ __forceinline__ void qprep_emit(float t, int64_t vec, int which, int col, float qn2, float* out, uint32_t* frag,
+                                           int G, int Qh, int mse_bits) {
+    out[(vec * 2 + which) * D + col] = t;
+    if (frag == nullptr) return;
+    const int qh = (int)(vec % Qh), g = qh % G;
+    const int64_t pair = (vec / Qh) * (Qh / G) + qh / G;   // (sequence, kv head)
+    const bool split = G > 4 || mse_bits == 3;             // separate rotated / sketched fragment sets
+    uint32_t* base = frag + pair * qf_words(D, split ? 8 : 4);
+    const float bound = sqrtf(qn2) * (which ? 2.f * sqrtf((float)D) : 1.f);
+    int e = 0;
+    if (bound > 0.f && bound < 3.0e38f) e = max(-100, min(100, 14 - ilogbf(bound)));
+    if (col == 0) reinterpret_cast<float*>(base)[which * 8 + g] = (float)e;
+    const int tig = col / (D / 4), rem = col % (D / 4);
+    int wi = rem >> 4, half = (rem >> 3) & 1, jf = rem & 7;
+    int r = wi * 8 + jf;
+    int sh = which ? sign_pos(sign_bit(wi, jf)) : 2 * code_pos(jf);
+    if (mse_bits == 3 && which == 0) {   // nibble codes: see tq_qprep_kernel
+        r = rem >> 1;
+        half = rem & 1;
+        sh = 0;
+    }
+    const int gid = split ? g : g + 4 * which;
+    const int set = split ? which : 0;
+    __half* dst = reinterpret_cast<__half*>(base + QF_HDR + ((set * (D / 8) + r) * 32 + gid * 4 + tig));
+    dst[half] = __float2half_rn(t * __int_as_float((127 + e - sh) << 23));
+}
+
+// Query preparation for large batches: a plain tiled fp32 product (64 vectors x 64 columns per CTA,
+// 4 x 4 outputs per thread) instead of the latency-oriented kernel above, whose CTAs re-read their
+// matrix slice and the queries from shared memory once per multiply-add.
+constexpr int QB_V = 64, QB_C = 64, QB_K = 32;
+template <int D>
+__global__ void __launch_bounds__(256) tq_qprep_batched_kernel(const void* __restrict__ q, int dt, int64_t nvec,
+                                                               const float* __restrict__ pi_t,
+                                                               const float* __restrict__ s_t, float* __restrict__ out,
+                                                               uint32_t* __restrict__ frag, int G, int Qh, int mse_bits) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    extern __shared__ __align__(16) float qb_smem[];
+    float* qT = qb_smem;                    // [D][QB_V] queries, transposed
+    float* mt = qT + D * QB_V;              // [QB_K][QB_C] matrix rows of the current k chunk
+    float* part = mt + QB_K * QB_C;         // [4][QB_V] partial squared norms
+    const int tid = threadIdx.x;
+    const int64_t v0 = (int64_t)blockIdx.y * QB_V;
+    const int col0 = blockIdx.x * QB_C;     // column of [Pi^T | S^T]
+    const int which = col0 / D, mcol0 = col0 % D;
+    const float* __restrict__ m = which ? s_t : pi_t;
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // the queries may come from the kernel ahead
+    {   // queries: 16-byte chunks, lanes walking the vectors so that the transposed stores spread over the banks
+        const int esz = dt == TQ_F32 ? 4 : 2, per = 16 / esz, chunks = D / per;
+        for (int i = tid; i < QB_V * chunks; i += 256) {
+            const int v = i & (QB_V - 1), c = i / QB_V;
+            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+            if (v0 + v < nvec)
+                raw = __ldg(reinterpret_cast<const uint4*>(static_cast<const char*>(q) + ((v0 + v) * D + (int64_t)c * per) * esz));
+            const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+            float* dst = qT + (c * per) * QB_V + v;
+            if (dt == TQ_F32) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) dst[j * QB_V] = __uint_as_float(w[j]);
+            } else if (dt == TQ_BF16) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    dst[(2 * j) * QB_V] = __uint_as_float(w[j] << 16);
+                    dst[(2 * j + 1) * QB_V] = __uint_as_float(w[j] & 0xffff0000u);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+                    dst[(2 * j) * QB_V] = f2.x;
+                    dst[(2 * j + 1) * QB_V] = f2.y;
+                }
+            }
+        }
+        __syncthreads();
+        const int v = tid & (QB_V - 1), qtr = tid >> 6;   // squared norm of vector v, a quarter of the channels each
+        float s2 = 0.f;
+        for (int k = qtr * (D / 4); k < (qtr + 1) * (D / 4); ++k) {
+            const float x = qT[k * QB_V + v];
+            s2 = fmaf(x, x, s2);
+        }
+        part[qtr * QB_V + v] = s2;
+    }
+    const int ty = tid >> 4, tx = tid & 15;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+#pragma unroll 1
+    for (int k0 = 0; k0 < D; k0 += QB_K) {
+        __syncthreads();   // queries stored (first round) / previous matrix chunk consumed
+        for (int i = tid; i < QB_K * QB_C / 4; i += 256) {
+            const int kk = i / (QB_C / 4), c4 = i % (QB_C / 4);
+            reinterpret_cast<float4*>(mt)[i] = __ldg(reinterpret_cast<const float4*>(m + (size_t)(k0 + kk) * D + mcol0) + c4);
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int kk = 0; kk < QB_K; ++kk) {
+            const float4 a = *reinterpret_cast<const float4*>(qT + (k0 + kk) * QB_V + 4 * ty);
+            const float4 b = *reinterpret_cast<const float4*>(mt + kk * QB_C + 4 * tx);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int v = 4 * ty + i;
+        if (v0 + v >= nvec) continue;
+        const float qn2 = (part[v] + part[QB_V + v]) + (part[2 * QB_V + v] + part[3 * QB_V + v]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            qprep_emit<D>(acc[i][j], v0 + v, which, mcol0 + 4 * tx + j, qn2, out, frag, G, Qh, mse_bits);
     }
 }
 
 int launch_qprep(const void* q, int dt, int64_t nvec, int D, const float* pi_t, const float* s_t, float* out,
                  uint32_t* frag, int G, int Qh, int mse_bits, const RingAppend& ap, cudaStream_t st) {
     cudaLaunchConfig_t cfg = {};
-    // four vectors per CTA: with eight the grid packs four CTAs onto each of the few SMs that free up first
-    // under a running decode kernel, and they then share one SM for the part after the wait (measured: slower)
-    constexpr int vpc = 4;
-    cfg.gridDim = dim3((unsigned)(2 * D / 32), (unsigned)((nvec + vpc - 1) / vpc));
-    cfg.blockDim = dim3(256);
-    cfg.dynamicSmemBytes = 0;
-    cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // its matrix loads may run under the previous kernel's tail
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    cfg.stream = st;
+    cfg.blockDim = dim3(256);
+    if (nvec >= 512 && ap.new_k == nullptr && !ap.early_inputs && ((uintptr_t)q & 15) == 0) {   // throughput kernel
+        const size_t smem = sizeof(float) * ((size_t)D * QB_V + QB_K * QB_C + 4 * QB_V);
+        cfg.gridDim = dim3((unsigned)(2 * D / QB_C), (unsigned)((nvec + QB_V - 1) / QB_V));
+        cfg.dynamicSmemBytes = smem;
+        const int dtb = dt;
+        cudaError_t eb;
+        if (D == 128) {
+            static TqSmemOptIn opt_in;
+            if (tq_opt_in_smem(tq_qprep_batched_kernel<128>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;
+            eb = cudaLaunchKernelEx(&cfg, tq_qprep_batched_kernel<128>, q, dtb, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits);
+        } else {
+            static TqSmemOptIn opt_in;
+            if (tq_opt_in_smem(tq_qprep_batched_kernel<256>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;
+            eb = cudaLaunchKernelEx(&cfg, tq_qprep_batched_kernel<256>, q, dtb, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits);
+        }
+        return eb == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
+    }
+    // four vectors per CTA: with eight the grid packs four CTAs onto each of the few SMs that free up first
+    // under a running decode kernel, and they then share one SM for the part after the wait (measured: slower)
+    constexpr int vpc = 4;
+    // large batches: about three waves of CTAs, each working through several groups of four vectors
+    const int64_t n_groups = (nvec + vpc - 1) / vpc;
+    const int64_t ctas_y_wanted = (3 * (int64_t)tq_sm_count() * 2) / (2 * D / 32) + 1;
+    int groups = (int)((n_groups + ctas_y_wanted - 1) / ctas_y_wanted);
+    if (groups < 1 || ap.early_inputs) groups = 1;
+    if (groups > 64) groups = 64;
+    cfg.gridDim = dim3((unsigned)(2 * D / 32), (unsigned)((n_groups + groups - 1) / groups));
+    cfg.dynamicSmemBytes = 0;
     const int dti = dt;
     cudaError_t e;
     const bool small = cfg.gridDim.x * cfg.gridDim.y <= 256u;
     if (D == 128 && small)
-        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<128, vpc, 2>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
+        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<128, vpc, 2>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap, groups);
     else if (D == 128)
-        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<128, vpc, 3>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
+        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<128, vpc, 3>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap, groups);
     else if (small)
-        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<256, vpc, 2>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
+        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<256, vpc, 2>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap, groups);
     else
-        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<256, vpc, 3>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap);
+        e = cudaLaunchKernelEx(&cfg, tq_qprep_kernel<256, vpc, 3>, q, dti, nvec, pi_t, s_t, out, frag, G, Qh, mse_bits, ap, groups);
     return e == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 

@@ -286,7 +286,7 @@ int launch_f32(const StoreParams& p, int64_t n_tokens, int n_heads, cudaStream_t
 int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* value, tq_dtype dtype, int64_t n_tokens,
                        int32_t n_heads, int64_t stride_token, int64_t stride_head, const int64_t* slot_mapping,
                        const int32_t* block_table, int64_t start_pos, const tq_pool* pool, cudaStream_t st,
-                       int* handled);
+                       int* handled, const TqPagedSource* paged);
 
 extern "C" int tq_store(const tq_consts* consts, const void* key, const void* value, tq_dtype dtype, int64_t n_tokens,
                         int32_t n_heads, int64_t stride_token, int64_t stride_head, const int64_t* slot_mapping,
@@ -306,7 +306,7 @@ extern "C" int tq_store(const tq_consts* consts, const void* key, const void* va
 
     int handled = 0;
     rc = tq_store_tc_launch(consts, key, value, dtype, n_tokens, n_heads, stride_token, stride_head, slot_mapping,
-                            block_table, start_pos, pool, st, &handled);
+                            block_table, start_pos, pool, st, &handled, nullptr);
     if (rc != TQ_OK || handled) return rc;
 
     StoreParams p;
@@ -343,4 +343,30 @@ extern "C" int tq_store(const tq_consts* consts, const void* key, const void* va
         TQ_LAUNCH(256, TQ_F16);
     }
 #undef TQ_LAUNCH
+}
+
+extern "C" int tq_store_paged(const tq_consts* consts, const void* key_cache, const void* value_cache, tq_dtype dtype,
+                              int64_t src_num_blocks, int32_t src_block_size, int32_t n_heads, int64_t stride_block,
+                              int64_t stride_token, int64_t stride_head, const int32_t* src_block_table,
+                              int64_t n_tokens, const int32_t* block_table, int64_t start_pos, const tq_pool* pool,
+                              void* stream) {
+    if (!consts || !key_cache || !value_cache || !src_block_table || !block_table || !pool || !pool->base)
+        return TQ_ERR_NULL;
+    int rc = tq_check_config(&consts->cfg);
+    if (rc != TQ_OK) return rc;
+    if (n_tokens < 0 || n_heads <= 0 || start_pos < 0 || src_num_blocks <= 0 || src_block_size <= 0) return TQ_ERR_SHAPE;
+    if (n_heads != pool->num_kv_heads || pool->num_blocks <= 0) return TQ_ERR_SHAPE;
+    if (stride_token < consts->cfg.head_dim || stride_block < consts->cfg.head_dim) return TQ_ERR_SHAPE;
+    if (((uintptr_t)pool->base & 15) != 0) return TQ_ERR_ALIGN;
+    if (n_tokens == 0) return TQ_OK;
+    TqPagedSource src;
+    src.table = src_block_table;
+    src.num_blocks = src_num_blocks;
+    src.block_size = src_block_size;
+    src.stride_block = stride_block;
+    int handled = 0;
+    rc = tq_store_tc_launch(consts, key_cache, value_cache, dtype, n_tokens, n_heads, stride_token, stride_head, nullptr,
+                            block_table, start_pos, pool, (cudaStream_t)stream, &handled, &src);
+    if (rc != TQ_OK) return rc;
+    return handled ? TQ_OK : TQ_ERR_UNSUPPORTED;
 }

@@ -61,6 +61,11 @@ struct TcParams {
     int n_tiles;                   // token tiles x heads (the launcher keeps it below 2^31)
     int n_rec_buf;                 // record images in shared memory (2 when they fit)
     int tok_outer;                 // tensor-map dimension order: 1 = (channel, head, token), 0 = (channel, token, head)
+    // paged source (a cache of fixed-size token blocks addressed through a table) instead of flat rows:
+    const int32_t* src_table;      // logical source block -> physical block; nullptr: flat rows
+    int32_t src_num_blocks;        // physical blocks of the source cache
+    int src_bs_log2;               // log2 of its block size in tokens (>= 4)
+    int64_t src_tail_block;        // logical block that holds fewer than a block's tokens (-1: none)
 };
 
 __device__ int g_tq_store_status;   // 0 or a tq_status left by a bounded wait that ran out
@@ -81,6 +86,12 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* tm, in
         ::"r"(tq_smem_u32(dst)), "l"(tm), "r"(x), "r"(y), "r"(z), "r"(tq_smem_u32(bar))
         : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* tm, int x, int y, int z, int w, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+        ::"r"(tq_smem_u32(dst)), "l"(tm), "r"(x), "r"(y), "r"(z), "r"(w), "r"(tq_smem_u32(bar))
+        : "memory");
+}
 
 // K-major operand tile written by a 128-byte-swizzled TMA box: rows of 128 bytes, 8-row groups 1024 bytes apart
 __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
@@ -90,6 +101,15 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 // kind::f16 instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, N = 128, M = 128
 constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 
+constexpr uint32_t IDESC_N256 = (1u << 4) | (1u << 7) | (1u << 10) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
+// D[tmem] (+)= A[smem] * B[smem], N = 256
+__device__ __forceinline__ void umma_ss_n256(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(IDESC_N256), "r"(accumulate)
+        : "memory");
+}
 // D[tmem] (+)= A[tmem] * B[smem]
 __device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t accumulate) {
     asm volatile(
@@ -176,7 +196,7 @@ __device__ __forceinline__ int rec_byte_offset(const TqLayout& L, int tl, int cb
 //                     in [0, 128); the code sits in the low mantissa bits
 // Codes go to the record image in the decode kernel's byte order, scale / zero point group-major.
 // ---------------------------------------------------------------------------
-template <int VAL_BITS>
+template <int VAL_BITS, int D = TC_D>
 __device__ __forceinline__ void quantize_value_group(const uint4 (&raw)[4], uint8_t* rec, const TqLayout& L, int tl,
                                                      int grp, bool wr) {
     constexpr uint32_t N_LEVELS = (1u << VAL_BITS) - 1u;
@@ -212,13 +232,13 @@ __device__ __forceinline__ void quantize_value_group(const uint4 (&raw)[4], uint
 #pragma unroll
         for (int bt = 0; bt < 8; ++bt) {   // byte = four codes, LSB first (kv_cache.py:80-84)
             const uint32_t t = code[2 * bt] | (code[2 * bt + 1] << 4);
-            vc[tq_vcode_native(TC_D, 2, tl, grp * 8 + bt)] = (uint8_t)(t | (t >> 14));
+            vc[tq_vcode_native(D, 2, tl, grp * 8 + bt)] = (uint8_t)(t | (t >> 14));
         }
     } else {
 #pragma unroll
         for (int bt = 0; bt < 16; ++bt) {  // byte = two codes (kv_cache.py:86-90)
             const uint32_t t = code[bt];
-            vc[tq_vcode_native(TC_D, 4, tl, grp * 16 + bt)] = (uint8_t)(t | (t >> 12));
+            vc[tq_vcode_native(D, 4, tl, grp * 16 + bt)] = (uint8_t)(t | (t >> 12));
         }
     }
 }
@@ -265,6 +285,101 @@ __device__ __forceinline__ void bucket(const BookRegs<MSE_BITS>& bk, float y, fl
     y_minus_c = r;
 }
 
+// Destination of one image block (16 rows) of a tile: asked for early, looked at when the records leave
+// (the loaded words are not touched before that - not even widened - so nobody waits for them).
+struct RecordDest {
+    int32_t blk = -1;     // block-table mode, lane 0: physical block
+    int64_t slot = -1;    // slot mode: slot of row `lane & 15`
+    bool asked = false;
+};
+__device__ __forceinline__ void ask_destination(const TcParams& p, int64_t tok0, int warp, int lane, RecordDest& d) {
+    if (warp >= 8) return;
+    if (p.slot_mapping == nullptr) {
+        const int64_t first = tok0 + warp * TQ_BLOCK_TOKENS;      // token index of the block's first row
+        d.asked = lane == 0 && first < p.n_tokens && first + TQ_BLOCK_TOKENS > 0;
+        if (d.asked) d.blk = __ldg(p.block_table + ((p.start_pos + first) >> 4));
+    } else {
+        const int64_t i = tok0 + warp * TQ_BLOCK_TOKENS + (lane & 15);
+        if (i >= 0 && i < p.n_tokens) d.slot = __ldg(p.slot_mapping + i);
+    }
+}
+// Warp j < 8 sends image block j on its way: one bulk (TMA) store when the block is a whole record of
+// the pool, a byte scatter to each token's own slot otherwise.
+__device__ __forceinline__ void leave_records(const TcParams& p, const TqLayout& L, const uint8_t* img, int h, int j,
+                                              int lane, const RecordDest& d) {
+    const int BB = L.block_bytes;
+    if (p.slot_mapping == nullptr) {
+        if (d.asked) {
+            if (d.blk >= 0 && d.blk < p.num_blocks) {
+                tq_bulk_s2g(p.pool + ((int64_t)d.blk * p.H + h) * (int64_t)BB, img + j * BB, (uint32_t)BB);
+                tq_bulk_commit();
+            } else {
+                atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_RANGE);
+            }
+        }
+        return;
+    }
+    // slot mapping: sixteen rows that fill one block in order leave as a whole record, anything else is
+    // scattered byte by byte
+    int64_t slot = d.slot;
+    if (slot >= 0 && (slot >> 4) >= p.num_blocks) {
+        atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_RANGE);
+        slot = -1;
+    }
+    const int64_t slot0 = __shfl_sync(0xffffffffu, slot, 0);
+    const bool whole = __all_sync(0xffffffffu, slot0 >= 0 && (slot0 & 15) == 0 && slot == slot0 + (lane & 15));
+    if (whole) {
+        if (lane == 0) {
+            tq_bulk_s2g(p.pool + ((slot0 >> 4) * p.H + h) * (int64_t)BB, img + j * BB, (uint32_t)BB);
+            tq_bulk_commit();
+        }
+        return;
+    }
+    const int per_tok = BB / TQ_BLOCK_TOKENS;
+    const uint8_t* src = img + j * BB;
+    for (int t = 0; t < TQ_BLOCK_TOKENS; ++t) {
+        const int64_t s = __shfl_sync(0xffffffffu, slot, t);
+        if (s < 0) continue;
+        uint8_t* dst = p.pool + ((s >> 4) * p.H + h) * (int64_t)BB;
+        for (int cb = lane; cb < per_tok; cb += 32)
+            dst[rec_byte_offset(L, (int)(s & 15), cb)] = src[rec_byte_offset(L, t, cb)];
+    }
+}
+
+// Rows of one tile (128 tokens of one head, n_cbox boxes of 64 channels) from a PAGED source: the tile
+// is covered by 128 / block_size source blocks (or lies inside one), each looked up in the source table
+// and fetched by its own lane of the issuing warp - the swizzle pattern depends on the shared-memory
+// address alone, so boxes of 16+ rows stacked 1024-byte aligned form the same image as one 128-row box.
+// Blocks past the end are requested out of range (zero fill); the block that is only partly valid goes
+// through `tm_tail`, the same cache with its token dimension cut to the valid rows, so that rows past
+// the last token read as zeros exactly as they do from flat rows.
+__device__ __forceinline__ void issue_paged_rows(uint8_t* dst, const CUtensorMap* tm, const CUtensorMap* tm_tail,
+                                                 uint64_t* bar, const TcParams& p, int64_t tok0, int head, int n_cbox,
+                                                 int lane, bool is_elected) {
+    const int lg = p.src_bs_log2;
+    const int rows = lg >= 7 ? TC_TOK : (1 << lg);          // token rows per box
+    const int per_tile = TC_TOK / rows;
+    if (is_elected) tq_mbar_expect_tx(bar, (uint32_t)(n_cbox * BOX_BYTES));
+    __syncwarp();
+    if (lane < per_tile * n_cbox) {
+        const int jj = lane / n_cbox, cb = lane - jj * n_cbox;
+        const int64_t tok = tok0 + (int64_t)jj * rows;
+        const int64_t sb = tok >> lg;
+        int32_t phys = p.src_num_blocks;                     // out of range: zeros
+        if (tok < p.n_tokens) {
+            phys = __ldg(p.src_table + sb);
+            if (phys < 0 || phys >= p.src_num_blocks) {
+                atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_RANGE);
+                phys = p.src_num_blocks;
+            }
+        }
+        const int in_blk = (int)(tok & (((int64_t)1 << lg) - 1));
+        tma_load_4d(dst + cb * BOX_BYTES + jj * rows * 128, sb == p.src_tail_block ? tm_tail : tm, 64 * cb,
+                    p.tok_outer ? head : in_blk, p.tok_outer ? in_blk : head, phys, bar);
+    }
+    __syncwarp();
+}
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tq_smem_u32(bar)) : "memory");
 }
@@ -286,6 +401,7 @@ __device__ __forceinline__ bool compute_barrier_or(bool flag) {
 template <int MSE_BITS, int VAL_BITS>
 __global__ void __launch_bounds__(TC_LAUNCH, 1)
 tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                   const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_vt,
                    const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
                    const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_b3,
                    const TcParams p) {
@@ -392,8 +508,12 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
                 asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
                 return pred != 0;
             };
-            auto issue_kv = [&](uint8_t* dst, const CUtensorMap* tm, uint64_t* bar, int tile) {
+            auto issue_kv = [&](uint8_t* dst, const CUtensorMap* tm, const CUtensorMap* tm_tail, uint64_t* bar, int tile) {
                 const int hh = tile_head(tile), t0 = (int)tile_tok0(tile);
+                if (p.src_table != nullptr) {
+                    issue_paged_rows(dst, tm, tm_tail, bar, p, tile_tok0(tile), hh, 2, lane, elected());
+                    return;
+                }
                 if (elected()) {
                     tq_mbar_expect_tx(bar, 2 * BOX_BYTES);
                     tma_load_3d(dst, tm, 0, p.tok_outer ? hh : t0, p.tok_outer ? t0 : hh, bar);
@@ -454,8 +574,8 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
                 }
             }
             __syncwarp();
-            issue_kv(sX, &tm_k, bar_k, tile0);
-            issue_kv(sV, &tm_v, bar_v, tile0);
+            issue_kv(sX, &tm_k, &tm_kt, bar_k, tile0);
+            issue_kv(sV, &tm_v, &tm_vt, bar_v, tile0);
             if (rmw) {   // the block this append continues, into block 0 of the first record image
                 if (elected()) {
                     const int64_t phys = p.block_table[p.start_pos >> 4];
@@ -476,16 +596,16 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
                 const int next = tile + (int)gridDim.x;
                 if (!wait1(bar_n, i & 1)) return false;
                 issue_mma_y();
-                if (next < p.n_tiles) issue_kv(sX, &tm_k, bar_k, next);
+                if (next < p.n_tiles) issue_kv(sX, &tm_k, &tm_kt, bar_k, next);
                 if (p.n_rec_buf == 2) {
                     if (!wait1(bar_vf, i & 1)) return false;
-                    if (next < p.n_tiles) issue_kv(sV, &tm_v, bar_v, next);
+                    if (next < p.n_tiles) issue_kv(sV, &tm_v, &tm_vt, bar_v, next);
                 }
                 if (!wait1(bar_a, i & 1)) return false;
                 issue_mma_e();
                 if (p.n_rec_buf != 2) {   // with one record image the values follow the record store
                     if (!wait1(bar_vf, i & 1)) return false;
-                    if (next < p.n_tiles) issue_kv(sV, &tm_v, bar_v, next);
+                    if (next < p.n_tiles) issue_kv(sV, &tm_v, &tm_vt, bar_v, next);
                 }
                 return true;
             };
@@ -592,21 +712,8 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
             uint8_t* nimg = sRec + (p.n_rec_buf == 2 ? ((tile_no + 1) & 1) : 0) * IMG;
             uint8_t* rec = img + blk_l * BB;
 
-            // destination of image block `warp` (warps 0-7): asked for now, looked at when the records leave
-            // (the loaded words are not touched before that - not even widened - so nobody waits for them here)
-            int32_t dest_blk = -1;    // block-table mode, lane 0: physical block
-            int64_t dest_slot = -1;   // slot mode: slot of row `lane & 15`
-            bool dest_asked = false;
-            if (warp < 8) {
-                if (!slot_mode) {
-                    const int64_t first = tok0 + warp * TQ_BLOCK_TOKENS;      // token index of the block's first row
-                    dest_asked = lane == 0 && first < p.n_tokens && first + TQ_BLOCK_TOKENS > 0;
-                    if (dest_asked) dest_blk = __ldg(p.block_table + ((p.start_pos + first) >> 4));
-                } else {
-                    const int64_t i = tok0 + warp * TQ_BLOCK_TOKENS + (lane & 15);
-                    if (i >= 0 && i < p.n_tokens) dest_slot = __ldg(p.slot_mapping + i);
-                }
-            }
+            RecordDest dest;
+            ask_destination(p, tok0, warp, lane, dest);
 
             // ---------------- C: codes and rotated-space residual of channels [32q, 32q+32) ----------------
             bad |= !wait_warp(bar_y, par);
@@ -706,44 +813,7 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
             // ---------------- the tile's block records leave ----------------
             if (warp < 8) {
-                const int j = warp;                                   // image block
-                if (!slot_mode) {
-                    if (dest_asked) {
-                        if (dest_blk >= 0 && dest_blk < p.num_blocks) {
-                            tq_bulk_s2g(p.pool + ((int64_t)dest_blk * p.H + h) * (int64_t)BB, img + j * BB, (uint32_t)BB);
-                            tq_bulk_commit();
-                        } else {
-                            atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_RANGE);
-                        }
-                    }
-                } else {
-                    // slot mapping: sixteen rows that fill one block in order leave as a whole record,
-                    // anything else is scattered byte by byte to each token's own slot
-                    int64_t slot = dest_slot;
-                    if (slot >= 0 && (slot >> 4) >= p.num_blocks) {
-                        atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_RANGE);
-                        slot = -1;
-                    }
-                    const int64_t slot0 = __shfl_sync(0xffffffffu, slot, 0);
-                    const bool whole =
-                        __all_sync(0xffffffffu, slot0 >= 0 && (slot0 & 15) == 0 && slot == slot0 + (lane & 15));
-                    if (whole) {
-                        if (lane == 0) {
-                            tq_bulk_s2g(p.pool + ((slot0 >> 4) * p.H + h) * (int64_t)BB, img + j * BB, (uint32_t)BB);
-                            tq_bulk_commit();
-                        }
-                    } else {
-                        const int per_tok = BB / TQ_BLOCK_TOKENS;
-                        const uint8_t* src = img + j * BB;
-                        for (int t = 0; t < TQ_BLOCK_TOKENS; ++t) {
-                            const int64_t s = __shfl_sync(0xffffffffu, slot, t);
-                            if (s < 0) continue;
-                            uint8_t* dst = p.pool + ((s >> 4) * p.H + h) * (int64_t)BB;
-                            for (int cb = lane; cb < per_tok; cb += 32)
-                                dst[rec_byte_offset(L, (int)(s & 15), cb)] = src[rec_byte_offset(L, t, cb)];
-                        }
-                    }
-                }
+                leave_records(p, L, img, h, warp, lane, dest);
                 if (lane == 0 && p.n_rec_buf == 1) tq_bulk_wait_all_read();
             }
             if (p.n_rec_buf == 1) {
@@ -754,6 +824,384 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         }
         if (!ok && tid == 0) atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_TIMEOUT);
         if (lane == 0 && warp < 8) tq_bulk_wait_all();   // the records must have landed before the CTA retires
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// head_dim 256
+// ---------------------------------------------------------------------------
+// Same arithmetic, different residency: four 256 x 256 operand matrices (512 KB) cannot stay in shared
+// memory, and a 128-row A operand of 256 packed channels takes 128 tensor-memory columns, so that u, e',
+// r'_hi and r'_lo alone would fill it.  Here the A operands live in SHARED memory - the key rows land by
+// TMA, are normalised in place, e' takes the place of the value rows once they are quantised, and r'_hi /
+// r'_lo overwrite both after the first products - tensor memory holds Y (256 columns) and E (256), later P
+// over Y, and the constant operands stream through a two-slot ring of 32 KB boxes (256 rows x 64
+// channels), each box used for every product that needs it while it is resident: Pi_hi for Y and E, Pi_lo
+// for Y, M_hi for r'_hi and r'_lo, M_lo for r'_hi - 512 KB from L2 per tile.  One tile in flight.
+// A compute thread (row, q) owns channels [64q, 64q+64): two value groups, one 128-byte row of a box.
+constexpr int D2 = 256;
+constexpr int D2_TILE_BYTES = 4 * BOX_BYTES;      // 128 rows x 256 bf16: four boxes
+constexpr int D2_CHUNK_BYTES = 2 * BOX_BYTES;     // 256 rows x 64 bf16 of a constant operand
+
+template <int MSE_BITS, int VAL_BITS>
+__global__ void __launch_bounds__(TC_LAUNCH, 1)
+tq_store_tc256_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                      const __grid_constant__ CUtensorMap tm_kt, const __grid_constant__ CUtensorMap tm_vt,
+                      const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
+                      const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_b3,
+                      const TcParams p) {
+    const TqLayout L = tq_make_layout(D2, MSE_BITS + 1, VAL_BITS);
+    const int BB = L.block_bytes;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = smem_raw + ((1024u - (tq_smem_u32(smem_raw) & 1023u)) & 1023u);
+    uint8_t* sA0 = smem;                              // key rows -> u -> r'_hi
+    uint8_t* sA1 = sA0 + D2_TILE_BYTES;               // value rows -> e' -> r'_lo
+    uint8_t* sBr = sA1 + D2_TILE_BYTES;               // two slots of the constant-operand ring
+    uint8_t* sRec = sBr + 2 * D2_CHUNK_BYTES;         // image of the tile's 8 block records
+    float* s_ss = reinterpret_cast<float*>(sRec + 8 * BB);   // [4][128] partial sums of squares (x, then r')
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_ss + 4 * TC_TOK);
+    uint64_t *bar_k = bars, *bar_v = bars + 1, *bar_m1 = bars + 2, *bar_m2 = bars + 3, *bar_r = bars + 4;
+    uint64_t *bar_full = bars + 5, *bar_empty = bars + 7;     // [2] each: ring slot filled / its products done
+    uint64_t *bar_n = bars + 9, *bar_c = bars + 10;           // 512 arrivals: u, e' written / r' written
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+    volatile int* s_fail = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const bool slot_mode = p.slot_mapping != nullptr;
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tq_smem_u32(tmem_slot)),
+                     "r"(TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    if (tid == 0) {
+#pragma unroll
+        for (int i = 0; i < 9; ++i) tq_mbar_init(bars + i, 1);
+        tq_mbar_init(bar_n, TC_THREADS);
+        tq_mbar_init(bar_c, TC_THREADS);
+        *s_fail = 0;
+        tq_mbar_fence_init();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    constexpr uint32_t C_Y = 0, C_E = 256;
+
+    auto tile_head = [&](int tile) { return (int)((uint32_t)tile % (uint32_t)p.H); };
+    auto tile_tok0 = [&](int tile) { return (int64_t)((uint32_t)tile / (uint32_t)p.H) * TC_TOK - p.lead; };
+    const int tile0 = blockIdx.x;
+    const bool rmw = !slot_mode && p.lead != 0 && tile0 < p.H;
+
+    if (warp == TC_THREADS / 32) {
+        // =============================== issuing warp (uniform, one elected lane issues) ===============================
+        const uint32_t tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
+        auto wait1 = [&](uint64_t* bar, uint32_t parity) -> bool {
+            uint32_t ok = 0;
+            for (int i = 0; i < (1 << 20); ++i) {
+                if (tq_mbar_try_wait(bar, parity)) {
+                    ok = 1;
+                    break;
+                }
+                __nanosleep(40);
+                if ((i & 255) == 255 && *s_fail) break;
+            }
+            ok = __all_sync(0xffffffffu, ok != 0);
+            if (!ok) *s_fail = 1;
+            return ok != 0;
+        };
+        auto elected = [&]() -> bool {
+            uint32_t pred;
+            asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+            return pred != 0;
+        };
+        auto issue_rows = [&](uint8_t* dst, const CUtensorMap* tm, const CUtensorMap* tm_tail, uint64_t* bar, int tile) {
+            const int hh = tile_head(tile), t0 = (int)tile_tok0(tile);
+            if (p.src_table != nullptr) {
+                issue_paged_rows(dst, tm, tm_tail, bar, p, tile_tok0(tile), hh, 4, lane, elected());
+                return;
+            }
+            if (elected()) {
+                tq_mbar_expect_tx(bar, D2_TILE_BYTES);
+#pragma unroll
+                for (int b = 0; b < 4; ++b)
+                    tma_load_3d(dst + b * BOX_BYTES, tm, 64 * b, p.tok_outer ? hh : t0, p.tok_outer ? t0 : hh, bar);
+            }
+            __syncwarp();
+        };
+        const CUtensorMap* tb[4] = {&tm_b0, &tm_b1, &tm_b2, &tm_b3};
+        const uint32_t a0 = tq_smem_u32(sA0), a1 = tq_smem_u32(sA1), ar = tq_smem_u32(sBr);
+        // chunk c of a tile: constant operand c / 4 (Pi_hi, Pi_lo, M_hi, M_lo), channels [64 (c % 4), +64)
+        int g_loaded = 0;       // chunks requested so far, over all tiles of this CTA
+        auto load_chunk = [&](int c) -> bool {
+            const int slot = g_loaded & 1;
+            if (g_loaded >= 2 && !wait1(bar_empty + slot, ((g_loaded - 2) >> 1) & 1)) return false;
+            if (elected()) {
+                tq_mbar_expect_tx(bar_full + slot, D2_CHUNK_BYTES);
+                tma_load_2d(sBr + slot * D2_CHUNK_BYTES, tb[c >> 2], 64 * (c & 3), 0, bar_full + slot);
+            }
+            __syncwarp();
+            ++g_loaded;
+            return true;
+        };
+        int g_used = 0;
+        auto use_chunk = [&](int c) -> bool {   // issue every product that reads chunk c, then release its slot
+            const int slot = g_used & 1, kc = c & 3, mat = c >> 2;
+            if (!wait1(bar_full + slot, (g_used >> 1) & 1)) return false;
+            tc_fence_after();
+            if (elected()) {
+                const uint32_t b_addr = ar + slot * D2_CHUNK_BYTES;
+#pragma unroll
+                for (int ks = 0; ks < 4; ++ks) {
+                    const uint64_t bd = smem_desc_sw128(b_addr + ks * 32);
+                    const uint64_t d0 = smem_desc_sw128(a0 + kc * BOX_BYTES + ks * 32);
+                    const uint64_t d1 = smem_desc_sw128(a1 + kc * BOX_BYTES + ks * 32);
+                    const uint32_t first = (kc | ks) == 0 ? 0u : 1u;
+                    if (mat == 0) {            // Pi_hi: Y (u) and E (e')
+                        umma_ss_n256(tmem_u + C_Y, d0, bd, first);
+                        umma_ss_n256(tmem_u + C_E, d1, bd, first);
+                    } else if (mat == 1) {     // Pi_lo: Y (u)
+                        umma_ss_n256(tmem_u + C_Y, d0, bd, 1u);
+                    } else if (mat == 2) {     // M_hi: P (r'_hi) and P (r'_lo), over Y's columns
+                        umma_ss_n256(tmem_u + C_Y, d0, bd, first);
+                        umma_ss_n256(tmem_u + C_Y, d1, bd, 1u);
+                    } else {                   // M_lo: P (r'_hi)
+                        umma_ss_n256(tmem_u + C_Y, d0, bd, 1u);
+                    }
+                }
+                umma_commit(bar_empty + slot);
+                if (c == 7) umma_commit(bar_m1);
+                if (c == 15) umma_commit(bar_m2);
+            }
+            __syncwarp();
+            ++g_used;
+            return true;
+        };
+
+        issue_rows(sA0, &tm_k, &tm_kt, bar_k, tile0);
+        issue_rows(sA1, &tm_v, &tm_vt, bar_v, tile0);
+        if (rmw) {
+            if (elected()) {
+                const int64_t phys = p.block_table[p.start_pos >> 4];
+                if (phys >= 0 && phys < p.num_blocks) {
+                    tq_mbar_expect_tx(bar_r, (uint32_t)BB);
+                    tq_bulk_g2s(sRec, p.pool + (phys * p.H + tile_head(tile0)) * (int64_t)BB, (uint32_t)BB, bar_r);
+                } else {
+                    atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_RANGE);
+                    tq_mbar_expect_tx(bar_r, 0);
+                }
+            }
+            __syncwarp();
+        }
+        bool ok = load_chunk(0) && load_chunk(1);
+        int i = 0;
+#pragma unroll 1
+        for (int tile = tile0; tile < p.n_tiles && ok; tile += (int)gridDim.x, ++i) {
+            const int next = tile + (int)gridDim.x;
+            if (!(ok = wait1(bar_n, i & 1))) break;              // u, e' in shared memory
+#pragma unroll 1
+            for (int c = 0; c < 16 && ok; ++c) {
+                if (c == 8 && !(ok = wait1(bar_c, i & 1))) break;   // r' limbs in shared memory
+                ok = use_chunk(c);
+                // keep the ring full: the chunk two ahead (of this tile, or the first ones of the next tile)
+                const int ahead = c + 2;
+                if (ok && (ahead < 16 || next < p.n_tiles)) ok = load_chunk(ahead & 15);
+            }
+            if (!ok) break;
+            if (next < p.n_tiles) {
+                if (!(ok = wait1(bar_m2, i & 1))) break;         // the A tiles are free again
+                issue_rows(sA0, &tm_k, &tm_kt, bar_k, next);
+                issue_rows(sA1, &tm_v, &tm_vt, bar_v, next);
+            }
+        }
+    } else {
+        // =============================== compute warps ===============================
+        const int row = tid & (TC_TOK - 1), q = tid >> 7;
+        const int blk_l = row >> 4, tl = row & 15;
+        const uint32_t lane_base = (uint32_t)(row & ~31) << 16;
+        BookRegs<MSE_BITS> bk;
+        bk.c0 = p.cb.centroids[0];
+#pragma unroll
+        for (int i = 0; i < (1 << MSE_BITS) - 1; ++i) {
+            bk.nb[i] = -p.cb.boundaries[i] * BIG;
+            bk.step[i] = p.cb.centroids[i + 1] - p.cb.centroids[i];
+        }
+        auto wait_warp = [&](uint64_t* bar, uint32_t parity) -> bool {
+            uint32_t ok = 1;
+            if (lane == 0) {
+                ok = 0;
+                for (int i = 0; i < (1 << 21); ++i) {
+                    if (tq_mbar_try_wait(bar, parity)) {
+                        ok = 1;
+                        break;
+                    }
+                    if (i >= 4) __nanosleep(20);
+                    if ((i & 255) == 255 && *s_fail) break;
+                }
+                if (!ok) *s_fail = 1;
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            __syncwarp();
+            return ok != 0;
+        };
+        // this thread's 128 bytes (64 channels) of row `row` in box q of an A tile
+        auto row_chunk = [&](uint8_t* tile, int c) { return reinterpret_cast<uint4*>(tile + q * BOX_BYTES + row * 128 + ((c ^ (row & 7)) << 4)); };
+        bool bad = false, ok = true;
+        int tile_no = 0;
+#pragma unroll 1
+        for (int tile = tile0; tile < p.n_tiles; tile += (int)gridDim.x, ++tile_no) {
+            const uint32_t par = tile_no & 1;
+            const int h = tile_head(tile);
+            const int64_t tok0 = tile_tok0(tile);
+            const bool wr = tok0 + row >= 0;
+            uint8_t* rec = sRec + blk_l * BB;
+            RecordDest dest;
+            ask_destination(p, tok0, warp, lane, dest);
+
+            // ---------------- V: the two value groups of channels [64q, 64q+64) ----------------
+            if (tile_no == 0 && rmw) bad |= !wait_warp(bar_r, 0);
+            bad |= !wait_warp(bar_v, par);
+#pragma unroll
+            for (int g2 = 0; g2 < 2; ++g2) {
+                uint4 vraw[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) vraw[c] = *row_chunk(sA1, 4 * g2 + c);
+                quantize_value_group<VAL_BITS, D2>(vraw, rec, L, tl, 2 * q + g2, wr);
+            }
+            // ---------------- N: norm, u in place of the key row, e' in place of the value row ----------------
+            bad |= !wait_warp(bar_k, par);
+            float nd;
+            {
+                uint32_t xw[32];
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const uint4 v = *row_chunk(sA0, c);
+                    xw[4 * c] = v.x; xw[4 * c + 1] = v.y; xw[4 * c + 2] = v.z; xw[4 * c + 3] = v.w;
+                }
+                float ss = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const float a = bf_lo(xw[i]), b = bf_hi(xw[i]);
+                    ss = fmaf(a, a, ss);
+                    ss = fmaf(b, b, ss);
+                }
+                s_ss[q * TC_TOK + row] = ss;
+                if (compute_barrier_or(bad)) {   // partial sums published; every thread has read its value row
+                    ok = false;
+                    break;
+                }
+                ss = (s_ss[row] + s_ss[TC_TOK + row]) + (s_ss[2 * TC_TOK + row] + s_ss[3 * TC_TOK + row]);
+                nd = bf16r(__fsqrt_rn(ss));
+                const float rden = __frcp_rn(bf16r(nd + 1e-10f));
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    uint32_t up[4], ep[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float q0 = bf_lo(xw[4 * c + i]) * rden, q1 = bf_hi(xw[4 * c + i]) * rden;
+                        up[i] = pack_bf16(q0, q1);
+                        ep[i] = pack_bf16(q0 - bf_lo(up[i]), q1 - bf_hi(up[i]));
+                    }
+                    *row_chunk(sA0, c) = make_uint4(up[0], up[1], up[2], up[3]);
+                    *row_chunk(sA1, c) = make_uint4(ep[0], ep[1], ep[2], ep[3]);
+                }
+            }
+            tq_fence_proxy_async();   // generic writes -> the MMA's reads
+            mbar_arrive(bar_n);
+
+            // ---------------- C: codes, r' limbs over u / e' ----------------
+            bad |= !wait_warp(bar_m1, par);
+            tc_fence_after();
+            float rn2 = 0.f;
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                float y[32];
+                tmem_ld32(tmem + lane_base + C_Y + q * 64 + hf * 32, y);
+                constexpr int WIDTH = MSE_BITS == 2 ? 2 : 4, PER_HALF = 16 / WIDTH;
+                uint32_t halves[32 / PER_HALF];
+#pragma unroll
+                for (int w = 0; w < 32 / PER_HALF; ++w) {
+                    float wf = 0.f;
+#pragma unroll
+                    for (int jj = 0; jj < PER_HALF; ++jj) {
+                        float code;
+                        bucket<MSE_BITS>(bk, y[w * PER_HALF + jj], code, y[w * PER_HALF + jj]);
+                        wf = fmaf(code, (float)(1u << (WIDTH * jj)), wf);
+                    }
+                    halves[w] = __float_as_uint(wf + 8388608.f) & 0xffffu;
+                }
+                if (wr) {
+                    uint32_t* kc = reinterpret_cast<uint32_t*>(rec + L.off_kcodes + tl * L.kcode_row) +
+                                   (2 * q + hf) * (16 / PER_HALF);
+#pragma unroll
+                    for (int w = 0; w < 16 / PER_HALF; ++w) kc[w] = halves[2 * w] | (halves[2 * w + 1] << 16);
+                }
+                float er[32];
+                tmem_ld32(tmem + lane_base + C_E + q * 64 + hf * 32, er);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t hi[4], lo[4];
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float a = y[8 * c + 2 * i] + er[8 * c + 2 * i], b = y[8 * c + 2 * i + 1] + er[8 * c + 2 * i + 1];
+                        rn2 = fmaf(a, a, rn2);
+                        rn2 = fmaf(b, b, rn2);
+                        hi[i] = pack_bf16(a, b);
+                        lo[i] = pack_bf16(a - bf_lo(hi[i]), b - bf_hi(hi[i]));
+                    }
+                    *row_chunk(sA0, 4 * hf + c) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                    *row_chunk(sA1, 4 * hf + c) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                }
+            }
+            s_ss[q * TC_TOK + row] = rn2;
+            tc_fence_before();
+            tq_fence_proxy_async();
+            mbar_arrive(bar_c);
+
+            // ---------------- S: sign bits, norms ----------------
+            bad |= !wait_warp(bar_m2, par);
+            tc_fence_after();
+#pragma unroll
+            for (int hf = 0; hf < 2; ++hf) {
+                float pr[32];
+                tmem_ld32(tmem + lane_base + C_Y + q * 64 + hf * 32, pr);
+                float w_lo = 0.f, w_hi = 0.f;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    w_lo = fmaf(mul_sat(mul_sat(pr[j], BIG), BIG), (float)(1u << j), w_lo);
+                    w_hi = fmaf(mul_sat(mul_sat(pr[16 + j], BIG), BIG), (float)(1u << j), w_hi);
+                }
+                uint32_t w = (__float_as_uint(w_lo + 8388608.f) & 0xffffu) | (__float_as_uint(w_hi + 8388608.f) << 16);
+                if (nd == 0.f) w = 0;
+                if (wr) reinterpret_cast<uint32_t*>(rec + L.off_ksigns + tl * L.ksign_row)[2 * q + hf] = w;
+            }
+            tc_fence_before();
+            if (compute_barrier_or(bad)) {   // the r' partial sums are published
+                ok = false;
+                break;
+            }
+            if (q == 0 && wr) {
+                const float r2 = (s_ss[row] + s_ss[TC_TOK + row]) + (s_ss[2 * TC_TOK + row] + s_ss[3 * TC_TOK + row]);
+                reinterpret_cast<__half*>(rec + L.off_knorm)[tl] = __float2half_rn(nd);
+                reinterpret_cast<__half*>(rec + L.off_krnorm)[tl] = __float2half_rn(nd * __fsqrt_rn(r2));
+            }
+            tq_fence_proxy_async();
+            compute_barrier_or(false);       // record image complete
+            if (warp < 8) {
+                leave_records(p, L, sRec, h, warp, lane, dest);
+                if (lane == 0) tq_bulk_wait_all_read();
+            }
+            compute_barrier_or(false);       // the image and s_ss are free for the next tile
+        }
+        if (!ok && tid == 0) atomicCAS(&g_tq_store_status, 0, (int)TQ_ERR_TIMEOUT);
+        if (lane == 0 && warp < 8) tq_bulk_wait_all();
     }
 
     tc_fence_before();
@@ -782,21 +1230,21 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// (128 x 128) bf16 matrix, row pitch 256 bytes: boxes of 64 columns x 128 rows, 128-byte swizzle
-bool make_matrix_map(CUtensorMap* tm, const void* base) {
-    const cuuint64_t dims[2] = {TC_D, TC_D};
-    const cuuint64_t strides[1] = {TC_D * 2};
-    const cuuint32_t box[2] = {64, TC_TOK};
+// (D x D) bf16 matrix, row-major: boxes of 64 columns x D rows (128 or 256), 128-byte swizzle
+bool make_matrix_map(CUtensorMap* tm, const void* base, int D) {
+    const cuuint64_t dims[2] = {(cuuint64_t)D, (cuuint64_t)D};
+    const cuuint64_t strides[1] = {(cuuint64_t)D * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)D};
     const cuuint32_t estr[2] = {1, 1};
     return encode_tiled_fn()(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
-// (tokens, heads, 128) bf16 with element strides: boxes of 64 channels x 128 tokens of one head; the
+// (tokens, heads, D) bf16 with element strides: boxes of 64 channels x 128 tokens of one head; the
 // dimension with the larger stride goes last
-bool make_rows_map(CUtensorMap* tm, const void* base, int64_t n_tokens, int n_heads, int64_t stride_token,
+bool make_rows_map(CUtensorMap* tm, const void* base, int D, int64_t n_tokens, int n_heads, int64_t stride_token,
                    int64_t stride_head, bool tok_outer) {
-    cuuint64_t dims[3] = {TC_D, (cuuint64_t)n_heads, (cuuint64_t)n_tokens};
+    cuuint64_t dims[3] = {(cuuint64_t)D, (cuuint64_t)n_heads, (cuuint64_t)n_tokens};
     cuuint64_t strides[2] = {(cuuint64_t)stride_head * 2, (cuuint64_t)stride_token * 2};
     cuuint32_t box[3] = {64, 1, TC_TOK};
     if (!tok_outer) {
@@ -810,21 +1258,57 @@ bool make_rows_map(CUtensorMap* tm, const void* base, int64_t n_tokens, int n_he
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Paged cache (blocks, block_size tokens, heads, D) bf16 with element strides: boxes of 64 channels x
+// `box_rows` tokens of one head of one block.  `rows` is the extent of the token dimension - the block
+// size, or fewer for the view whose rows past the sequence's last token must read as zeros.
+bool make_paged_map(CUtensorMap* tm, const void* base, int D, int64_t num_blocks, int rows, int box_rows, int n_heads,
+                    int64_t stride_block, int64_t stride_token, int64_t stride_head, bool tok_outer) {
+    cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)n_heads, (cuuint64_t)rows, (cuuint64_t)num_blocks};
+    cuuint64_t strides[3] = {(cuuint64_t)stride_head * 2, (cuuint64_t)stride_token * 2, (cuuint64_t)stride_block * 2};
+    cuuint32_t box[4] = {64, 1, (cuuint32_t)box_rows, 1};
+    if (!tok_outer) {
+        dims[1] = (cuuint64_t)rows; dims[2] = (cuuint64_t)n_heads;
+        strides[0] = (cuuint64_t)stride_token * 2; strides[1] = (cuuint64_t)stride_head * 2;
+        box[1] = (cuuint32_t)box_rows; box[2] = 1;
+    }
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    return encode_tiled_fn()(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
-// Launches the tensor-core kernel when the call fits it: head_dim 128, bf16, 16-byte aligned rows, the
-// split operands present.  Otherwise *handled stays 0 and tq_store runs its fp32 kernel.
+// Launches a tensor-core kernel when the call fits one: head_dim 128 (any bit widths) or 256 (3-bit keys
+// with 2-bit values, the combination whose record image fits beside the operands), bf16, 16-byte aligned
+// rows, the split operands present.  Otherwise *handled stays 0 and tq_store runs its fp32 kernel.
+//
+// `paged` (may be null) makes key / value the two planes of a paged cache: rows are then addressed as
+// (source block from paged->table, token in block) instead of by stride_token from one base.
 int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* value, tq_dtype dtype, int64_t n_tokens,
                        int32_t n_heads, int64_t stride_token, int64_t stride_head, const int64_t* slot_mapping,
                        const int32_t* block_table, int64_t start_pos, const tq_pool* pool, cudaStream_t st,
-                       int* handled) {
+                       int* handled, const TqPagedSource* paged) {
     *handled = 0;
     const tq_config& cfg = consts->cfg;
-    if (cfg.head_dim != TC_D || dtype != TQ_BF16) return TQ_OK;
+    const int D = cfg.head_dim;
+    if ((D != TC_D && D != D2) || dtype != TQ_BF16) return TQ_OK;
+    const TqLayout L = tq_make_layout(D, cfg.key_bits, cfg.value_bits);
+    const size_t img = (size_t)8 * L.block_bytes;
+    const size_t smem256 = 2 * (size_t)D2_TILE_BYTES + 2 * (size_t)D2_CHUNK_BYTES + img + 4 * TC_TOK * sizeof(float) +
+                           11 * sizeof(uint64_t) + 16 + 1024;
+    if (D == D2 && smem256 > SMEM_LIMIT) return TQ_OK;
     if (!consts->pi_limbs[0] || !consts->pi_limbs[1] || !consts->m_limbs[0] || !consts->m_limbs[1]) return TQ_OK;
     if (((uintptr_t)key & 15) || ((uintptr_t)value & 15) || (stride_token & 7) || (stride_head & 7)) return TQ_OK;
-    if (stride_token < TC_D || (n_heads > 1 && stride_head < TC_D)) return TQ_OK;
-    if (n_heads == 1) stride_head = stride_token > TC_D ? TC_D : stride_token;   // never dereferenced; keep the map well formed
+    if (stride_token < D || (n_heads > 1 && stride_head < D)) return TQ_OK;
+    if (n_heads == 1) stride_head = stride_token > D ? D : stride_token;
+    int bs_log2 = 0;
+    if (paged) {   // block sizes the box stacking can express: 16, 32, 64 and multiples of 128 that are powers of two
+        while ((1 << bs_log2) < paged->block_size && bs_log2 < 30) ++bs_log2;
+        if ((1 << bs_log2) != paged->block_size || bs_log2 < 4) return TQ_OK;
+        if ((start_pos & 15) || slot_mapping || (paged->stride_block & 7) || paged->num_blocks >= ((int64_t)1 << 31))
+            return TQ_OK;
+    }   // never dereferenced; keep the map well formed
     for (int i = 0; i < 2; ++i)
         if (((uintptr_t)consts->pi_limbs[i] & 15) || ((uintptr_t)consts->m_limbs[i] & 15)) return TQ_OK;
     if (n_tokens >= ((int64_t)1 << 31) - 256) return TQ_OK;   // 32-bit box coordinates
@@ -846,6 +1330,10 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
     p.num_blocks = pool->num_blocks;
     p.H = n_heads;
     p.tok_outer = stride_token >= stride_head ? 1 : 0;
+    p.src_table = paged ? paged->table : nullptr;
+    p.src_num_blocks = paged ? (int32_t)paged->num_blocks : 0;
+    p.src_bs_log2 = bs_log2;
+    p.src_tail_block = paged && (n_tokens & (paged->block_size - 1)) ? n_tokens >> bs_log2 : -1;
     for (int i = 0; i < TQ_MAX_CENTROIDS; ++i) {
         p.cb.centroids[i] = consts->centroids[i];
         p.cb.boundaries[i] = consts->boundaries[i];
@@ -854,27 +1342,49 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
     if (n_tiles >= ((int64_t)1 << 30)) return TQ_OK;
     p.n_tiles = (int)n_tiles;
 
-    CUtensorMap tm_k, tm_v, tm_b[4];
-    if (!make_rows_map(&tm_k, key, n_tokens, n_heads, stride_token, stride_head, p.tok_outer != 0) ||
-        !make_rows_map(&tm_v, value, n_tokens, n_heads, stride_token, stride_head, p.tok_outer != 0) ||
-        !make_matrix_map(&tm_b[0], consts->pi_limbs[0]) || !make_matrix_map(&tm_b[1], consts->pi_limbs[1]) ||
-        !make_matrix_map(&tm_b[2], consts->m_limbs[0]) || !make_matrix_map(&tm_b[3], consts->m_limbs[1]))
+    CUtensorMap tm_k, tm_v, tm_kt, tm_vt, tm_b[4];
+    bool maps_ok;
+    if (paged) {
+        const int bs = paged->block_size, box_rows = bs < TC_TOK ? bs : TC_TOK;
+        const int tail = (int)(n_tokens & (bs - 1));
+        const bool to = p.tok_outer != 0;
+        maps_ok = make_paged_map(&tm_k, key, D, paged->num_blocks, bs, box_rows, n_heads, paged->stride_block, stride_token, stride_head, to) &&
+                  make_paged_map(&tm_v, value, D, paged->num_blocks, bs, box_rows, n_heads, paged->stride_block, stride_token, stride_head, to) &&
+                  make_paged_map(&tm_kt, key, D, paged->num_blocks, tail ? tail : bs, box_rows, n_heads, paged->stride_block, stride_token, stride_head, to) &&
+                  make_paged_map(&tm_vt, value, D, paged->num_blocks, tail ? tail : bs, box_rows, n_heads, paged->stride_block, stride_token, stride_head, to);
+    } else {
+        maps_ok = make_rows_map(&tm_k, key, D, n_tokens, n_heads, stride_token, stride_head, p.tok_outer != 0) &&
+                  make_rows_map(&tm_v, value, D, n_tokens, n_heads, stride_token, stride_head, p.tok_outer != 0);
+        tm_kt = tm_k;
+        tm_vt = tm_v;
+    }
+    if (!maps_ok || !make_matrix_map(&tm_b[0], consts->pi_limbs[0], D) || !make_matrix_map(&tm_b[1], consts->pi_limbs[1], D) ||
+        !make_matrix_map(&tm_b[2], consts->m_limbs[0], D) || !make_matrix_map(&tm_b[3], consts->m_limbs[1], D))
         return TQ_OK;   // a stride pattern the tensor map cannot express: the fp32 kernel takes the call
     *handled = 1;
 
     const int mse_bits = cfg.key_bits - 1;
-    const TqLayout L = tq_make_layout(TC_D, cfg.key_bits, cfg.value_bits);
-    const size_t img = (size_t)8 * L.block_bytes;
+    const int sms = tq_sm_count();
+    const unsigned grid = (unsigned)(p.n_tiles < sms ? p.n_tiles : sms);
+    if (D == D2) {
+        p.n_rec_buf = 1;
+        if (mse_bits != 2 || cfg.value_bits != 2) {   // unreachable: no other image passed the size check above
+            *handled = 0;
+            return TQ_OK;
+        }
+        static TqSmemOptIn opt_in;
+        if (tq_opt_in_smem(tq_store_tc256_kernel<2, 2>, smem256, opt_in) != TQ_OK) return TQ_ERR_CUDA;
+        tq_store_tc256_kernel<2, 2><<<grid, TC_LAUNCH, smem256, st>>>(tm_k, tm_v, tm_kt, tm_vt, tm_b[0], tm_b[1], tm_b[2], tm_b[3], p);
+        return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
+    }
     const size_t fixed = (size_t)6 * MAT_BYTES + 8 * TC_TOK * sizeof(float) + 11 * sizeof(uint64_t) + 16 + 1024;
     p.n_rec_buf = fixed + 2 * img <= SMEM_LIMIT ? 2 : 1;
     const size_t smem = fixed + (size_t)p.n_rec_buf * img;
-    const int sms = tq_sm_count();
-    const unsigned grid = (unsigned)(p.n_tiles < sms ? p.n_tiles : sms);
 #define TQ_TC(MB, VB)                                                                                            \
     do {                                                                                                         \
         static TqSmemOptIn opt_in;                                                                               \
         if (tq_opt_in_smem(tq_store_tc_kernel<MB, VB>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;               \
-        tq_store_tc_kernel<MB, VB><<<grid, TC_LAUNCH, smem, st>>>(tm_k, tm_v, tm_b[0], tm_b[1], tm_b[2], tm_b[3], p); \
+        tq_store_tc_kernel<MB, VB><<<grid, TC_LAUNCH, smem, st>>>(tm_k, tm_v, tm_kt, tm_vt, tm_b[0], tm_b[1], tm_b[2], tm_b[3], p); \
     } while (0)
     if (mse_bits == 2 && cfg.value_bits == 2) TQ_TC(2, 2);
     else if (mse_bits == 2) TQ_TC(2, 4);

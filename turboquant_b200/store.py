@@ -86,6 +86,30 @@ class CompressedKVStore:
         self._seq_len_dev.fill_(self._num_tokens)
         self._flat = None
 
+    def append_from_paged(self, key_cache: torch.Tensor, value_cache: torch.Tensor, src_block_table: torch.Tensor,
+                          num_tokens: int) -> None:
+        """Compress and append the first `num_tokens` tokens of a sequence held in a paged cache
+        ((num_blocks, block_size, H, D) planes, `src_block_table` logical -> physical block): what
+        `append_chunk` does to the gathered rows, without gathering them when the table-walking kernel
+        takes the call.  No reference counterpart as a single call (capture.py:187-217 gathers first)."""
+        if num_tokens == 0:
+            return
+        if key_cache.shape[2] != self.num_kv_heads or key_cache.shape[3] != self.head_dim:
+            raise ValueError(f"expected (num_blocks, block_size, {self.num_kv_heads}, {self.head_dim}) planes")
+        self.reserve(self._num_tokens + num_tokens)
+        table = src_block_table.to(device=self.device, dtype=torch.int32).contiguous()
+        if not E.store_paged(self.consts, self.pool, key_cache, value_cache, src_block_table=table,
+                             n_tokens=num_tokens, block_table=self.block_table, start_pos=self._num_tokens):
+            bs = key_cache.shape[1]
+            phys = table[:(num_tokens + bs - 1) // bs].long()
+            k = key_cache.index_select(0, phys).flatten(0, 1)[:num_tokens]
+            v = value_cache.index_select(0, phys).flatten(0, 1)[:num_tokens]
+            return self.append_chunk(k, v)
+        self._num_tokens += num_tokens
+        self._num_chunks += 1
+        self._seq_len_dev.fill_(self._num_tokens)
+        self._flat = None
+
     def get_flat_cache(self) -> Optional[FlatCache]:
         """The reference's flat planes (H, N, ...), rebuilt after a write."""
         if self._num_tokens == 0:
