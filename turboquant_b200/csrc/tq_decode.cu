@@ -322,7 +322,7 @@ int launch_qprep(const void* q, int dt, int64_t nvec, int D, const float* pi_t, 
     cfg.numAttrs = 1;
     cfg.stream = st;
     cfg.blockDim = dim3(256);
-    if (nvec >= 512 && ap.new_k == nullptr && !ap.early_inputs && ((uintptr_t)q & 15) == 0) {   // throughput kernel
+    if (nvec >= 4096 && ap.new_k == nullptr && !ap.early_inputs && ((uintptr_t)q & 15) == 0) {   // throughput kernel
         const size_t smem = sizeof(float) * ((size_t)D * QB_V + QB_K * QB_C + 4 * QB_V);
         cfg.gridDim = dim3((unsigned)(2 * D / QB_C), (unsigned)((nvec + QB_V - 1) / QB_V));
         cfg.dynamicSmemBytes = smem;

@@ -380,6 +380,11 @@ __device__ __forceinline__ void issue_paged_rows(uint8_t* dst, const CUtensorMap
     __syncwarp();
 }
 
+// This launch may have started while the launch ahead of it in the stream still runs (programmatic
+// dependent launch): inputs are read-only and may be fetched at once, but the pool - which that launch
+// may write, and whose stream order of writes the caller relies on - is touched only after this wait.
+__device__ __forceinline__ void pool_writes_may_begin() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(tq_smem_u32(bar)) : "memory");
 }
@@ -432,6 +437,9 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool slot_mode = p.slot_mapping != nullptr;
+    // The launch that follows in the stream may take over each SM as soon as this CTA leaves it; whatever
+    // it reads or writes in the pool comes after its own wait for this grid (see pool_writes_may_begin).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tq_smem_u32(tmem_slot)),
@@ -577,6 +585,7 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
             issue_kv(sX, &tm_k, &tm_kt, bar_k, tile0);
             issue_kv(sV, &tm_v, &tm_vt, bar_v, tile0);
             if (rmw) {   // the block this append continues, into block 0 of the first record image
+                pool_writes_may_begin();
                 if (elected()) {
                     const int64_t phys = p.block_table[p.start_pos >> 4];
                     if (phys >= 0 && phys < p.num_blocks) {
@@ -813,6 +822,7 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
             // ---------------- the tile's block records leave ----------------
             if (warp < 8) {
+                if (tile_no == 0) pool_writes_may_begin();
                 leave_records(p, L, img, h, warp, lane, dest);
                 if (lane == 0 && p.n_rec_buf == 1) tq_bulk_wait_all_read();
             }
@@ -874,6 +884,9 @@ tq_store_tc256_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const bool slot_mode = p.slot_mapping != nullptr;
+    // The launch that follows in the stream may take over each SM as soon as this CTA leaves it; whatever
+    // it reads or writes in the pool comes after its own wait for this grid (see pool_writes_may_begin).
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tq_smem_u32(tmem_slot)),
@@ -988,6 +1001,7 @@ tq_store_tc256_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
         issue_rows(sA0, &tm_k, &tm_kt, bar_k, tile0);
         issue_rows(sA1, &tm_v, &tm_vt, bar_v, tile0);
         if (rmw) {
+            pool_writes_may_begin();
             if (elected()) {
                 const int64_t phys = p.block_table[p.start_pos >> 4];
                 if (phys >= 0 && phys < p.num_blocks) {
@@ -1195,6 +1209,7 @@ tq_store_tc256_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_con
             tq_fence_proxy_async();
             compute_barrier_or(false);       // record image complete
             if (warp < 8) {
+                if (tile_no == 0) pool_writes_may_begin();
                 leave_records(p, L, sRec, h, warp, lane, dest);
                 if (lane == 0) tq_bulk_wait_all_read();
             }
@@ -1366,6 +1381,16 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
     const int mse_bits = cfg.key_bits - 1;
     const int sms = tq_sm_count();
     const unsigned grid = (unsigned)(p.n_tiles < sms ? p.n_tiles : sms);
+    // programmatic dependent launch: this grid may begin under the tail of the launch ahead of it
+    cudaLaunchConfig_t lc = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr;
+    lc.numAttrs = 1;
+    lc.stream = st;
+    lc.gridDim = dim3(grid);
+    lc.blockDim = dim3(TC_LAUNCH);
     if (D == D2) {
         p.n_rec_buf = 1;
         if (mse_bits != 2 || cfg.value_bits != 2) {   // unreachable: no other image passed the size check above
@@ -1374,24 +1399,28 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
         }
         static TqSmemOptIn opt_in;
         if (tq_opt_in_smem(tq_store_tc256_kernel<2, 2>, smem256, opt_in) != TQ_OK) return TQ_ERR_CUDA;
-        tq_store_tc256_kernel<2, 2><<<grid, TC_LAUNCH, smem256, st>>>(tm_k, tm_v, tm_kt, tm_vt, tm_b[0], tm_b[1], tm_b[2], tm_b[3], p);
-        return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
+        lc.dynamicSmemBytes = smem256;
+        return cudaLaunchKernelEx(&lc, tq_store_tc256_kernel<2, 2>, tm_k, tm_v, tm_kt, tm_vt, tm_b[0], tm_b[1], tm_b[2],
+                                  tm_b[3], p) == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
     }
     const size_t fixed = (size_t)6 * MAT_BYTES + 8 * TC_TOK * sizeof(float) + 11 * sizeof(uint64_t) + 16 + 1024;
     p.n_rec_buf = fixed + 2 * img <= SMEM_LIMIT ? 2 : 1;
     const size_t smem = fixed + (size_t)p.n_rec_buf * img;
+    cudaError_t launched = cudaSuccess;
 #define TQ_TC(MB, VB)                                                                                            \
     do {                                                                                                         \
         static TqSmemOptIn opt_in;                                                                               \
         if (tq_opt_in_smem(tq_store_tc_kernel<MB, VB>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;               \
-        tq_store_tc_kernel<MB, VB><<<grid, TC_LAUNCH, smem, st>>>(tm_k, tm_v, tm_kt, tm_vt, tm_b[0], tm_b[1], tm_b[2], tm_b[3], p); \
+        lc.dynamicSmemBytes = smem;                                                                              \
+        launched = cudaLaunchKernelEx(&lc, tq_store_tc_kernel<MB, VB>, tm_k, tm_v, tm_kt, tm_vt, tm_b[0], tm_b[1],   \
+                                      tm_b[2], tm_b[3], p);                                                      \
     } while (0)
     if (mse_bits == 2 && cfg.value_bits == 2) TQ_TC(2, 2);
     else if (mse_bits == 2) TQ_TC(2, 4);
     else if (cfg.value_bits == 2) TQ_TC(3, 2);
     else TQ_TC(3, 4);
 #undef TQ_TC
-    return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
+    return launched == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 
 // Status left by the tensor-core store kernel (0, or a tq_status if a bounded
