@@ -137,6 +137,29 @@ int tq_scores_workspace_bytes(const tq_config* cfg, int64_t n_vectors, size_t* o
 const char* tq_strerror(int status);
 const char* tq_version(void);
 
+/* ---- prefill attention (no paged cache) ----------------------------------- */
+
+/* Causal attention of one sequence's n_tokens query tokens over its own keys
+ * and values, grouped query heads (query head q reads kv head
+ * q / (num_q_heads / num_kv_heads)).  Replaces _no_alloc_prefill_attention
+ * (integration/vllm.py:150-180: repeat_interleave of the kv heads +
+ * F.scaled_dot_product_attention(is_causal=True)).  Element (t, h, :) of a
+ * tensor is at base + t*stride_token + h*stride_head (in elements), head_dim
+ * contiguous; bf16 or fp16, head_dim 128 or 256 (else TQ_ERR_UNSUPPORTED);
+ * bases 16-byte aligned, strides multiples of 8 elements, token stride >=
+ * head stride.  `out` in the input dtype.  Runs on the tensor cores
+ * (tcgen05); the launch lets the next launch of the stream - normally
+ * tq_store of the same keys and values - begin under its tail. */
+int tq_prefill_attention(const void* query, const void* key, const void* value, void* out, tq_dtype dtype,
+                         int64_t n_tokens, int32_t num_q_heads, int32_t num_kv_heads, int32_t head_dim,
+                         int64_t q_stride_token, int64_t q_stride_head, int64_t kv_stride_token,
+                         int64_t kv_stride_head, int64_t out_stride_token, int64_t out_stride_head,
+                         float scale, void* stream);
+
+/* Status left by the prefill attention kernel (0, or TQ_ERR_TIMEOUT if one
+ * of its bounded device-side waits ran out).  Synchronises the device. */
+int tq_prefill_attention_read_status(int32_t* out);
+
 /* ---- store path ---------------------------------------------------------- */
 
 /* Compress `n_tokens` key/value vectors of `n_heads` kv heads and write them

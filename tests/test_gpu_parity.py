@@ -953,3 +953,42 @@ def test_paged_cache_to_compressed_store(d, kb, vb, bs, n, hnd, dev):
     for x, y in zip(e1.ring.peek(), e2.ring.peek()):
         assert torch.equal(x, y)
     assert E.store_status() == 0
+
+
+@pytest.mark.parametrize("d,qh,h,n,dtype", [(128, 8, 2, 1, torch.bfloat16), (128, 8, 2, 17, torch.bfloat16),
+                                            (128, 4, 4, 128, torch.bfloat16), (128, 8, 2, 129, torch.float16),
+                                            (128, 16, 2, 1000, torch.bfloat16), (128, 32, 8, 4096, torch.bfloat16),
+                                            (256, 4, 1, 300, torch.bfloat16), (256, 8, 4, 2049, torch.float16),
+                                            (256, 16, 4, 3000, torch.bfloat16)])
+def test_prefill_attention_vs_fp32_reference(d, qh, h, n, dtype, dev):
+    """Causal prefill attention kernel (tcgen05) against plain fp32 softmax(QK^T)V on the same 16-bit
+    inputs - what the reference's no-alloc mode gets from F.scaled_dot_product_attention after
+    repeat_interleave of the kv heads (integration/vllm.py:150-180).  Tolerance: 16-bit probabilities
+    and outputs, |err| <= 2e-2 absolute on values of order one and cos_sim >= 0.9999 per call."""
+    from turboquant_b200 import _engine as E
+    g = torch.Generator(device=dev)
+    g.manual_seed(1000 + n)
+    q = (torch.randn(n, qh, d, generator=g, device=dev) * 1.5).to(dtype)
+    k = torch.randn(n, h, d, generator=g, device=dev).to(dtype)
+    v = torch.randn(n, h, d, generator=g, device=dev).to(dtype)
+    if n >= 100:        # a few dominant keys: the running maximum has to move late in the row
+        k[n // 2] *= 4.0
+        k[n - 3] *= 6.0
+    scale = 1.0 / d ** 0.5
+    out = E.prefill_attention(q, k, v, scale=scale)
+    assert E.prefill_attention_status() == 0
+    rep = qh // h
+    kf, vf = k.float().repeat_interleave(rep, dim=1), v.float().repeat_interleave(rep, dim=1)
+    logits = torch.einsum("qhd,khd->hqk", q.float(), kf) * scale
+    mask = torch.ones(n, n, dtype=torch.bool, device=dev).tril()
+    logits = logits.masked_fill(~mask, float("-inf"))
+    ref = torch.einsum("hqk,khd->qhd", torch.softmax(logits, dim=-1), vf)
+    assert torch.isfinite(out.float()).all()
+    assert _cos(out, ref) >= 0.9999
+    torch.testing.assert_close(out.float(), ref, rtol=2e-2, atol=2e-2)
+    # a strided view (the fused qkv projection's output): heads of q, k and v side by side per token
+    qkv = torch.cat([q.reshape(n, -1), k.reshape(n, -1), v.reshape(n, -1)], dim=1).contiguous()
+    qs = qkv[:, :qh * d].view(n, qh, d)
+    ks = qkv[:, qh * d:(qh + h) * d].view(n, h, d)
+    vs = qkv[:, (qh + h) * d:].view(n, h, d)
+    assert torch.equal(E.prefill_attention(qs, ks, vs, scale=scale), out)

@@ -412,6 +412,48 @@ def pack_stage(consts: LayerConstants, y: torch.Tensor, projected: torch.Tensor)
     return codes.reshape(*y.shape[:-1], -1), signs.reshape(*y.shape[:-1], -1)
 
 
+def prefill_attention_supported(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor) -> bool:
+    """Whether `prefill_attention` takes these tensors (CUDA, bf16 / fp16, head_dim 128 or 256, 16-byte
+    aligned rows); otherwise the caller keeps its own attention."""
+    return (query.is_cuda and key.is_cuda and value.is_cuda and query.dtype in (torch.bfloat16, torch.float16)
+            and key.dtype == query.dtype and value.dtype == query.dtype and query.dim() == 3 and key.dim() == 3
+            and query.shape[-1] in (128, 256) and key.shape == value.shape and key.shape[-1] == query.shape[-1]
+            and query.shape[1] % key.shape[1] == 0 and key.shape[0] == query.shape[0])
+
+
+def prefill_attention(query: torch.Tensor, key: torch.Tensor, value: torch.Tensor, scale: Optional[float] = None,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of a sequence over itself: query (n, Qh, D), key / value (n, H, D) -> (n, Qh, D)."""
+    if not prefill_attention_supported(query, key, value):
+        raise ValueError("prefill_attention needs CUDA bf16/fp16 tensors (n, heads, 128 or 256)")
+
+    def rows(t):   # D contiguous, 16-byte aligned rows, token stride >= head stride
+        ok = t.stride(2) == 1 and t.stride(0) % 8 == 0 and t.stride(1) % 8 == 0 and t.data_ptr() % 16 == 0 \
+            and (t.stride(0) >= t.stride(1) or t.shape[1] == 1) and t.stride(1) >= t.shape[2]
+        return t if ok else t.contiguous()
+
+    q, k, v = rows(query), rows(key), rows(value)
+    if k.stride() != v.stride():
+        k, v = k.contiguous(), v.contiguous()
+    n, qh, d = q.shape
+    if out is None:
+        out = torch.empty((n, qh, d), dtype=q.dtype, device=q.device)
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    check(lib().tq_prefill_attention(q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dtype_code(q.dtype),
+                                     n, qh, k.shape[1], d, q.stride(0), q.stride(1), k.stride(0), k.stride(1),
+                                     out.stride(0), out.stride(1), float(scale), stream_ptr(q.device)),
+          "tq_prefill_attention")
+    return out
+
+
+def prefill_attention_status() -> int:
+    """Status word of the prefill attention kernel (0 = fine); synchronises the device."""
+    out = C.c_int32(0)
+    check(lib().tq_prefill_attention_read_status(C.byref(out)), "tq_prefill_attention_read_status")
+    return out.value
+
+
 def store_status() -> int:
     """Status word of the tensor-core store kernel (0 = fine); synchronises the device."""
     out = C.c_int32(0)

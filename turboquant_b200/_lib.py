@@ -78,6 +78,10 @@ SIGNATURES = {
                                  C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64,
                                  C.POINTER(tq_pool), C.c_void_p]),
     "tq_store_read_status": (C.c_int, [C.POINTER(C.c_int32)]),
+    "tq_prefill_attention": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int64, C.c_int32,
+                                       C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                       C.c_int64, C.c_float, C.c_void_p]),
+    "tq_prefill_attention_read_status": (C.c_int, [C.POINTER(C.c_int32)]),
     "tq_decode": (C.c_int, [C.POINTER(tq_consts), C.POINTER(tq_pool), C.POINTER(tq_decode_args), C.c_void_p]),
     "tq_decode_host_io": (C.c_int, [C.POINTER(tq_consts), C.POINTER(tq_pool), C.POINTER(tq_decode_args), C.c_void_p,
                                     C.c_void_p, C.c_size_t, C.c_void_p, C.c_size_t, C.c_void_p]),

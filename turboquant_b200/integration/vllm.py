@@ -23,6 +23,7 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
+from .. import _engine as E
 from ..capture import KVCaptureEngine
 from ..score import compute_hybrid_attention
 from ..store import CompressedKVStore
@@ -137,16 +138,22 @@ def _deliver(result: torch.Tensor, query: torch.Tensor, output, n: int):
 
 
 def _no_alloc_prefill_attention(state: LayerState, impl, query, key, value, attn_metadata) -> torch.Tensor:
-    """Causal prefill attention from the layer's own K/V when no paged cache exists."""
+    """Causal prefill attention from the layer's own K/V when no paged cache exists (reference
+    vllm.py:150-180).  16-bit CUDA tensors with head_dim 128 / 256 go through the library's tensor-core
+    kernel, which reads each kv head in place for its group of query heads (no repeat_interleave) and
+    lets the store of the same K/V, launched next on the stream, begin under its tail; anything else
+    takes torch's attention like the reference."""
     c = state.config
     n = attn_metadata.num_actual_tokens
     q = _as_heads(query, n, c.num_query_heads, c.head_dim)
     k = _as_heads(key, n, c.num_kv_heads, c.head_dim)
     v = _as_heads(value, n, c.num_kv_heads, c.head_dim)
+    scale = getattr(impl, "scale", 1.0 / math.sqrt(c.head_dim))
+    if E.prefill_attention_supported(q, k, v):
+        return E.prefill_attention(q, k, v, scale=scale)
     rep = c.num_query_heads // c.num_kv_heads
     if rep > 1:
         k, v = k.repeat_interleave(rep, dim=1), v.repeat_interleave(rep, dim=1)
-    scale = getattr(impl, "scale", 1.0 / math.sqrt(c.head_dim))
     out = F.scaled_dot_product_attention(q.transpose(0, 1).unsqueeze(0), k.transpose(0, 1).unsqueeze(0),
                                          v.transpose(0, 1).unsqueeze(0), is_causal=True, scale=scale)
     return out.squeeze(0).transpose(0, 1)
