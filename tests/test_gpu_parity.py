@@ -992,3 +992,93 @@ def test_prefill_attention_vs_fp32_reference(d, qh, h, n, dtype, dev):
     ks = qkv[:, qh * d:(qh + h) * d].view(n, h, d)
     vs = qkv[:, (qh + h) * d:].view(n, h, d)
     assert torch.equal(E.prefill_attention(qs, ks, vs, scale=scale), out)
+
+
+@pytest.mark.parametrize("d,h,qh,kb,vb", [(128, 8, 32, 3, 2), (128, 2, 8, 4, 4), (256, 4, 16, 3, 2)])
+def test_engine_allocated_compressed_paged_cache(d, h, qh, kb, vb, dev):
+    """A paged cache the ENGINE allocates at compressed size (CompressedCacheSpec.page_size_bytes), laid
+    over its buffer without a copy; a batch of ragged sequences is written through one slot mapping per
+    step (prefill of all sequences in one call, then single decode tokens with padding slots) and read
+    by one batched decode per step.  Every sequence must come out as from its own CompressedKVStore +
+    compute_hybrid_attention (reference store.py:73-90, score.py:33-91), and its records must be the
+    bytes a whole-sequence append writes."""
+    from turboquant_b200 import CompressedKVStore, compute_hybrid_attention
+    from turboquant_b200 import _engine as E
+    from turboquant_b200.paged_cache import CompressedCacheSpec, CompressedPagedKVCache
+    spec = CompressedCacheSpec(d, h, kb, vb)
+    assert spec.page_size_bytes == 16 * h * spec.bytes_per_token and spec.bf16_page_size_bytes == 16 * h * d * 4
+    lens0 = [700, 33, 1, 257]
+    steps = 20
+    budget = 80 * spec.page_size_bytes + 100                   # the engine's arithmetic: memory -> pages
+    num_blocks = spec.num_blocks_for(budget)
+    assert num_blocks == 80 and spec.max_memory_usage_bytes(700 + steps) == 45 * spec.page_size_bytes
+    raw = torch.zeros(budget, dtype=torch.uint8, device=dev)
+    cache = CompressedPagedKVCache(spec, raw[:num_blocks * spec.page_size_bytes])
+    assert cache.pool.data.data_ptr() == raw.data_ptr() and cache.num_blocks == 80
+    with pytest.raises(RuntimeError):
+        cache.pool.resize(81)
+
+    # the engine's block manager: blocks handed out in shuffled order
+    g = torch.Generator().manual_seed(3)
+    free = torch.randperm(num_blocks, generator=g).tolist()
+    tables = [[] for _ in lens0]
+    kv = [O.synth_kv(n + steps, h, d, seed=600 + i, dtype=torch.bfloat16) for i, n in enumerate(lens0)]
+
+    def slots(seq, start, count):
+        out = []
+        for pos in range(start, start + count):
+            while pos // 16 >= len(tables[seq]):
+                tables[seq].append(free.pop())
+            out.append(tables[seq][pos // 16] * 16 + pos % 16)
+        return out
+
+    # prefill: all sequences' tokens concatenated, one call
+    sl = [s_ for i, n in enumerate(lens0) for s_ in slots(i, 0, n)]
+    k_all = torch.cat([kv[i][0][:n] for i, n in enumerate(lens0)]).to(dev)
+    v_all = torch.cat([kv[i][1][:n] for i, n in enumerate(lens0)]).to(dev)
+    cache.write(k_all, v_all, torch.tensor(sl, dtype=torch.int64, device=dev))
+    refs = []
+    for i, n in enumerate(lens0):
+        st = CompressedKVStore(d, h, kb, vb, device=dev, capacity_tokens=n + steps)
+        st.append_chunk(kv[i][0][:n].to(dev), kv[i][1][:n].to(dev))
+        refs.append(st)
+    lens = list(lens0)
+    for step in range(steps):
+        # one new token per sequence plus two padding rows the engine marks with slot -1
+        rows_k = [kv[i][0][lens[i]:lens[i] + 1] for i in range(len(lens))]
+        rows_v = [kv[i][1][lens[i]:lens[i] + 1] for i in range(len(lens))]
+        pad = torch.full((2, h, d), 7.0, dtype=torch.bfloat16)
+        sl = [slots(i, lens[i], 1)[0] for i in range(len(lens))] + [-1, -1]
+        cache.write(torch.cat(rows_k + [pad]).to(dev), torch.cat(rows_v + [pad]).to(dev),
+                    torch.tensor(sl, dtype=torch.int64, device=dev))
+        for i in range(len(lens)):
+            refs[i].append_chunk(rows_k[i].to(dev), rows_v[i].to(dev))
+            lens[i] += 1
+        width = max(len(t) for t in tables)
+        bt = torch.tensor([t + [0] * (width - len(t)) for t in tables], dtype=torch.int32, device=dev)
+        q = O.synth_query(len(lens), qh, d, seed=700 + step, dtype=torch.bfloat16).to(dev)
+        out = cache.decode(q, bt, torch.tensor(lens, dtype=torch.int32, device=dev), max(lens))
+        assert cache.workspace.status() == 0
+        for i in range(len(lens)):
+            st = refs[i]
+            if lens[i] >= 16:      # the reference ignores a compressed history shorter than 16 tokens (score.py:44-47)
+                want = compute_hybrid_attention(q[i:i + 1], st, None, None, qh)
+            else:
+                want = E.decode(st.consts, st.pool, st.workspace, q[i:i + 1], st.block_table.unsqueeze(0),
+                                st.seq_len_device, lens[i], min_history=1)
+            assert _cos(out[i:i + 1], want) >= 0.99999
+            torch.testing.assert_close(out[i:i + 1].float(), want.float(), rtol=2e-2, atol=2e-3)
+            if step == steps - 1:  # and the oracle on the reference's own read path
+                c = st.consts
+                of = O.OracleStore(d, h, kb, vb, c.centroids_cpu, c.boundaries_cpu, pi=c.Pi.cpu(), s=c.S.cpu())
+                of.append_chunk(kv[i][0][:lens[i]], kv[i][1][:lens[i]])
+                ref = O.hybrid_attention(q[i:i + 1].cpu(), of.get_flat_cache(), None, None, h, c.Pi.cpu(), c.S.cpu(),
+                                         c.centroids_cpu)
+                assert _cos(out[i:i + 1].cpu(), ref) >= 0.9995
+    assert E.store_status() == 0
+    # records: same bytes as the per-sequence stores hold (token by token, whatever block they live in)
+    for i in range(len(lens)):
+        a = E.pool_to_planes(cache.consts, cache.pool, torch.tensor(tables[i], dtype=torch.int32, device=dev), lens[i])
+        b = E.pool_to_planes(refs[i].consts, refs[i].pool, refs[i].block_table, lens[i])
+        for f_ in ("mse_indices", "qjl_signs", "norms", "residual_norms", "v_data", "v_scales", "v_zeros"):
+            assert torch.equal(getattr(a, f_), getattr(b, f_)), (i, f_)

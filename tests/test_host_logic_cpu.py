@@ -81,3 +81,16 @@ def test_own_lloyd_max_solver_reproduces_the_shipped_code_books(d, bits):
     assert np.abs(np.array(own["boundaries"]) - np.array(shipped["boundaries"])).max() <= 1e-6
     assert abs(own["mse_per_coord"] - shipped["mse_per_coord"]) <= 1e-9
     assert own["boundaries"][0] == -1.0 and own["boundaries"][-1] == 1.0
+
+
+def test_compressed_cache_spec_page_arithmetic():
+    """Page geometry an engine sizes its block pool with: bytes per page = 16 tokens x kv heads x the
+    reference's per-token accounting (store.py:116-128), against bf16 K+V pages of the same block."""
+    from turboquant_b200.paged_cache import CompressedCacheSpec
+    s = CompressedCacheSpec(128, 8, 3, 2)
+    assert (s.bytes_per_token, s.page_size_bytes, s.bf16_page_size_bytes) == (100, 12800, 65536)
+    assert CompressedCacheSpec(256, 4, 3, 2).bytes_per_token == 196
+    assert CompressedCacheSpec(128, 8, 4, 4).bytes_per_token == 164
+    assert s.num_blocks_for(10 ** 9) == 78125 and s.max_memory_usage_bytes(32768 + 5) == 2049 * 12800
+    with pytest.raises(ValueError):
+        CompressedCacheSpec(128, 8, 3, 2, block_size=32)

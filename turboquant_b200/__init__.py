@@ -9,5 +9,6 @@ from .kv_cache import TurboQuantKVCache
 from .capture import RingBuffer, KVCaptureEngine
 from .store import CompressedKVStore
 from .score import compute_hybrid_attention
+from .paged_cache import CompressedCacheSpec, CompressedPagedKVCache
 
 __version__ = "0.1.0"

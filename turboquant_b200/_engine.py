@@ -143,6 +143,28 @@ class BlockPool:
     def nbytes(self) -> int:
         return self.data.numel()
 
+    @classmethod
+    def over(cls, consts: LayerConstants, num_kv_heads: int, raw: torch.Tensor) -> "BlockPool":
+        """A pool laid over memory somebody else allocated (a serving engine's KV-cache buffer): `raw`
+        is a contiguous uint8 device tensor, 16-byte aligned; as many whole blocks as fit are used.
+        The pool never grows and never copies."""
+        if raw.dtype != torch.uint8 or not raw.is_cuda or not raw.is_contiguous() or raw.data_ptr() % 16:
+            raise ValueError("the pool needs a contiguous, 16-byte aligned uint8 device tensor")
+        per_block = num_kv_heads * consts.block_bytes
+        n = raw.numel() // per_block
+        if n < 1:
+            raise ValueError(f"{raw.numel()} bytes hold no block of {per_block} bytes")
+        pool = cls.__new__(cls)
+        pool.consts, pool.num_kv_heads, pool.num_blocks = consts, num_kv_heads, n
+        pool.data = raw.view(-1)[: n * per_block]
+        pool.c = _lib.tq_pool(pool.data.data_ptr(), n, num_kv_heads)
+        pool.resize = pool._fixed
+        return pool
+
+    def _fixed(self, num_blocks: int) -> None:
+        if num_blocks > self.num_blocks:
+            raise RuntimeError(f"a pool over engine memory cannot grow ({self.num_blocks} -> {num_blocks} blocks)")
+
 
 class Workspace:
     """Zero-initialised scratch for tq_decode / tq_scores; grows on demand."""
