@@ -6,14 +6,15 @@
 // own diagonal:
 //   TMA   : Q once, K and V tiles (128-byte-swizzled boxes of 64 channels) -> shared memory
 //   MMA 1 : S = Q K^T            (tcgen05, operands from shared memory, fp32 in tensor memory)
-//   soft  : D/64 threads per query row read their share of the row of S, exchange the row maximum,
+//   soft  : four threads per query row read their share of the row of S, exchange the row maximum,
 //           exponentiate against a running maximum that is only moved when the true one has grown by
 //           more than 2^8 (the accumulator is then rescaled in tensor memory - rare), and write the
 //           probabilities back to tensor memory as a 16-bit A operand
 //   MMA 2 : O += P V             (A from tensor memory; V is used as it lies, its channel dimension
 //                                 contiguous: the MN-major operand form)
 // and finally divides by the row sums.  K/V are read from L2 / HBM once per query head and tile; no
-// score matrix ever leaves the SM.  Tensor memory: S 128 columns | P 64 | O head_dim.
+// score matrix ever leaves the SM.  Tensor memory: S 128 columns | P 64 | O head_dim; at head_dim 128
+// S and P are doubled and Q K^T of the next tile runs under the softmax of this one.
 //
 // One warp issues every TMA load and MMA (one elected lane); the compute threads hand over through
 // mbarriers.  Every wait is bounded; a timeout frees tensor memory and leaves a status.
@@ -28,7 +29,13 @@ namespace {
 
 constexpr int PA_TOK = 128;                   // query rows and key rows per tile
 constexpr int PA_BOX = PA_TOK * 128;          // one swizzled box: 128 rows x 64 channels of 16 bits
-constexpr uint32_t PA_COL_S = 0, PA_COL_P = 128, PA_COL_O = 256;
+constexpr int PA_TPR = 4;                     // compute threads per query row
+constexpr int PA_THREADS = PA_TOK * PA_TPR + 32;   // plus the issuing warp
+// tensor-memory columns.  head_dim 128: two S buffers and two P buffers, so that Q K^T of the next tile
+// runs under the softmax of this one; head_dim 256 (O takes 256 columns): one of each.
+template <int D> struct PaCols;
+template <> struct PaCols<128> { static constexpr uint32_t S = 0, S_STEP = 128, P = 256, P_STEP = 64, O = 384; };
+template <> struct PaCols<256> { static constexpr uint32_t S = 0, S_STEP = 0, P = 128, P_STEP = 0, O = 256; };
 constexpr float PA_RESCALE_STEP = 8.f;        // log2 of the factor the running maximum may lag behind
 
 struct PrefillParams {
@@ -51,6 +58,11 @@ __device__ __forceinline__ float pa_ex2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float pa_max3(float a, float b, float c) {
+    float y;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
+}
 __device__ __forceinline__ uint32_t pa_pack(float lo, float hi, bool bf16) {
     if (bf16) return pack_bf16(lo, hi);
     const __half2 h = __floats2half2_rn(lo, hi);
@@ -58,14 +70,17 @@ __device__ __forceinline__ uint32_t pa_pack(float lo, float hi, bool bf16) {
 }
 
 template <int D>
-__global__ void __launch_bounds__(2 * D + 32, 1)
+__global__ void __launch_bounds__(PA_THREADS, 1)
 tq_prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
-    constexpr int TPR = D / 64;               // threads per query row
+    constexpr int TPR = PA_TPR;               // threads per query row
+    constexpr int OC = D / TPR;               // accumulator columns per thread
     constexpr int NCOMP = PA_TOK * TPR;       // compute threads
     constexpr int SC = PA_TOK / TPR;          // columns of S per thread
     constexpr int NBOX = D / 64;              // boxes per tile
     constexpr int NST = D == 128 ? 2 : 1;     // key/value stages
+    constexpr bool AHEAD = D == 128;          // S of tile t+1 is issued before P V of tile t
+    using Col = PaCols<D>;
     constexpr int TILE_BYTES = NBOX * PA_BOX;
 
     extern __shared__ uint8_t smem_raw[];
@@ -73,10 +88,10 @@ tq_prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     uint8_t* sQ = smem;
     uint8_t* sK = sQ + TILE_BYTES;            // [NST]
     uint8_t* sV = sK + NST * TILE_BYTES;      // [NST]
-    float* s_red = reinterpret_cast<float*>(sV + NST * TILE_BYTES);   // [TPR][128]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(s_red + TPR * PA_TOK);
-    uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 3, *bar_s = bars + 5, *bar_p = bars + 6, *bar_o = bars + 7;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+    float* s_red = reinterpret_cast<float*>(sV + NST * TILE_BYTES);   // [2][TPR][128], by tile parity
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_red + 2 * TPR * PA_TOK);
+    uint64_t *bar_q = bars, *bar_k = bars + 1, *bar_v = bars + 3, *bar_s = bars + 5, *bar_p = bars + 7, *bar_o = bars + 8;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
     volatile int* s_fail = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -91,7 +106,7 @@ tq_prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
     if (tid == 0) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) tq_mbar_init(bars + i, i == 6 ? NCOMP : 1);
+        for (int i = 0; i < 9; ++i) tq_mbar_init(bars + i, i == 7 ? NCOMP : 1);
         *s_fail = 0;
         tq_mbar_fence_init();
     }
@@ -140,44 +155,72 @@ tq_prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         load_tile(sQ, &tm_q, bar_q, q0, qh);
         load_tile(sK, &tm_k, bar_k, 0, kvh);
         load_tile(sV, &tm_v, bar_v, 0, kvh);
+        if (AHEAD && n_kv_tiles > 1) {
+            load_tile(sK + TILE_BYTES, &tm_k, bar_k + 1, PA_TOK, kvh);
+            load_tile(sV + TILE_BYTES, &tm_v, bar_v + 1, PA_TOK, kvh);
+        }
         bool ok = wait1(bar_q, 0);
         const uint32_t aQ = tq_smem_u32(sQ), aK = tq_smem_u32(sK), aV = tq_smem_u32(sV);
-#pragma unroll 1
-        for (int t = 0; t < n_kv_tiles && ok; ++t) {
+        auto issue_s = [&](int t) -> bool {   // S_t = Q K_t^T into S buffer t % 2 (head_dim 128) or the only one
             const int st = t % NST;
-            const uint32_t ph = (uint32_t)(t / NST) & 1u;
-            if (!(ok = wait1(bar_k + st, ph))) break;
+            if (!wait1(bar_k + st, (uint32_t)(t / NST) & 1u)) return false;
             tc_fence_after();
-            if (elected()) {   // S = Q K^T: the threads passed bar_p of the tile before, S is free
+            if (elected()) {
 #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t off = (ks >> 2) * PA_BOX + (ks & 3) * 32;
-                    umma_ss(tmem_u + PA_COL_S, smem_desc_sw128(aQ + off), smem_desc_sw128(aK + st * TILE_BYTES + off),
-                            idesc_s, ks ? 1u : 0u);
+                    umma_ss(tmem_u + Col::S + (t & 1) * Col::S_STEP, smem_desc_sw128(aQ + off),
+                            smem_desc_sw128(aK + st * TILE_BYTES + off), idesc_s, ks ? 1u : 0u);
                 }
-                umma_commit(bar_s);
+                umma_commit(bar_s + (AHEAD ? (t & 1) : 0));
             }
             __syncwarp();
-            if (NST == 2 && t + 1 < n_kv_tiles) {   // the other stage was read by the products of tile t-1
-                if (t >= 1 && !(ok = wait1(bar_o, (uint32_t)(t - 1) & 1u))) break;
-                load_tile(sK + ((t + 1) % NST) * TILE_BYTES, &tm_k, bar_k + (t + 1) % NST, (t + 1) * PA_TOK, kvh);
-                load_tile(sV + ((t + 1) % NST) * TILE_BYTES, &tm_v, bar_v + (t + 1) % NST, (t + 1) * PA_TOK, kvh);
-            }
-            if (!(ok = wait1(bar_p, (uint32_t)t & 1u))) break;     // probabilities in tensor memory
-            if (!(ok = wait1(bar_v + st, ph))) break;
+            return true;
+        };
+        auto issue_pv = [&](int t) -> bool {  // O += P_t V_t, sixteen key tokens per step
+            const int st = t % NST;
+            if (!wait1(bar_v + st, (uint32_t)(t / NST) & 1u)) return false;
             tc_fence_after();
-            if (elected()) {   // O += P V, sixteen key tokens per step
+            if (elected()) {
 #pragma unroll
                 for (int ks = 0; ks < PA_TOK / 16; ++ks)
-                    umma_ts(tmem_u + PA_COL_O, tmem_u + PA_COL_P + ks * 8,
+                    umma_ts(tmem_u + Col::O, tmem_u + Col::P + (t & 1) * Col::P_STEP + ks * 8,
                             smem_desc_sw128_mn(aV + st * TILE_BYTES + ks * 2048, PA_BOX), idesc_o, (t | ks) ? 1u : 0u);
                 umma_commit(bar_o);
             }
             __syncwarp();
-            if (NST == 1 && t + 1 < n_kv_tiles) {
-                if (!(ok = wait1(bar_o, (uint32_t)t & 1u))) break;
-                load_tile(sK, &tm_k, bar_k, (t + 1) * PA_TOK, kvh);
-                load_tile(sV, &tm_v, bar_v, (t + 1) * PA_TOK, kvh);
+            return true;
+        };
+        if (AHEAD) {
+            // S_0 | S_1, PV_0 | S_2, PV_1 | ...: the tensor pipe works on S_{t+1} while the threads turn S_t
+            // into P_t.  S buffer (t+1) % 2 is free because the threads passed bar_p of tile t-1; the key stage
+            // of tile t is free once S_t has been computed, the value stage once P_t V_t has completed.
+            ok = ok && issue_s(0);
+#pragma unroll 1
+            for (int t = 0; t < n_kv_tiles && ok; ++t) {
+                if (t + 1 < n_kv_tiles && !(ok = issue_s(t + 1))) break;
+                if (t + 2 < n_kv_tiles) {   // S_t has been computed (long ago, as a rule): its key stage is free
+                    if (!(ok = wait1(bar_s + (t & 1), (uint32_t)(t >> 1) & 1u))) break;
+                    load_tile(sK + (t % NST) * TILE_BYTES, &tm_k, bar_k + t % NST, (t + 2) * PA_TOK, kvh);
+                }
+                if (!(ok = wait1(bar_p, (uint32_t)t & 1u))) break;
+                if (!(ok = issue_pv(t))) break;
+                if (t + 2 < n_kv_tiles) {
+                    if (!(ok = wait1(bar_o, (uint32_t)t & 1u))) break;
+                    load_tile(sV + (t % NST) * TILE_BYTES, &tm_v, bar_v + t % NST, (t + 2) * PA_TOK, kvh);
+                }
+            }
+        } else {
+#pragma unroll 1
+            for (int t = 0; t < n_kv_tiles && ok; ++t) {
+                if (!(ok = issue_s(t))) break;          // the threads passed bar_p of the tile before: S is free
+                if (!(ok = wait1(bar_p, (uint32_t)t & 1u))) break;
+                if (!(ok = issue_pv(t))) break;
+                if (t + 1 < n_kv_tiles) {
+                    if (!(ok = wait1(bar_o, (uint32_t)t & 1u))) break;
+                    load_tile(sK, &tm_k, bar_k, (t + 1) * PA_TOK, kvh);
+                    load_tile(sV, &tm_v, bar_v, (t + 1) * PA_TOK, kvh);
+                }
             }
         }
     } else {
@@ -218,31 +261,38 @@ tq_prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         bool ok = true;
 #pragma unroll 1
         for (int t = 0; t < n_kv_tiles; ++t) {
-            bool bad = !wait_warp(bar_s, (uint32_t)t & 1u);
+            bool bad = !wait_warp(bar_s + (AHEAD ? (t & 1) : 0), (uint32_t)(AHEAD ? t >> 1 : t) & 1u);
             tc_fence_after();
+            const uint32_t col_s = Col::S + (t & 1) * Col::S_STEP, col_p = Col::P + (t & 1) * Col::P_STEP;
+            // raw logits; the softmax scale (> 0, times log2 e) is applied inside the exponent's multiply-add
             float s[SC];
 #pragma unroll
             for (int c = 0; c < SC / 32; ++c) {
                 float v[32];
-                tmem_ld32(tmem + lane_base + PA_COL_S + part * SC + c * 32, v);
+                tmem_ld32(tmem + lane_base + col_s + part * SC + c * 32, v);
 #pragma unroll
-                for (int i = 0; i < 32; ++i) s[c * 32 + i] = v[i] * p.scale_log2;
+                for (int i = 0; i < 32; ++i) s[c * 32 + i] = v[i];
             }
             if (t == qt) {   // the diagonal tile: a key after the query is masked
 #pragma unroll
                 for (int i = 0; i < SC; ++i)
                     if (part * SC + i > row) s[i] = -INFINITY;
             }
-            float mx = s[0];
+            float mx = pa_max3(s[0], s[1], s[2]);
 #pragma unroll
-            for (int i = 1; i < SC; ++i) mx = fmaxf(mx, s[i]);
-            s_red[part * PA_TOK + row] = mx;
+            for (int i = 3; i + 1 < SC; i += 2) mx = pa_max3(mx, s[i], s[i + 1]);
+            if ((SC & 1) == 0) mx = fmaxf(mx, s[SC - 1]);
+            // two exchange buffers: with S issued a tile ahead, a fast thread may start the next tile while a
+            // slow one still reads this tile's maxima; it cannot get two tiles ahead of the barrier below
+            float* red = s_red + (t & 1) * TPR * PA_TOK;
+            red[part * PA_TOK + row] = mx;
             if (barrier_or(bad)) {
                 ok = false;
                 break;
             }
 #pragma unroll
-            for (int q = 0; q < TPR; ++q) mx = fmaxf(mx, s_red[q * PA_TOK + row]);
+            for (int q = 0; q < TPR; ++q) mx = fmaxf(mx, red[q * PA_TOK + row]);
+            mx *= p.scale_log2;
             // every tile holds at least key 0 <= row unmasked, so mx is finite
             float alpha = 1.f;
             const bool move = mx > m_run + PA_RESCALE_STEP;   // also the first tile (m_run = -inf)
@@ -252,9 +302,10 @@ tq_prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             }
             float sum = 0.f;
             uint32_t pk[SC / 2];
+            const float neg_m = -m_run;
 #pragma unroll
             for (int i = 0; i < SC / 2; ++i) {
-                const float a = pa_ex2(s[2 * i] - m_run), b = pa_ex2(s[2 * i + 1] - m_run);
+                const float a = pa_ex2(fmaf(s[2 * i], p.scale_log2, neg_m)), b = pa_ex2(fmaf(s[2 * i + 1], p.scale_log2, neg_m));
                 sum += a + b;
                 pk[i] = pa_pack(a, b, bf16);
             }
@@ -264,44 +315,49 @@ tq_prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 uint32_t w[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) w[i] = pk[c * 16 + i];
-                tmem_st16(tmem + lane_base + PA_COL_P + part * (SC / 2) + c * 16, w);
+                tmem_st16(tmem + lane_base + col_p + part * (SC / 2) + c * 16, w);
             }
-            // S of this tile was issued after the product of the tile before: that product is complete,
-            // the accumulator may be rescaled in place
+            // The accumulator may be rescaled in place once the product of the tile before has completed:
+            // implied by this tile's S when the products are issued in tile order; waited for otherwise -
+            // by every thread at every tile, so that each sees every phase of bar_o and a later wait on
+            // its parity cannot be satisfied by an older phase.
+            if (AHEAD && t > 0) {
+                if (!wait_warp(bar_o, (uint32_t)(t - 1) & 1u)) *s_fail = 1;
+                tc_fence_after();
+            }
             if (t > 0 && __any_sync(0xffffffffu, move)) {
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
+                for (int c = 0; c < OC / 32; ++c) {
                     float o[32];
-                    tmem_ld32(tmem + lane_base + PA_COL_O + part * 64 + c * 32, o);
+                    tmem_ld32(tmem + lane_base + Col::O + part * OC + c * 32, o);
 #pragma unroll
                     for (int i = 0; i < 32; ++i) o[i] *= alpha;
-                    tmem_st32(tmem + lane_base + PA_COL_O + part * 64 + c * 32, o);
+                    tmem_st32(tmem + lane_base + Col::O + part * OC + c * 32, o);
                 }
             }
             tmem_st_wait();
             tc_fence_before();
-            // the barrier above also orders this tile's reads of s_red before the next tile's writes:
-            // a thread writes s_red again only after bar_s of the next tile, which needs every arrival here
             pa_arrive(bar_p);
         }
         if (ok) {
             bool bad = !wait_warp(bar_o, (uint32_t)(n_kv_tiles - 1) & 1u);
             tc_fence_after();
-            s_red[part * PA_TOK + row] = l_run;
+            float* red = s_red + (n_kv_tiles & 1) * TPR * PA_TOK;
+            red[part * PA_TOK + row] = l_run;
             if (barrier_or(bad)) ok = false;
             if (ok) {
                 float l = 0.f;
 #pragma unroll
-                for (int q = 0; q < TPR; ++q) l += s_red[q * PA_TOK + row];
+                for (int q = 0; q < TPR; ++q) l += red[q * PA_TOK + row];
                 const float inv = 1.f / l;
                 const int64_t tok = (int64_t)q0 + row;
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
+                for (int c = 0; c < OC / 32; ++c) {
                     float o[32];
-                    tmem_ld32(tmem + lane_base + PA_COL_O + part * 64 + c * 32, o);
+                    tmem_ld32(tmem + lane_base + Col::O + part * OC + c * 32, o);
                     if (tok < p.n_tokens) {
                         uint16_t* dst = static_cast<uint16_t*>(p.out) + tok * p.out_stride_token +
-                                        (int64_t)qh * p.out_stride_head + part * 64 + c * 32;
+                                        (int64_t)qh * p.out_stride_head + part * OC + c * 32;
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             uint4 w;
@@ -392,18 +448,18 @@ extern "C" int tq_prefill_attention(const void* query, const void* key, const vo
     p.out_stride_token = out_stride_token;
     p.out_stride_head = out_stride_head;
     const int nbox = D / 64, nst = D == 128 ? 2 : 1;
-    const size_t smem = (size_t)(1 + 2 * nst) * nbox * PA_BOX + (size_t)(D / 64) * PA_TOK * sizeof(float) +
-                        8 * sizeof(uint64_t) + 16 + 1024;
+    const size_t smem = (size_t)(1 + 2 * nst) * nbox * PA_BOX + (size_t)2 * PA_TPR * PA_TOK * sizeof(float) +
+                        9 * sizeof(uint64_t) + 16 + 1024;
     const dim3 grid((unsigned)p.n_tiles, (unsigned)num_q_heads);
     cudaStream_t st = (cudaStream_t)stream;
     if (D == 128) {
         static TqSmemOptIn opt_in;
         if (tq_opt_in_smem(tq_prefill_attn_kernel<128>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;
-        tq_prefill_attn_kernel<128><<<grid, 2 * 128 + 32, smem, st>>>(tm_q, tm_k, tm_v, p);
+        tq_prefill_attn_kernel<128><<<grid, PA_THREADS, smem, st>>>(tm_q, tm_k, tm_v, p);
     } else {
         static TqSmemOptIn opt_in;
         if (tq_opt_in_smem(tq_prefill_attn_kernel<256>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;
-        tq_prefill_attn_kernel<256><<<grid, 2 * 256 + 32, smem, st>>>(tm_q, tm_k, tm_v, p);
+        tq_prefill_attn_kernel<256><<<grid, PA_THREADS, smem, st>>>(tm_q, tm_k, tm_v, p);
     }
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
