@@ -189,40 +189,12 @@ __global__ void __launch_bounds__(256, OCC) tq_qprep_kernel(const void* __restri
     }
 }
 
-// One element of the query preparation's output: the fp32 value and, when asked for, its place in the
-// fp16 MMA fragments of the tensor-core decode kernel.  `which` 0: rotated (q Pi^T), 1: sketched (q S^T);
-// `qn2`: squared norm of the query vector (the fragment's power-of-two scale is derived from it alone).
-template <int D>
-__device__ __forceinline__ void qprep_emit(float t, int64_t vec, int which, int col, float qn2, float* out, uint32_t* frag,
-                                           int G, int Qh, int mse_bits) {
-    out[(vec * 2 + which) * D + col] = t;
-    if (frag == nullptr) return;
-    const int qh = (int)(vec % Qh), g = qh % G;
-    const int64_t pair = (vec / Qh) * (Qh / G) + qh / G;   // (sequence, kv head)
-    const bool split = G > 4 || mse_bits == 3;             // separate rotated / sketched fragment sets
-    uint32_t* base = frag + pair * qf_words(D, split ? 8 : 4);
-    const float bound = sqrtf(qn2) * (which ? 2.f * sqrtf((float)D) : 1.f);
-    int e = 0;
-    if (bound > 0.f && bound < 3.0e38f) e = max(-100, min(100, 14 - ilogbf(bound)));
-    if (col == 0) reinterpret_cast<float*>(base)[which * 8 + g] = (float)e;
-    const int tig = col / (D / 4), rem = col % (D / 4);
-    int wi = rem >> 4, half = (rem >> 3) & 1, jf = rem & 7;
-    int r = wi * 8 + jf;
-    int sh = which ? sign_pos(sign_bit(wi, jf)) : 2 * code_pos(jf);
-    if (mse_bits == 3 && which == 0) {   // nibble codes: see tq_qprep_kernel
-        r = rem >> 1;
-        half = rem & 1;
-        sh = 0;
-    }
-    const int gid = split ? g : g + 4 * which;
-    const int set = split ? which : 0;
-    __half* dst = reinterpret_cast<__half*>(base + QF_HDR + ((set * (D / 8) + r) * 32 + gid * 4 + tig));
-    dst[half] = __float2half_rn(t * __int_as_float((127 + e - sh) << 23));
-}
-
 // Query preparation for large batches: a plain tiled fp32 product (64 vectors x 64 columns per CTA,
 // 4 x 4 outputs per thread) instead of the latency-oriented kernel above, whose CTAs re-read their
-// matrix slice and the queries from shared memory once per multiply-add.
+// matrix slice and the queries from shared memory once per multiply-add.  A CTA's 64 columns are four
+// strips of 16 - one in each quarter of the head dimension - because that is what fills whole rows of
+// the fp16 MMA fragments (a fragment row holds, for eight query heads, the four quarters' elements of
+// one position): the results are staged in shared memory and leave as full 128-byte rows.
 constexpr int QB_V = 64, QB_C = 64, QB_K = 32;
 template <int D>
 __global__ void __launch_bounds__(256) tq_qprep_batched_kernel(const void* __restrict__ q, int dt, int64_t nvec,
@@ -231,13 +203,14 @@ __global__ void __launch_bounds__(256) tq_qprep_batched_kernel(const void* __res
                                                                uint32_t* __restrict__ frag, int G, int Qh, int mse_bits) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     extern __shared__ __align__(16) float qb_smem[];
-    float* qT = qb_smem;                    // [D][QB_V] queries, transposed
+    float* qT = qb_smem;                    // [D][QB_V] queries, transposed; later the [QB_V][QB_C + 1] results
     float* mt = qT + D * QB_V;              // [QB_K][QB_C] matrix rows of the current k chunk
     float* part = mt + QB_K * QB_C;         // [4][QB_V] partial squared norms
     const int tid = threadIdx.x;
     const int64_t v0 = (int64_t)blockIdx.y * QB_V;
-    const int col0 = blockIdx.x * QB_C;     // column of [Pi^T | S^T]
-    const int which = col0 / D, mcol0 = col0 % D;
+    const int which = blockIdx.x / (D / 64), strip = blockIdx.x % (D / 64);
+    // local column lc: quarter lc / 16 of the head dimension, position 16 * strip + lc % 16 inside it
+    auto column = [&](int lc) { return (lc >> 4) * (D / 4) + 16 * strip + (lc & 15); };
     const float* __restrict__ m = which ? s_t : pi_t;
     asm volatile("griddepcontrol.wait;" ::: "memory");   // the queries may come from the kernel ahead
     {   // queries: 16-byte chunks, lanes walking the vectors so that the transposed stores spread over the banks
@@ -287,7 +260,7 @@ __global__ void __launch_bounds__(256) tq_qprep_batched_kernel(const void* __res
         __syncthreads();   // queries stored (first round) / previous matrix chunk consumed
         for (int i = tid; i < QB_K * QB_C / 4; i += 256) {
             const int kk = i / (QB_C / 4), c4 = i % (QB_C / 4);
-            reinterpret_cast<float4*>(mt)[i] = __ldg(reinterpret_cast<const float4*>(m + (size_t)(k0 + kk) * D + mcol0) + c4);
+            reinterpret_cast<float4*>(mt)[i] = __ldg(reinterpret_cast<const float4*>(m + (size_t)(k0 + kk) * D + column(4 * c4)));
         }
         __syncthreads();
 #pragma unroll 8
@@ -301,14 +274,44 @@ __global__ void __launch_bounds__(256) tq_qprep_batched_kernel(const void* __res
                 for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
         }
     }
+    __syncthreads();   // the queries are consumed: their space takes the results
+    constexpr int RP = QB_C + 1;
+    float* res = qT;   // [QB_V][RP]
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int v = 4 * ty + i;
-        if (v0 + v >= nvec) continue;
-        const float qn2 = (part[v] + part[QB_V + v]) + (part[2 * QB_V + v] + part[3 * QB_V + v]);
+    for (int i = 0; i < 4; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-            qprep_emit<D>(acc[i][j], v0 + v, which, mcol0 + 4 * tx + j, qn2, out, frag, G, Qh, mse_bits);
+        for (int j = 0; j < 4; ++j) res[(4 * ty + i) * RP + 4 * tx + j] = acc[i][j];
+    __syncthreads();
+    // fp32 results: 64-byte runs (one strip of one quarter)
+    for (int i = tid; i < QB_V * QB_C; i += 256) {
+        const int v = i / QB_C, lc = i % QB_C;
+        if (v0 + v < nvec) out[((v0 + v) * 2 + which) * D + column(lc)] = res[v * RP + lc];
+    }
+    if (frag == nullptr) return;
+    // fragment words: thread = (quarter, vector); lanes (quarter, vector % 8) write one 128-byte fragment row
+    // when eight query heads share a kv head.  Element layout as in tq_qprep_kernel.
+    const int tig = tid & 3, v = tid >> 2;
+    if (v0 + v >= nvec) return;
+    const int64_t vec = v0 + v;
+    const int qh = (int)(vec % Qh), g = qh % G;
+    const int64_t pair = (vec / Qh) * (Qh / G) + qh / G;   // (sequence, kv head)
+    const bool split = G > 4 || mse_bits == 3;             // separate rotated / sketched fragment sets
+    uint32_t* base = frag + pair * qf_words(D, split ? 8 : 4);
+    const float qn2 = (part[v] + part[QB_V + v]) + (part[2 * QB_V + v] + part[3 * QB_V + v]);
+    const float bound = sqrtf(qn2) * (which ? 2.f * sqrtf((float)D) : 1.f);
+    int e = 0;
+    if (bound > 0.f && bound < 3.0e38f) e = max(-100, min(100, 14 - ilogbf(bound)));
+    if (strip == 0 && tig == 0) reinterpret_cast<float*>(base)[which * 8 + g] = (float)e;
+    const bool nibble = mse_bits == 3 && which == 0;       // two adjacent positions per word instead of j, j + 8
+    const int gid = split ? g : g + 4 * which;
+    const int set = split ? which : 0;
+#pragma unroll
+    for (int rl = 0; rl < 8; ++rl) {
+        const int lc0 = tig * 16 + (nibble ? 2 * rl : rl), lc1 = tig * 16 + (nibble ? 2 * rl + 1 : rl + 8);
+        const int sh = nibble ? 0 : (which ? sign_pos(sign_bit(strip, rl)) : 2 * code_pos(rl));
+        const float scale = __int_as_float((127 + e - sh) << 23);
+        const __half2 h2 = __floats2half2_rn(res[v * RP + lc0] * scale, res[v * RP + lc1] * scale);
+        base[QF_HDR + (set * (D / 8) + 8 * strip + rl) * 32 + gid * 4 + tig] = *reinterpret_cast<const uint32_t*>(&h2);
     }
 }
 

@@ -32,6 +32,9 @@
 // mbarrier is bounded; a timeout frees tensor memory and returns with a status.
 #include <cuda.h>
 
+#include <cstring>
+#include <mutex>
+
 #include "tq_common.cuh"
 #include "tq_tcgen05.cuh"
 
@@ -1191,6 +1194,37 @@ bool make_rows_map(CUtensorMap* tm, const void* base, int D, int64_t n_tokens, i
                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// The four constant operands' maps are the same for every call of a layer: the last few sets are kept
+// (a map holds only the address and the geometry, never the matrix).
+struct OperandMapSet {
+    const void* ptr[4];
+    int D;
+    CUtensorMap tm[4];
+};
+bool operand_maps(CUtensorMap (&out)[4], const tq_consts* consts, int D) {
+    constexpr int SETS = 16;
+    static std::mutex mu;
+    static OperandMapSet sets[SETS];
+    static int n_sets = 0, next = 0;
+    const void* want[4] = {consts->pi_limbs[0], consts->pi_limbs[1], consts->m_limbs[0], consts->m_limbs[1]};
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < n_sets; ++i)
+        if (sets[i].D == D && memcmp(sets[i].ptr, want, sizeof(want)) == 0) {
+            memcpy(out, sets[i].tm, sizeof(sets[i].tm));
+            return true;
+        }
+    OperandMapSet fresh;
+    memcpy(fresh.ptr, want, sizeof(want));
+    fresh.D = D;
+    for (int i = 0; i < 4; ++i)
+        if (!make_matrix_map(&fresh.tm[i], want[i], D)) return false;
+    sets[next] = fresh;
+    next = (next + 1) % SETS;
+    if (n_sets < SETS) ++n_sets;
+    memcpy(out, fresh.tm, sizeof(fresh.tm));
+    return true;
+}
+
 // Paged cache (blocks, block_size tokens, heads, D) bf16 with element strides: boxes of 64 channels x
 // `box_rows` tokens of one head of one block.  `rows` is the extent of the token dimension - the block
 // size, or fewer for the view whose rows past the sequence's last token must read as zeros.
@@ -1291,8 +1325,7 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
         tm_kt = tm_k;
         tm_vt = tm_v;
     }
-    if (!maps_ok || !make_matrix_map(&tm_b[0], consts->pi_limbs[0], D) || !make_matrix_map(&tm_b[1], consts->pi_limbs[1], D) ||
-        !make_matrix_map(&tm_b[2], consts->m_limbs[0], D) || !make_matrix_map(&tm_b[3], consts->m_limbs[1], D))
+    if (!maps_ok || !operand_maps(tm_b, consts, D))
         return TQ_OK;   // a stride pattern the tensor map cannot express: the fp32 kernel takes the call
     *handled = 1;
 
