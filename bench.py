@@ -283,6 +283,54 @@ def measure_store(dev):
             "api_gbs": nbytes / ms_api / 1e6, "device_status": status}
 
 
+def measure_prefill(dev):
+    """Causal prefill attention of the no-alloc mode (the layer's own K/V, no paged cache) followed by the
+    store of the same K/V: one 8192-token sequence, 32 query heads over 8 kv heads, head_dim 128, bf16.  The
+    attention kernel is tensor-bound: flops = 4 * n^2 / 2 * D * Qh against the measured bf16 matmul peak."""
+    from turboquant_b200 import CompressedKVStore, _engine as E
+    n, qh, h, d = 8192, 32, 8, 128
+    g = torch.Generator(device=dev)
+    g.manual_seed(8)
+    q = torch.randn(n, qh, d, generator=g, device=dev).to(torch.bfloat16)
+    k = torch.randn(n, h, d, generator=g, device=dev).to(torch.bfloat16)
+    v = torch.randn(n, h, d, generator=g, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    st = CompressedKVStore(d, h, 3, 2, device=dev, capacity_tokens=n)
+
+    def step(with_store):
+        E.prefill_attention(q, k, v, out=out)
+        if with_store:
+            st.reset()
+            st.append_chunk(k, v)
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ms = {}
+    for with_store in (False, True):
+        for _ in range(3):
+            step(with_store)
+        torch.cuda.synchronize()
+        reps = 10
+        e0.record()
+        for _ in range(reps):
+            step(with_store)
+        e1.record()
+        torch.cuda.synchronize()
+        ms[with_store] = e0.elapsed_time(e1) / reps
+    flops = 4.0 * n * n / 2 * d * qh
+    peak_tf = 1590.0
+    kind = "fallback"
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            peak_tf, kind = float(json.load(fh)["bf16_tflops"]), "measured"
+    tf = flops / (ms[False] * 1e-3) / 1e12
+    return {"workload": "causal prefill attention, 8192 tokens, 32 query / 8 kv heads, D=128, bf16", "ms_attention": ms[False],
+            "ms_attention_and_store": ms[True], "tflops": tf,
+            "roofline": {"bound": "tensor", "achieved": tf, "peak": peak_tf, "unit": "TFLOP/s", "frac": tf / peak_tf,
+                         "peak_kind": f"of {kind} (burst)"},
+            "device_status": E.prefill_attention_status()}
+
+
 def measure_decode_large(dev, n_seq: int = 256, n_tok: int = 8192):
     """Batched decode of one Llama-3-70B-shaped layer: 256 sequences x
     8192 compressed tokens, 8 kv heads, 64 query heads, head_dim 128, 3-bit keys / 2-bit values.
@@ -712,6 +760,7 @@ def run_ours(args):
 
     sharded = measure_sharded(dev, dist, rank, world) if not args.no_large else None   # every rank takes part
     store = measure_store(dev) if rank == 0 else None
+    prefill = measure_prefill(dev) if (rank == 0 and not args.no_large) else None
     large = measure_decode_large(dev) if (rank == 0 and not args.no_large) else None
     paged = measure_decode_paged(dev) if (rank == 0 and not args.no_large) else None
     base = cpu_baseline(3, 1, w["N"]) if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
@@ -742,7 +791,7 @@ def run_ours(args):
                     "h2d_bytes_per_step": (2 * w["H"] + w["Qh"]) * w["D"] * 2,
                     "d2h_bytes_per_step": w["Qh"] * w["D"] * 2},
             "gpu_launches": launches, "device_status": status, "clocks": clocks, "store": store,
-            "decode_large": large, "decode_paged": paged, "sharded": sharded,
+            "decode_large": large, "decode_paged": paged, "sharded": sharded, "prefill": prefill,
         }
         if base is not None:
             line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
@@ -763,6 +812,7 @@ def main():
     ap.add_argument("--only-large", action="store_true", help="run only the batched decode measurement (profiling)")
     ap.add_argument("--only-store", action="store_true", help="run only the store-path measurement (profiling)")
     ap.add_argument("--only-paged", action="store_true", help="run only the paged batched decode measurement (profiling)")
+    ap.add_argument("--only-prefill", action="store_true", help="run only the prefill attention measurement (profiling)")
     ap.add_argument("--sharded", action="store_true",
                     help="only the partitioned layer stack with its all-gather of head outputs (strong scaling)")
     args = ap.parse_args()
@@ -770,6 +820,9 @@ def main():
     if args.only_store:
         torch.cuda.set_device(0)
         print(json.dumps(measure_store(torch.device("cuda", 0))), flush=True)
+    elif args.only_prefill:
+        torch.cuda.set_device(0)
+        print(json.dumps(measure_prefill(torch.device("cuda", 0))), flush=True)
     elif args.only_paged:
         torch.cuda.set_device(0)
         print(json.dumps(measure_decode_paged(torch.device("cuda", 0))), flush=True)

@@ -353,7 +353,8 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     uint64_t* bar_a = bars + 8;    // P of the tile before read: E's columns are free
     uint64_t* bar_c = bars + 9;    // r' limbs written, Y and E read
     uint64_t* bar_vf = bars + 10;  // value rows consumed
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+    uint64_t* bar_m = bars + 11;   // (TMA bytes, count 1) M_hi, M_lo landed; bar_b: Pi_hi, Pi_lo
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile int* s_fail = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -373,6 +374,7 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
         for (int i = 0; i < 7; ++i) tq_mbar_init(bars + i, 1);
 #pragma unroll
         for (int i = 7; i < 11; ++i) tq_mbar_init(bars + i, TC_THREADS);
+        tq_mbar_init(bar_m, 1);
         *s_fail = 0;
         tq_mbar_fence_init();
     }
@@ -493,18 +495,23 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
                 __syncwarp();
             };
 
-            if (elected()) {
-                tq_mbar_expect_tx(bar_b, 4 * MAT_BYTES);
-                const CUtensorMap* tb[4] = {&tm_b0, &tm_b1, &tm_b2, &tm_b3};
-#pragma unroll
-                for (int m = 0; m < 4; ++m) {
-                    tma_load_2d(sB + m * MAT_BYTES, tb[m], 0, 0, bar_b);
-                    tma_load_2d(sB + m * MAT_BYTES + BOX_BYTES, tb[m], 64, 0, bar_b);
-                }
-            }
-            __syncwarp();
+            // in the order they are needed: key rows (normalisation), Pi (Y and E products), value rows, M (P product)
             issue_kv(sX, &tm_k, &tm_kt, bar_k, tile0);
+            const CUtensorMap* tb[4] = {&tm_b0, &tm_b1, &tm_b2, &tm_b3};
+            auto load_pair = [&](int m0, uint64_t* bar) {
+                if (elected()) {
+                    tq_mbar_expect_tx(bar, 2 * MAT_BYTES);
+#pragma unroll
+                    for (int m = m0; m < m0 + 2; ++m) {
+                        tma_load_2d(sB + m * MAT_BYTES, tb[m], 0, 0, bar);
+                        tma_load_2d(sB + m * MAT_BYTES + BOX_BYTES, tb[m], 64, 0, bar);
+                    }
+                }
+                __syncwarp();
+            };
+            load_pair(0, bar_b);
             issue_kv(sV, &tm_v, &tm_vt, bar_v, tile0);
+            load_pair(2, bar_m);
             if (rmw) {   // the block this append continues, into block 0 of the first record image
                 pool_writes_may_begin();
                 if (elected()) {
@@ -541,6 +548,7 @@ tq_store_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
             };
             int i = 0;
             ok = ok && feed(0, tile0);
+            ok = ok && wait1(bar_m, 0);
 #pragma unroll 1
             for (int tile = tile0; tile < p.n_tiles && ok; tile += (int)gridDim.x, ++i) {
                 if (!(ok = wait1(bar_c, i & 1))) break;
@@ -1354,7 +1362,7 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
         return cudaLaunchKernelEx(&lc, tq_store_tc256_kernel<2, 2>, tm_k, tm_v, tm_kt, tm_vt, tm_b[0], tm_b[1], tm_b[2],
                                   tm_b[3], p) == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
     }
-    const size_t fixed = (size_t)6 * MAT_BYTES + 8 * TC_TOK * sizeof(float) + 11 * sizeof(uint64_t) + 16 + 1024;
+    const size_t fixed = (size_t)6 * MAT_BYTES + 8 * TC_TOK * sizeof(float) + 12 * sizeof(uint64_t) + 16 + 1024;
     p.n_rec_buf = fixed + 2 * img <= SMEM_LIMIT ? 2 : 1;
     const size_t smem = fixed + (size_t)p.n_rec_buf * img;
     cudaError_t launched = cudaSuccess;
