@@ -169,7 +169,15 @@ int tq_prefill_attention_read_status(int32_t* out);
  * base + t*stride_token + h*stride_head (in elements), D contiguous.
  * Destination of token t: slot_mapping[t] (= block*16 + offset, negative =
  * skip) when slot_mapping is given, else position start_pos+t of the
- * sequence whose blocks are block_table[0..]. */
+ * sequence whose blocks are block_table[0..].
+ * bf16 input with 16-byte aligned rows runs on the tensor cores (head_dim 128;
+ * head_dim 256 with 3-bit keys and 2-bit values); those kernels are launched
+ * as programmatic dependents: one that follows another store or
+ * tq_prefill_attention on the stream may fetch its key / value rows while
+ * that launch is still running, and touches the pool only after it has
+ * completed.  A store that follows one of the tq_decode* calls on the stream
+ * (whose ring append may still be writing rows the store is about to read)
+ * is launched in plain stream order.  Device-side status: tq_store_read_status. */
 int tq_store(const tq_consts* consts, const void* key, const void* value, tq_dtype dtype,
              int64_t n_tokens, int32_t n_heads, int64_t stride_token, int64_t stride_head,
              const int64_t* slot_mapping, const int32_t* block_table, int64_t start_pos,

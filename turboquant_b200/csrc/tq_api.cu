@@ -1,4 +1,6 @@
 // Host-only entry points: configuration checks, layout queries, messages.
+#include <mutex>
+
 #include "tq_common.cuh"
 
 int tq_check_config(const tq_config* cfg) {
@@ -25,6 +27,42 @@ int tq_sm_count() {
         sms[dev] = n;
     }
     return sms[dev];
+}
+
+namespace {
+struct StreamNote {
+    cudaStream_t st;
+    bool writes_rows;
+};
+std::mutex g_note_mu;
+StreamNote g_notes[TQ_MAX_DEVICES][8];
+int g_note_count[TQ_MAX_DEVICES], g_note_next[TQ_MAX_DEVICES];
+}  // namespace
+
+void tq_note_launch(cudaStream_t st, bool writes_caller_rows) {
+    const int dev = tq_current_device();
+    if (dev < 0 || dev >= TQ_MAX_DEVICES) return;
+    std::lock_guard<std::mutex> lock(g_note_mu);
+    for (int i = 0; i < g_note_count[dev]; ++i)
+        if (g_notes[dev][i].st == st) {
+            g_notes[dev][i].writes_rows = writes_caller_rows;
+            return;
+        }
+    const int slot = g_note_next[dev];
+    g_notes[dev][slot] = StreamNote{st, writes_caller_rows};
+    g_note_next[dev] = (slot + 1) % 8;
+    if (g_note_count[dev] < 8) ++g_note_count[dev];
+}
+
+// True unless the stream's latest library launch is known not to write caller rows (a stream that was never
+// noted, or whose note was displaced, counts as unknown: plain stream order).
+bool tq_rows_may_be_in_flight(cudaStream_t st) {
+    const int dev = tq_current_device();
+    if (dev < 0 || dev >= TQ_MAX_DEVICES) return true;
+    std::lock_guard<std::mutex> lock(g_note_mu);
+    for (int i = 0; i < g_note_count[dev]; ++i)
+        if (g_notes[dev][i].st == st) return g_notes[dev][i].writes_rows;
+    return true;
 }
 
 extern "C" int tq_get_layout(const tq_config* cfg, tq_layout* out) {

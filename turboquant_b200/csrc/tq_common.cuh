@@ -221,6 +221,15 @@ constexpr int TQ_MAX_DEVICES = 64;
 int tq_current_device();   // ordinal of the calling thread's current device, -1 on error
 int tq_sm_count();         // multiprocessors of the current device (148 when the query fails)
 
+// Which of the library's kernels was launched last on a stream.  The store kernels fetch their key / value
+// rows before they wait for the launch ahead of them (programmatic dependent launch); that is only safe when
+// the launches still in flight cannot be writing those rows.  The decode family is the one that can - it
+// appends the new token to the ring and lets its dependents begin at once - so a store that follows a decode
+// launch on the same stream is launched with plain stream order instead.  Kernels of other libraries between
+// two of ours never start early and only make the order stricter.
+void tq_note_launch(cudaStream_t st, bool writes_caller_rows);
+bool tq_rows_may_be_in_flight(cudaStream_t st);
+
 // Largest dynamic shared-memory size a kernel has been opted in for, per device.
 // A paged bf16 cache as the source of a store call (see tq_store_paged).
 struct TqPagedSource {

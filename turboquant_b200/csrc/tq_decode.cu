@@ -688,6 +688,7 @@ static int decode_impl(const tq_consts* consts, const tq_pool* pool, const tq_de
     if (!consts->pi_t || !consts->s_t) return TQ_ERR_NULL;
     int rc = tq_check_config(&consts->cfg);
     if (rc != TQ_OK) return rc;
+    if (!validate_only) tq_note_launch((cudaStream_t)stream, true);   // the ring append writes rows a later store may read
     const int D = consts->cfg.head_dim, H = pool->num_kv_heads;
     if (a->batch <= 0 || a->num_q_heads <= 0 || H <= 0 || a->max_seq_len < 0 || a->block_table_stride < 0)
         return TQ_ERR_SHAPE;

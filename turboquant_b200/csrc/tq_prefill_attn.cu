@@ -452,6 +452,7 @@ extern "C" int tq_prefill_attention(const void* query, const void* key, const vo
                         9 * sizeof(uint64_t) + 16 + 1024;
     const dim3 grid((unsigned)p.n_tiles, (unsigned)num_q_heads);
     cudaStream_t st = (cudaStream_t)stream;
+    tq_note_launch(st, false);   // plain stream order for this launch; it writes none of a later store's rows
     if (D == 128) {
         static TqSmemOptIn opt_in;
         if (tq_opt_in_smem(tq_prefill_attn_kernel<128>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;
