@@ -16,92 +16,99 @@ from .store import CompressedKVStore
 
 
 class RingBuffer:
-    """Fixed-capacity buffer of the most recent tokens, (capacity, H, D).
+    """The `capacity` most recent tokens, exact, as (capacity, H, D) key and value tensors.
 
-    Same contract as the reference: `write` returns everything that had to be
-    drained to make room (the whole buffer at once), else None.
+    Contract of the reference's ring (capture.py:21-131): tokens accumulate until the buffer is full;
+    the token that arrives next evicts the WHOLE buffer, and `write` hands back everything that was
+    evicted during the call (oldest first), or None.
     """
 
-    __slots__ = ("capacity", "num_kv_heads", "head_dim", "device", "dtype", "_k", "_v", "_pos", "_total_written",
-                 "_len_dev", "_len_dev_val")
-
     def __init__(self, capacity: int, num_kv_heads: int, head_dim: int, device, dtype: torch.dtype = torch.bfloat16):
+        if capacity < 1:
+            raise ValueError("the ring needs room for at least one token")
         self.capacity, self.num_kv_heads, self.head_dim = capacity, num_kv_heads, head_dim
         self.device, self.dtype = device, dtype
-        self._k = torch.zeros(capacity, num_kv_heads, head_dim, device=device, dtype=dtype)
-        self._v = torch.zeros(capacity, num_kv_heads, head_dim, device=device, dtype=dtype)
-        self._pos = 0
-        self._total_written = 0
-        self._len_dev: Optional[torch.Tensor] = None      # device copy of _pos, kept by device_len()
-        self._len_dev_val = -1
+        self._keys = torch.zeros(capacity, num_kv_heads, head_dim, device=device, dtype=dtype)
+        self._values = torch.zeros_like(self._keys)
+        self._fill = 0                                     # tokens held
+        self._seen = 0                                     # tokens ever written
+        self._fill_dev: Optional[torch.Tensor] = None      # device mirror of _fill, kept by device_len()
+        self._fill_dev_val = -1
 
     def device_len(self) -> torch.Tensor:
-        """(1,) int32 device tensor equal to `size`.  The fused decode step lets
-        the kernel write the new token at this position and increment it; the
-        host mirror is advanced by `advance_after_device_append`."""
-        if self._len_dev is None:
-            self._len_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
-            self._len_dev_val = 0
-        if self._len_dev_val != self._pos:
-            self._len_dev.fill_(self._pos)
-            self._len_dev_val = self._pos
-        return self._len_dev
+        """(1,) int32 device tensor equal to `size`.  The fused decode step lets the kernel write the new
+        token at this position and increment it; the host count follows in `advance_after_device_append`."""
+        if self._fill_dev is None:
+            self._fill_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self._fill_dev_val = 0
+        if self._fill_dev_val != self._fill:
+            self._fill_dev.fill_(self._fill)
+            self._fill_dev_val = self._fill
+        return self._fill_dev
 
     def advance_after_device_append(self) -> None:
-        self._pos += 1
-        self._len_dev_val += 1
-        self._total_written += 1
+        self._fill += 1
+        self._fill_dev_val += 1
+        self._seen += 1
 
     @property
     def storage(self):
         """The whole (capacity, H, D) key and value buffers."""
-        return self._k, self._v
+        return self._keys, self._values
 
     @property
     def size(self) -> int:
-        return self._pos
+        return self._fill
 
     @property
     def is_full(self) -> bool:
-        return self._pos >= self.capacity
+        return self._fill >= self.capacity
 
     @property
     def total_written(self) -> int:
-        return self._total_written
+        return self._seen
 
     def write(self, key: torch.Tensor, value: torch.Tensor, num_tokens: int):
-        drained_k, drained_v = [], []
-        done = 0
-        while done < num_tokens:
-            if self._pos >= self.capacity:
-                drained_k.append(self._k[: self._pos].clone())
-                drained_v.append(self._v[: self._pos].clone())
-                self._pos = 0
-            n = min(num_tokens - done, self.capacity - self._pos)
-            self._k[self._pos: self._pos + n] = key[done: done + n]
-            self._v[self._pos: self._pos + n] = value[done: done + n]
-            self._pos += n
-            done += n
-        self._total_written += num_tokens
-        if drained_k:
-            return torch.cat(drained_k, 0), torch.cat(drained_v, 0)
-        return None
+        """Append `num_tokens` tokens.  Seen as one stream - the tokens held, then the new ones - every
+        full buffer's worth that is followed by at least one more token leaves; what stays is the tail of
+        1..capacity tokens.  No loop over buffers: the split point is arithmetic."""
+        held, cap = self._fill, self.capacity
+        total = held + num_tokens
+        self._seen += num_tokens
+        if num_tokens <= 0:
+            return None
+        evicted_buffers = (total - 1) // cap               # full buffers with a successor
+        cut = evicted_buffers * cap - held                 # new tokens that leave with them
+        if evicted_buffers == 0:
+            self._keys[held:total] = key[:num_tokens]
+            self._values[held:total] = value[:num_tokens]
+            self._fill = total
+            return None
+        out_k = torch.cat((self._keys[:held], key[:cut]), 0)
+        out_v = torch.cat((self._values[:held], value[:cut]), 0)
+        stay = num_tokens - cut
+        self._keys[:stay] = key[cut:num_tokens]
+        self._values[:stay] = value[cut:num_tokens]
+        self._fill = stay
+        return out_k, out_v
 
     def drain(self):
-        if self._pos == 0:
+        """Everything held, as copies; the ring is empty afterwards."""
+        if self._fill == 0:
             return None
-        k, v = self._k[: self._pos].clone(), self._v[: self._pos].clone()
-        self._pos = 0
-        return k, v
+        taken = self._keys[: self._fill].clone(), self._values[: self._fill].clone()
+        self._fill = 0
+        return taken
 
     def peek(self):
-        if self._pos == 0:
+        """Views of what is held (None when empty)."""
+        if self._fill == 0:
             return None
-        return self._k[: self._pos], self._v[: self._pos]
+        return self._keys[: self._fill], self._values[: self._fill]
 
     def reset(self) -> None:
-        self._pos = 0
-        self._total_written = 0
+        self._fill = 0
+        self._seen = 0
 
 
 class KVCaptureEngine:
