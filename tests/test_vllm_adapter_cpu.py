@@ -96,3 +96,17 @@ def test_free_kv_cache_swaps_hooked_layers_only():
     assert freed == 2 * big[0].numel() * 2
     assert ctx["layers.0.attn"].kv_cache[0].numel() == 1 and ctx["layers.mla"].kv_cache[0] is big[2]
     assert r.kv_caches[0].numel() == 1 and r.kv_caches[1][0].numel() == 1 and r.kv_caches[2] is big[2]
+
+
+def test_compressed_cache_specs_follow_the_layer_configuration():
+    """The engine-facing page specs: one per hooked flash layer, with that layer's bit widths (the first
+    layers keep one more key bit), none for MLA layers; a page of 16 tokens x 2 kv heads."""
+    r = _runner(6)
+    adapter.install_hooks(r, key_bits=3, value_bits=2, mode=adapter.MODE_OFF)
+    specs = adapter.compressed_cache_specs(r)
+    assert sorted(specs) == [f"layers.{i}.attn" for i in range(6)]
+    assert [specs[f"layers.{i}.attn"].key_bits for i in range(6)] == [4, 4, 4, 4, 3, 3]
+    s = specs["layers.5.attn"]
+    assert (s.head_dim, s.num_kv_heads, s.page_size_bytes) == (128, 2, 16 * 2 * 100)
+    assert specs["layers.0.attn"].page_size_bytes == 16 * 2 * 132      # 4-bit keys: 3-bit codes in nibbles, 32 bytes more per token
+    assert adapter.compressed_cache_specs(types.SimpleNamespace()) == {}

@@ -296,6 +296,17 @@ def free_kv_cache(model_runner) -> int:
     return freed
 
 
+def compressed_cache_specs(model_runner) -> dict:
+    """Page geometry per hooked attention layer, for an engine that allocates its KV block pool at COMPRESSED
+    size instead of allocating bf16 pages first and dropping them with `free_kv_cache` (reference
+    vllm.py:452-501).  {layer name: CompressedCacheSpec}; MLA layers, which the hooks leave alone, are absent.
+    The engine sizes its pool with `spec.page_size_bytes`, hands each layer's buffer to
+    `CompressedPagedKVCache(spec, raw, layer_idx)` and then writes with its slot mappings and reads with its
+    block tables."""
+    from ..paged_cache import kv_cache_specs
+    return kv_cache_specs(getattr(model_runner, "_tq_layer_states", None) or {})
+
+
 def get_stats(model_runner) -> dict:
     states = getattr(model_runner, "_tq_layer_states", None)
     if not states:
