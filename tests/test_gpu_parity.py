@@ -941,6 +941,22 @@ def test_paged_cache_to_compressed_store(d, kb, vb, bs, n, hnd, dev):
     assert _bit_frac(pa.qjl_signs.cpu(), torch.from_numpy(of.qjl_signs)) <= TIE_BUDGET
     assert torch.equal(pa.v_data.cpu(), torch.from_numpy(of.v_data))
 
+    # appended behind tokens the store already holds (a block boundary: the table-walking launch; mid-block: gathered)
+    for held in (160, 37):
+        k0, v0 = O.synth_kv(held, h, d, seed=900 + held, dtype=torch.bfloat16)
+        pair = []
+        for paged in (True, False):
+            st = CompressedKVStore(d, h, kb, vb, device=dev, capacity_tokens=held + n)
+            st.append_chunk(k0.to(dev), v0.to(dev))
+            if paged:
+                st.append_from_paged(cache_d[0], cache_d[1], table_d, n)
+            else:
+                st.append_chunk(k.to(dev), v.to(dev))
+            pair.append(st)
+        nb2 = E.blocks_for(held + n) * h * pair[0].consts.block_bytes
+        assert pair[0].num_tokens == held + n and torch.equal(pair[0].pool.data[:nb2], pair[1].pool.data[:nb2])
+    assert E.store_status() == 0
+
     # the engine's prefill entry: all but the ring's tokens compressed, the last ones exact in the ring
     cap = 48
     e1 = KVCaptureEngine(CompressedKVStore(d, h, kb, vb, device=dev, capacity_tokens=n), ring_capacity=cap, device=dev)
