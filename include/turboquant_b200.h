@@ -86,6 +86,10 @@ typedef struct tq_consts {
      * split into two.  With any of them NULL the store runs its fp32 kernel. */
     const void* pi_limbs[3];
     const void* m_limbs[2];
+    /* Optional operands of the tensor-core query preparation (large decode
+     * batches at head_dim 128): S split into two bf16 limbs, (D,D) row-major.
+     * With either NULL (or pi_limbs missing) the fp32 kernels prepare the queries. */
+    const void* s_limbs[2];
 } tq_consts;
 
 /* Byte offsets inside one block record. */

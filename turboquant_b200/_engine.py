@@ -90,6 +90,8 @@ class LayerConstants:
         m = s.double() @ pi.double().T
         self.pi_limbs = [t.contiguous().to(dev) for t in _split_bf16(pi.double(), 3)]
         self.m_limbs = [t.contiguous().to(dev) for t in _split_bf16(m, 2)]
+        # and of the tensor-core query preparation: S as two bf16 limbs (Pi's first two serve there too)
+        self.s_limbs = [t.contiguous().to(dev) for t in _split_bf16(s.double(), 2)]
 
         c = _lib.tq_consts()
         c.cfg = self.cfg
@@ -107,6 +109,7 @@ class LayerConstants:
             c.pi_limbs[i] = self.pi_limbs[i].data_ptr() if tensor_core_store else None
         for i in range(2):
             c.m_limbs[i] = self.m_limbs[i].data_ptr() if tensor_core_store else None
+            c.s_limbs[i] = self.s_limbs[i].data_ptr() if tensor_core_store else None
         self.c = c
 
     @property

@@ -32,7 +32,7 @@ class tq_consts(C.Structure):
     _fields_ = [("cfg", tq_config), ("pi", C.c_void_p), ("pi_t", C.c_void_p), ("s", C.c_void_p),
                 ("s_t", C.c_void_p), ("centroids", C.c_float * TQ_MAX_CENTROIDS),
                 ("boundaries", C.c_float * TQ_MAX_CENTROIDS), ("qjl_scale", C.c_float),
-                ("pi_limbs", C.c_void_p * 3), ("m_limbs", C.c_void_p * 2)]
+                ("pi_limbs", C.c_void_p * 3), ("m_limbs", C.c_void_p * 2), ("s_limbs", C.c_void_p * 2)]
 
 
 class tq_layout(C.Structure):

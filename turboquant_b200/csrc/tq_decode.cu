@@ -751,7 +751,13 @@ static int decode_impl(const tq_consts* consts, const tq_pool* pool, const tq_de
     if (validate_only) return TQ_OK;   // every host-side check has passed; nothing was enqueued
     if (!a->query_prepared) {
         const int64_t nvec = (int64_t)a->batch * a->num_q_heads;
-        if (launch_qprep(a->query, a->q_dtype, nvec, D, consts->pi_t, consts->s_t, qprep, qfrag, G, a->num_q_heads,
+        int on_tensor_cores = 0;
+        if (ap.new_k == nullptr && !early_inputs &&
+            tq_qprep_tc_launch(consts, a->query, a->q_dtype, nvec, qprep, qfrag, G, a->num_q_heads,
+                               consts->cfg.key_bits - 1, (int*)ws, st, &on_tensor_cores) != TQ_OK)
+            return TQ_ERR_CUDA;
+        if (!on_tensor_cores &&
+            launch_qprep(a->query, a->q_dtype, nvec, D, consts->pi_t, consts->s_t, qprep, qfrag, G, a->num_q_heads,
                          consts->cfg.key_bits - 1, ap, st) != TQ_OK)
             return TQ_ERR_CUDA;
     }

@@ -430,3 +430,7 @@ int tq_decode_mma_launch(const DecodeParams& p, int D, int mse_bits, int val_bit
                          cudaStream_t st, int* handled);
 
 }  // namespace tqdec
+
+// Tensor-core query preparation (tq_qprep_tc.cu): *handled = 0 when the call does not fit it.
+int tq_qprep_tc_launch(const tq_consts* consts, const void* q, int dt, int64_t nvec, float* out, uint32_t* frag, int G,
+                       int Qh, int mse_bits, int* status, cudaStream_t st, int* handled);
