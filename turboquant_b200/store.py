@@ -46,6 +46,7 @@ class CompressedKVStore:
         self._num_tokens = 0
         self._num_chunks = 0
         self._seq_len_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self._seq_len_dev_val = 0          # what the device copy holds; brought up to date when it is asked for
         self._flat: Optional[FlatCache] = None
 
     @property
@@ -58,7 +59,12 @@ class CompressedKVStore:
 
     @property
     def seq_len_device(self) -> torch.Tensor:
-        """(1,) int32 device tensor holding num_tokens (what the decode kernel reads)."""
+        """(1,) int32 device tensor holding num_tokens (what the decode kernel reads).  The device copy is
+        refreshed HERE, not by every append (a fill between two store launches would keep the second from
+        starting under the first): ask for it after the last append, on the stream the decode will use."""
+        if self._seq_len_dev_val != self._num_tokens:
+            self._seq_len_dev.fill_(self._num_tokens)
+            self._seq_len_dev_val = self._num_tokens
         return self._seq_len_dev
 
     def reserve(self, n_tokens: int) -> None:
@@ -83,7 +89,6 @@ class CompressedKVStore:
                 n_tokens=t, n_heads=self.num_kv_heads, block_table=self.block_table, start_pos=self._num_tokens)
         self._num_tokens += t
         self._num_chunks += 1
-        self._seq_len_dev.fill_(self._num_tokens)
         self._flat = None
 
     def append_from_paged(self, key_cache: torch.Tensor, value_cache: torch.Tensor, src_block_table: torch.Tensor,
@@ -107,7 +112,6 @@ class CompressedKVStore:
             return self.append_chunk(k, v)
         self._num_tokens += num_tokens
         self._num_chunks += 1
-        self._seq_len_dev.fill_(self._num_tokens)
         self._flat = None
 
     def get_flat_cache(self) -> Optional[FlatCache]:
@@ -130,4 +134,5 @@ class CompressedKVStore:
         self._num_tokens = 0
         self._num_chunks = 0
         self._seq_len_dev.zero_()
+        self._seq_len_dev_val = 0
         self._flat = None
