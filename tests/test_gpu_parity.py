@@ -1098,3 +1098,36 @@ def test_engine_allocated_compressed_paged_cache(d, h, qh, kb, vb, dev):
         b = E.pool_to_planes(refs[i].consts, refs[i].pool, refs[i].block_table, lens[i])
         for f_ in ("mse_indices", "qjl_signs", "norms", "residual_norms", "v_data", "v_scales", "v_zeros"):
             assert torch.equal(getattr(a, f_), getattr(b, f_)), (i, f_)
+
+
+@pytest.mark.parametrize("d,h,qh,kb,vb,nseq,dtype", [(128, 8, 32, 3, 2, 37, torch.bfloat16), (128, 4, 32, 4, 4, 33, torch.bfloat16),
+                                                     (128, 8, 32, 3, 2, 129, torch.float16), (256, 4, 16, 3, 2, 258, torch.bfloat16)])
+def test_large_batch_query_preparation_matches_small_batch(d, h, qh, kb, vb, nseq, dtype, dev):
+    """Large batches of query vectors are prepared by other kernels than small ones (tcgen05 from 1024 bf16
+    vectors at head_dim 128, tiled fp32 from 4096 vectors otherwise): one batched decode of nseq sequences - a vector count that is not a
+    multiple of the kernels' tiles - against the same sequences decoded one by one."""
+    from turboquant_b200 import _engine as E
+    n = 200
+    c = E.LayerConstants(d, kb, vb, dev, seed=42)
+    nblk = E.blocks_for(n)
+    pool = E.BlockPool(c, h, nseq * nblk)
+    bt = torch.arange(nseq * nblk, dtype=torch.int32, device=dev).view(nseq, nblk)
+    g = torch.Generator(device=dev)
+    g.manual_seed(77)
+    lens_l = [int(x) for x in torch.randint(17, n + 1, (nseq,), generator=torch.Generator().manual_seed(5))]
+    for s_ in range(nseq):
+        k = torch.randn(n, h, d, generator=g, device=dev).to(torch.bfloat16)
+        v = torch.randn(n, h, d, generator=g, device=dev).to(torch.bfloat16)
+        E.store(c, pool, k, v, stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h, block_table=bt[s_], start_pos=0)
+    assert nseq * qh >= 1024 and (nseq * qh) % 128 != 0
+    q = (torch.randn(nseq, qh, d, generator=g, device=dev) * 1.3).to(dtype)
+    lens = torch.tensor(lens_l, dtype=torch.int32, device=dev)
+    ws = E.Workspace(dev)
+    out = E.decode(c, pool, ws, q, bt, lens, n, min_history=1)
+    assert ws.status() == 0
+    ws1 = E.Workspace(dev)
+    for s_ in (0, 1, nseq // 2, nseq - 1):
+        one = E.decode(c, pool, ws1, q[s_:s_ + 1], bt[s_:s_ + 1], lens[s_:s_ + 1], lens_l[s_], min_history=1)
+        assert _cos(out[s_:s_ + 1], one) >= 0.99999
+        torch.testing.assert_close(out[s_:s_ + 1].float(), one.float(), rtol=2e-2, atol=2e-3)
+    assert ws1.status() == 0
