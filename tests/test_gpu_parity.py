@@ -1101,6 +1101,7 @@ def test_engine_allocated_compressed_paged_cache(d, h, qh, kb, vb, dev):
 
 
 @pytest.mark.parametrize("d,h,qh,kb,vb,nseq,dtype", [(128, 8, 32, 3, 2, 37, torch.bfloat16), (128, 4, 32, 4, 4, 33, torch.bfloat16),
+                                                     (128, 4, 16, 3, 2, 65, torch.bfloat16),
                                                      (128, 8, 32, 3, 2, 129, torch.float16), (256, 4, 16, 3, 2, 258, torch.bfloat16)])
 def test_large_batch_query_preparation_matches_small_batch(d, h, qh, kb, vb, nseq, dtype, dev):
     """Large batches of query vectors are prepared by other kernels than small ones (tcgen05 from 1024 bf16
@@ -1119,7 +1120,7 @@ def test_large_batch_query_preparation_matches_small_batch(d, h, qh, kb, vb, nse
         k = torch.randn(n, h, d, generator=g, device=dev).to(torch.bfloat16)
         v = torch.randn(n, h, d, generator=g, device=dev).to(torch.bfloat16)
         E.store(c, pool, k, v, stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h, block_table=bt[s_], start_pos=0)
-    assert nseq * qh >= 1024 and (nseq * qh) % 128 != 0
+    assert nseq * qh >= 1024 and (nseq * qh) % 128 != 0      # 65 x 16: the last tile ends inside a warp
     q = (torch.randn(nseq, qh, d, generator=g, device=dev) * 1.3).to(dtype)
     lens = torch.tensor(lens_l, dtype=torch.int32, device=dev)
     ws = E.Workspace(dev)

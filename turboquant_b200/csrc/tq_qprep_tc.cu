@@ -40,7 +40,8 @@ tq_qprep_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     uint8_t* smem = smem_raw + ((1024u - (tq_smem_u32(smem_raw) & 1023u)) & 1023u);
     uint8_t* sQ = smem;                           // 2 boxes
     uint8_t* sB = sQ + 2 * QT_BOX;                // [2 limbs][2 channel boxes][256 rows]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + 4 * QT_BBOX);
+    float* s_tr = reinterpret_cast<float*>(sB + 4 * QT_BBOX);   // [8 warps][32][33] transposition buffers
+    uint64_t* bars = reinterpret_cast<uint64_t*>(s_tr + 8 * 32 * 33);
     uint64_t *bar_q = bars, *bar_b = bars + 1, *bar_d = bars + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3);
     volatile int* s_fail = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -146,37 +147,56 @@ tq_qprep_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
         ok = wait_warp(bar_d) && ok;
         tc_fence_after();
         const int64_t vec = v0 + row;
-        if (ok && vec < p.nvec) {
-            float* orow = p.out + (vec * 2 + which) * QT_D;
-            const int qh = (int)(vec % p.Qh), g = qh % p.G;
-            const int64_t pair = (vec / p.Qh) * (p.Qh / p.G) + qh / p.G;     // (sequence, kv head)
-            const bool split = p.G > 4 || p.mse_bits == 3;                   // separate rotated / sketched fragment sets
-            uint32_t* base = p.frag ? p.frag + pair * qf_words(QT_D, split ? 8 : 4) : nullptr;
-            const float bound = sqrtf(qn2) * (which ? 2.f * sqrtf((float)QT_D) : 1.f);
-            int e = 0;
-            if (bound > 0.f && bound < 3.0e38f) e = max(-100, min(100, 14 - ilogbf(bound)));
-            if (base) reinterpret_cast<float*>(base)[which * 8 + g] = (float)e;
-            const bool nibble = p.mse_bits == 3 && which == 0;
-            const int gid = split ? g : g + 4 * which;
-            const int set = split ? which : 0;
-            // a chunk of 32 columns is one quarter of the head dimension: fragment index tig
-#pragma unroll 1
-            for (int tig = 0; tig < 4; ++tig) {
-                float v[32];
-                tmem_ld32(tmem + lane_base + which * QT_D + tig * 32, v);
+        const bool live = vec < p.nvec;          // tensor-memory loads are warp-wide: only the stores are guarded
+        if (ok) {
+            // all 128 columns of this thread's half row; a chunk of 32 is one quarter of the head dimension
+            // (fragment index tig)
+            float v[4][32];
 #pragma unroll
-                for (int i = 0; i < 8; ++i)
-                    reinterpret_cast<float4*>(orow + tig * 32)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-                if (base == nullptr) continue;
+            for (int tig = 0; tig < 4; ++tig) tmem_ld32(tmem + lane_base + which * QT_D + tig * 32, v[tig]);
+            if (live && p.frag != nullptr) {
+                const int qh = (int)(vec % p.Qh), g = qh % p.G;
+                const int64_t pair = (vec / p.Qh) * (p.Qh / p.G) + qh / p.G;     // (sequence, kv head)
+                const bool split = p.G > 4 || p.mse_bits == 3;                   // separate rotated / sketched fragment sets
+                uint32_t* base = p.frag + pair * qf_words(QT_D, split ? 8 : 4);
+                const float bound = sqrtf(qn2) * (which ? 2.f * sqrtf((float)QT_D) : 1.f);
+                int e = 0;
+                if (bound > 0.f && bound < 3.0e38f) e = max(-100, min(100, 14 - ilogbf(bound)));
+                reinterpret_cast<float*>(base)[which * 8 + g] = (float)e;
+                const bool nibble = p.mse_bits == 3 && which == 0;
+                const int gid = split ? g : g + 4 * which;
+                const int set = split ? which : 0;
+                // one 16-byte store per fragment row: the four quarters' words of this (vector, position) are
+                // adjacent, and the eight query heads of a kv head fill the 128-byte row
 #pragma unroll
                 for (int r = 0; r < 16; ++r) {   // element layout as in tq_qprep_kernel
                     const int wi = r >> 3, jf = r & 7;
                     const int c0 = nibble ? 2 * r : wi * 16 + jf, c1 = nibble ? 2 * r + 1 : wi * 16 + 8 + jf;
                     const int sh = nibble ? 0 : (which ? sign_pos(sign_bit(wi, jf)) : 2 * code_pos(jf));
                     const float scale = __int_as_float((127 + e - sh) << 23);
-                    const __half2 h2 = __floats2half2_rn(v[c0] * scale, v[c1] * scale);
-                    base[QF_HDR + (set * (QT_D / 8) + r) * 32 + gid * 4 + tig] = *reinterpret_cast<const uint32_t*>(&h2);
+                    uint32_t w[4];
+#pragma unroll
+                    for (int tig = 0; tig < 4; ++tig) {
+                        const __half2 h2 = __floats2half2_rn(v[tig][c0] * scale, v[tig][c1] * scale);
+                        w[tig] = *reinterpret_cast<const uint32_t*>(&h2);
+                    }
+                    *reinterpret_cast<uint4*>(base + QF_HDR + (set * (QT_D / 8) + r) * 32 + gid * 4) =
+                        make_uint4(w[0], w[1], w[2], w[3]);
                 }
+            }
+            // fp32 results: transposed through shared memory, a warp's 32 rows one after the other, so that
+            // every store instruction writes 128 consecutive bytes of one row (rows past the end are skipped)
+            float* tbuf = s_tr + warp * (32 * 33);
+            const int64_t row0 = v0 + (row & ~31);
+#pragma unroll
+            for (int tig = 0; tig < 4; ++tig) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) tbuf[lane * 33 + i] = v[tig][i];
+                __syncwarp();
+#pragma unroll 4
+                for (int r = 0; r < 32; ++r)
+                    if (row0 + r < p.nvec) p.out[((row0 + r) * 2 + which) * QT_D + tig * 32 + lane] = tbuf[r * 33 + lane];
+                __syncwarp();
             }
         }
         if (!ok && lane == 0) atomicCAS(p.status, 0, (int)TQ_ERR_TIMEOUT);
@@ -237,7 +257,7 @@ int tq_qprep_tc_launch(const tq_consts* consts, const void* q, int dt, int64_t n
     p.Qh = Qh;
     p.mse_bits = mse_bits;
     p.status = status;
-    const size_t smem = 2 * (size_t)QT_BOX + 4 * (size_t)QT_BBOX + 3 * sizeof(uint64_t) + 16 + 1024;
+    const size_t smem = 2 * (size_t)QT_BOX + 4 * (size_t)QT_BBOX + 8 * 32 * 33 * sizeof(float) + 3 * sizeof(uint64_t) + 16 + 1024;
     static TqSmemOptIn opt_in;
     if (tq_opt_in_smem(tq_qprep_tc_kernel, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;
     cudaLaunchConfig_t cfg = {};
