@@ -29,13 +29,19 @@ namespace {
 
 constexpr int PA_TOK = 128;                   // query rows and key rows per tile
 constexpr int PA_BOX = PA_TOK * 128;          // one swizzled box: 128 rows x 64 channels of 16 bits
-constexpr int PA_TPR = 4;                     // compute threads per query row
+// Kernel variants.
+//   AHEAD (head_dim 128): two S and two P buffers, two key/value stages: Q K^T of tile t+1 runs under the softmax
+//         of tile t.
+//   WIDE  (head_dim 256): O takes 256 tensor-memory columns, leaving one S and one P buffer; one key/value stage,
+//         the key tile refilled as soon as S has been computed, the value tile once P V has completed.
+// (Two CTAs per SM with P written over S - 256 columns and 97 KB each, serial chains covering one another - were
+// measured at head_dim 128: 8 % slower than AHEAD.)
+enum PaVariant { PA_AHEAD = 1, PA_WIDE = 2 };
+template <int V> struct PaCols;
+template <> struct PaCols<PA_AHEAD> { static constexpr uint32_t S = 0, S_STEP = 128, P = 256, P_STEP = 64, O = 384; };
+template <> struct PaCols<PA_WIDE> { static constexpr uint32_t S = 0, S_STEP = 0, P = 128, P_STEP = 0, O = 256; };
+constexpr int PA_TPR = 4;                          // compute threads per query row
 constexpr int PA_THREADS = PA_TOK * PA_TPR + 32;   // plus the issuing warp
-// tensor-memory columns.  head_dim 128: two S buffers and two P buffers, so that Q K^T of the next tile
-// runs under the softmax of this one; head_dim 256 (O takes 256 columns): one of each.
-template <int D> struct PaCols;
-template <> struct PaCols<128> { static constexpr uint32_t S = 0, S_STEP = 128, P = 256, P_STEP = 64, O = 384; };
-template <> struct PaCols<256> { static constexpr uint32_t S = 0, S_STEP = 0, P = 128, P_STEP = 0, O = 256; };
 constexpr float PA_RESCALE_STEP = 8.f;        // log2 of the factor the running maximum may lag behind
 
 struct PrefillParams {
@@ -69,18 +75,19 @@ __device__ __forceinline__ uint32_t pa_pack(float lo, float hi, bool bf16) {
     return *reinterpret_cast<const uint32_t*>(&h);
 }
 
-template <int D>
+template <int D, int VAR>
 __global__ void __launch_bounds__(PA_THREADS, 1)
 tq_prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const PrefillParams p) {
-    constexpr int TPR = PA_TPR;               // threads per query row
+    constexpr int TPR = PA_TPR;                   // compute threads per query row
     constexpr int OC = D / TPR;               // accumulator columns per thread
     constexpr int NCOMP = PA_TOK * TPR;       // compute threads
     constexpr int SC = PA_TOK / TPR;          // columns of S per thread
     constexpr int NBOX = D / 64;              // boxes per tile
-    constexpr int NST = D == 128 ? 2 : 1;     // key/value stages
-    constexpr bool AHEAD = D == 128;          // S of tile t+1 is issued before P V of tile t
-    using Col = PaCols<D>;
+    constexpr int NST = VAR == PA_AHEAD ? 2 : 1;  // key/value stages
+    constexpr bool AHEAD = VAR == PA_AHEAD;       // S of tile t+1 is issued before P V of tile t
+    using Col = PaCols<VAR>;
+    static_assert((VAR == PA_WIDE) == (D == 256), "head_dim 256 runs the wide variant, head_dim 128 the other");
     constexpr int TILE_BYTES = NBOX * PA_BOX;
 
     extern __shared__ uint8_t smem_raw[];
@@ -211,14 +218,19 @@ tq_prefill_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                 }
             }
         } else {
+            // one S buffer: S_t, P_t V_t, S_{t+1} ... in tile order.  The key stage is refilled as soon as S_t has
+            // been computed, the value stage once P_t V_t has completed; both loads run under the softmax.
 #pragma unroll 1
             for (int t = 0; t < n_kv_tiles && ok; ++t) {
-                if (!(ok = issue_s(t))) break;          // the threads passed bar_p of the tile before: S is free
+                if (!(ok = issue_s(t))) break;          // P_{t-1} V_{t-1} has completed: S (and P over it) is free
+                if (t + 1 < n_kv_tiles) {
+                    if (!(ok = wait1(bar_s, (uint32_t)t & 1u))) break;
+                    load_tile(sK, &tm_k, bar_k, (t + 1) * PA_TOK, kvh);
+                }
                 if (!(ok = wait1(bar_p, (uint32_t)t & 1u))) break;
                 if (!(ok = issue_pv(t))) break;
                 if (t + 1 < n_kv_tiles) {
                     if (!(ok = wait1(bar_o, (uint32_t)t & 1u))) break;
-                    load_tile(sK, &tm_k, bar_k, (t + 1) * PA_TOK, kvh);
                     load_tile(sV, &tm_v, bar_v, (t + 1) * PA_TOK, kvh);
                 }
             }
@@ -447,20 +459,23 @@ extern "C" int tq_prefill_attention(const void* query, const void* key, const vo
     p.out = out;
     p.out_stride_token = out_stride_token;
     p.out_stride_head = out_stride_head;
-    const int nbox = D / 64, nst = D == 128 ? 2 : 1;
-    const size_t smem = (size_t)(1 + 2 * nst) * nbox * PA_BOX + (size_t)2 * PA_TPR * PA_TOK * sizeof(float) +
-                        9 * sizeof(uint64_t) + 16 + 1024;
     const dim3 grid((unsigned)p.n_tiles, (unsigned)num_q_heads);
     cudaStream_t st = (cudaStream_t)stream;
     tq_note_launch(st, false);   // plain stream order for this launch; it writes none of a later store's rows
+    auto smem_of = [&](int nst, int tpr) {
+        return (size_t)(1 + 2 * nst) * (D / 64) * PA_BOX + (size_t)2 * tpr * PA_TOK * sizeof(float) + 11 * sizeof(uint64_t) +
+               16 + 1024;
+    };
     if (D == 128) {
+        const size_t smem = smem_of(2, PA_TPR);
         static TqSmemOptIn opt_in;
-        if (tq_opt_in_smem(tq_prefill_attn_kernel<128>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;
-        tq_prefill_attn_kernel<128><<<grid, PA_THREADS, smem, st>>>(tm_q, tm_k, tm_v, p);
+        if (tq_opt_in_smem(tq_prefill_attn_kernel<128, PA_AHEAD>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;
+        tq_prefill_attn_kernel<128, PA_AHEAD><<<grid, PA_THREADS, smem, st>>>(tm_q, tm_k, tm_v, p);
     } else {
+        const size_t smem = smem_of(1, PA_TPR);
         static TqSmemOptIn opt_in;
-        if (tq_opt_in_smem(tq_prefill_attn_kernel<256>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;
-        tq_prefill_attn_kernel<256><<<grid, PA_THREADS, smem, st>>>(tm_q, tm_k, tm_v, p);
+        if (tq_opt_in_smem(tq_prefill_attn_kernel<256, PA_WIDE>, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;
+        tq_prefill_attn_kernel<256, PA_WIDE><<<grid, PA_THREADS, smem, st>>>(tm_q, tm_k, tm_v, p);
     }
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
