@@ -160,8 +160,9 @@ int tq_prefill_attention(const void* query, const void* key, const void* value, 
                          int64_t kv_stride_head, int64_t out_stride_token, int64_t out_stride_head,
                          float scale, void* stream);
 
-/* Status left by the prefill attention kernel (0, or TQ_ERR_TIMEOUT if one
- * of its bounded device-side waits ran out).  Synchronises the device. */
+/* Status left by the prefill attention kernel since the last call (0, or
+ * TQ_ERR_TIMEOUT if one of its bounded device-side waits ran out); reading
+ * clears it.  Synchronises the device. */
 int tq_prefill_attention_read_status(int32_t* out);
 
 /* ---- store path ---------------------------------------------------------- */
@@ -207,9 +208,11 @@ int tq_store_paged(const tq_consts* consts, const void* key_cache, const void* v
                    int64_t stride_token, int64_t stride_head, const int32_t* src_block_table, int64_t n_tokens,
                    const int32_t* block_table, int64_t start_pos, const tq_pool* pool, void* stream);
 
-/* Status word of the tensor-core store kernel: 0, or TQ_ERR_TIMEOUT / TQ_ERR_RANGE
- * if one of its bounded waits ran out or a block index was out of range.
- * Synchronises the device. */
+/* Status left by the tensor-core store kernels since the last call: 0, or
+ * TQ_ERR_TIMEOUT / TQ_ERR_RANGE if one of their bounded waits ran out or a
+ * block index (destination or paged source) was out of range - such a
+ * record is skipped, nothing outside the pool is touched.  Reading clears
+ * the word.  Synchronises the device. */
 int tq_store_read_status(int32_t* out);
 
 /* ---- read path ------------------------------------------------------------ */

@@ -1132,3 +1132,46 @@ def test_large_batch_query_preparation_matches_small_batch(d, h, qh, kb, vb, nse
         assert _cos(out[s_:s_ + 1], one) >= 0.99999
         torch.testing.assert_close(out[s_:s_ + 1].float(), one.float(), rtol=2e-2, atol=2e-3)
     assert ws1.status() == 0
+
+
+@pytest.mark.parametrize("d", [128, 256])
+def test_tensor_core_store_reports_bad_block_indices(d, dev):
+    """Block indices are checked on the device: a destination block past the pool, a negative one, and a paged
+    source block past the cache are skipped (or read as zeros) and leave TQ_ERR_RANGE in the store's status
+    word - which reading clears -, the records of the valid blocks are written as usual."""
+    from turboquant_b200 import _engine as E
+    h, n = 2, 256
+    c = E.LayerConstants(d, 3, 2, dev, seed=42)
+    k, v = O.synth_kv(n, h, d, seed=31, dtype=torch.bfloat16)
+    kd, vd = k.to(dev), v.to(dev)
+    nb = E.blocks_for(n)
+    good = E.BlockPool(c, h, nb)
+    ident = E.identity_block_table(nb, dev)
+    E.store(c, good, kd, vd, stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h, block_table=ident, start_pos=0)
+    assert E.store_status() == 0
+    per_block = h * c.block_bytes
+    for bad_value in (nb + 3, -1):
+        pool = E.BlockPool(c, h, nb)
+        guard = pool.data.clone()
+        bt = ident.clone()
+        bt[5] = bad_value
+        E.store(c, pool, kd, vd, stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h, block_table=bt, start_pos=0)
+        assert E.store_status() == -7 and E.store_status() == 0         # reported once, then cleared
+        want = good.data.clone()
+        want[5 * per_block:6 * per_block] = guard[5 * per_block:6 * per_block]   # the skipped block stays untouched
+        assert torch.equal(pool.data, want)
+    # paged source: a table entry past the cache reads as zeros and is reported
+    cache = torch.zeros(2, nb, 16, h, d, dtype=torch.bfloat16, device=dev)
+    cache[0].view(-1, h, d)[:n] = kd
+    cache[1].view(-1, h, d)[:n] = vd
+    src = ident.clone()
+    src[2] = nb + 1
+    pool = E.BlockPool(c, h, nb)
+    assert E.store_paged(c, pool, cache[0], cache[1], src_block_table=src, n_tokens=n, block_table=ident)
+    assert E.store_status() == -7 and E.store_status() == 0
+    k2, v2 = kd.clone(), vd.clone()
+    k2[32:48] = 0
+    v2[32:48] = 0
+    ref = E.BlockPool(c, h, nb)
+    E.store(c, ref, k2, v2, stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h, block_table=ident, start_pos=0)
+    assert torch.equal(pool.data, ref.data) and E.store_status() == 0

@@ -480,12 +480,16 @@ extern "C" int tq_prefill_attention(const void* query, const void* key, const vo
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 
-// Status left by the prefill attention kernel (0, or TQ_ERR_TIMEOUT if a bounded wait ran out).
-// Synchronises the device.
+// Status left by the prefill attention kernel since the last call (0, or TQ_ERR_TIMEOUT if a bounded wait ran
+// out); reading it clears it.  Synchronises the device.
 extern "C" int tq_prefill_attention_read_status(int32_t* out) {
     if (!out) return TQ_ERR_NULL;
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_tq_prefill_status, sizeof(int)) != cudaSuccess) return TQ_ERR_CUDA;
+    if (v != 0) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_tq_prefill_status, &zero, sizeof(int)) != cudaSuccess) return TQ_ERR_CUDA;
+    }
     *out = v;
     return TQ_OK;
 }

@@ -1384,12 +1384,16 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
     return launched == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 
-// Status left by the tensor-core store kernel (0, or a tq_status if a bounded
-// wait ran out or a block index was out of range).  Synchronises the device.
+// Status left by the tensor-core store kernels since the last call (0, or a tq_status if a bounded wait ran
+// out or a block index was out of range); reading it clears it.  Synchronises the device.
 extern "C" int tq_store_read_status(int32_t* out) {
     if (!out) return TQ_ERR_NULL;
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_tq_store_status, sizeof(int)) != cudaSuccess) return TQ_ERR_CUDA;
+    if (v != 0) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_tq_store_status, &zero, sizeof(int)) != cudaSuccess) return TQ_ERR_CUDA;
+    }
     *out = v;
     return TQ_OK;
 }
