@@ -759,11 +759,20 @@ def run_ours(args):
     clocks = sampler.stop()
 
     sharded = measure_sharded(dev, dist, rank, world) if not args.no_large else None   # every rank takes part
-    store = measure_store(dev) if rank == 0 else None
-    prefill = measure_prefill(dev) if (rank == 0 and not args.no_large) else None
-    large = measure_decode_large(dev) if (rank == 0 and not args.no_large) else None
-    paged = measure_decode_paged(dev) if (rank == 0 and not args.no_large) else None
-    base = cpu_baseline(3, 1, w["N"]) if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
+    def extra(fn, *a):
+        """A secondary measurement (rank 0 only, no collective inside): its failure is reported in its key
+        instead of taking the headline line down with it."""
+        try:
+            return fn(*a)
+        except Exception as exc:      # noqa: BLE001 - the line must still be printed
+            torch.cuda.synchronize()
+            return {"error": f"{type(exc).__name__}: {exc}"[:300]}
+
+    store = extra(measure_store, dev) if rank == 0 else None
+    prefill = extra(measure_prefill, dev) if (rank == 0 and not args.no_large) else None
+    large = extra(measure_decode_large, dev) if (rank == 0 and not args.no_large) else None
+    paged = extra(measure_decode_paged, dev) if (rank == 0 and not args.no_large) else None
+    base = extra(cpu_baseline, 3, 1, w["N"]) if (rank == 0 and world == 1 and not args.no_cpu_baseline) else None
 
     if rank == 0:
         line = {
@@ -794,7 +803,7 @@ def run_ours(args):
             "decode_large": large, "decode_paged": paged, "sharded": sharded, "prefill": prefill,
         }
         if base is not None:
-            line["cpu_baseline"] = {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
+            line["cpu_baseline"] = base if "error" in base else {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")}
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.barrier()
