@@ -1175,3 +1175,40 @@ def test_tensor_core_store_reports_bad_block_indices(d, dev):
     ref = E.BlockPool(c, h, nb)
     E.store(c, ref, k2, v2, stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h, block_table=ident, start_pos=0)
     assert torch.equal(pool.data, ref.data) and E.store_status() == 0
+
+
+def test_store_that_reads_the_ring_right_after_a_fused_append(dev):
+    """A decode call appends the new token to the ring on the device and lets the next launch begin at once;
+    a store launched right behind it with the ring itself as its input (no copy in between, as a caller
+    that flushes the ring in place does) must see the appended row: the library launches that store in
+    plain stream order.  Compared with a store of a copy taken after a synchronise."""
+    from turboquant_b200 import _engine as E
+    d, h, qh, n, cap = 128, 4, 16, 256, 64
+    c = E.LayerConstants(d, 3, 2, dev, seed=42)
+    k, v = O.synth_kv(n + cap, h, d, seed=61, dtype=torch.bfloat16)
+    pool = E.BlockPool(c, h, E.blocks_for(n))
+    bt = E.identity_block_table(pool.num_blocks, dev)
+    E.store(c, pool, k[:n].to(dev), v[:n].to(dev), stride_token=h * d, stride_head=d, n_tokens=n, n_heads=h,
+            block_table=bt, start_pos=0)
+    lens = torch.tensor([n], dtype=torch.int32, device=dev)
+    ring_k = torch.zeros(cap, h, d, dtype=torch.bfloat16, device=dev)
+    ring_v = torch.zeros_like(ring_k)
+    ring_len = torch.zeros(1, dtype=torch.int32, device=dev)
+    ws = E.Workspace(dev)
+    scratch_bt = E.identity_block_table(E.blocks_for(cap), dev)
+    for step in range(cap):
+        q = O.synth_query(1, qh, d, seed=80 + step, dtype=torch.bfloat16).to(dev)
+        nk, nv = k[n + step:n + step + 1].to(dev).contiguous(), v[n + step:n + step + 1].to(dev).contiguous()
+        E.decode(c, pool, ws, q, bt.unsqueeze(0), lens, n, ring_k=ring_k, ring_v=ring_v, ring_lens=ring_len,
+                 max_ring_len=step + 1, ring_stride_seq=0, ring_stride_token=h * d, append_k=nk, append_v=nv)
+        if step % 8 == 7:          # flush-like store of the ring as it is, right behind the decode launch
+            a = E.BlockPool(c, h, E.blocks_for(cap))
+            E.store(c, a, ring_k, ring_v, stride_token=h * d, stride_head=d, n_tokens=step + 1, n_heads=h,
+                    block_table=scratch_bt, start_pos=0)
+            torch.cuda.synchronize()
+            b = E.BlockPool(c, h, E.blocks_for(cap))
+            E.store(c, b, ring_k.clone(), ring_v.clone(), stride_token=h * d, stride_head=d, n_tokens=step + 1,
+                    n_heads=h, block_table=scratch_bt, start_pos=0)
+            assert torch.equal(a.data, b.data)
+            assert torch.equal(ring_k[:step + 1].cpu(), k[n:n + step + 1])
+    assert E.store_status() == 0 and ws.status() == 0
