@@ -182,7 +182,10 @@ int tq_prefill_attention_read_status(int32_t* out);
  * that launch is still running, and touches the pool only after it has
  * completed.  A store that follows one of the tq_decode* calls on the stream
  * (whose ring append may still be writing rows the store is about to read)
- * is launched in plain stream order.  Device-side status: tq_store_read_status. */
+ * is launched in plain stream order; likewise the first kernel of a tq_decode*
+ * call that follows one of these stores (the decode kernels fetch lengths,
+ * block tables and their first records before they wait for the launch ahead).
+ * Device-side status: tq_store_read_status. */
 int tq_store(const tq_consts* consts, const void* key, const void* value, tq_dtype dtype,
              int64_t n_tokens, int32_t n_heads, int64_t stride_token, int64_t stride_head,
              const int64_t* slot_mapping, const int32_t* block_table, int64_t start_pos,

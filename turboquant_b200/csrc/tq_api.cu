@@ -32,37 +32,36 @@ int tq_sm_count() {
 namespace {
 struct StreamNote {
     cudaStream_t st;
-    bool writes_rows;
+    int kind;
 };
 std::mutex g_note_mu;
 StreamNote g_notes[TQ_MAX_DEVICES][8];
 int g_note_count[TQ_MAX_DEVICES], g_note_next[TQ_MAX_DEVICES];
 }  // namespace
 
-void tq_note_launch(cudaStream_t st, bool writes_caller_rows) {
+void tq_note_launch(cudaStream_t st, int kind) {
     const int dev = tq_current_device();
     if (dev < 0 || dev >= TQ_MAX_DEVICES) return;
     std::lock_guard<std::mutex> lock(g_note_mu);
     for (int i = 0; i < g_note_count[dev]; ++i)
         if (g_notes[dev][i].st == st) {
-            g_notes[dev][i].writes_rows = writes_caller_rows;
+            g_notes[dev][i].kind = kind;
             return;
         }
     const int slot = g_note_next[dev];
-    g_notes[dev][slot] = StreamNote{st, writes_caller_rows};
+    g_notes[dev][slot] = StreamNote{st, kind};
     g_note_next[dev] = (slot + 1) % 8;
     if (g_note_count[dev] < 8) ++g_note_count[dev];
 }
 
-// True unless the stream's latest library launch is known not to write caller rows (a stream that was never
-// noted, or whose note was displaced, counts as unknown: plain stream order).
-bool tq_rows_may_be_in_flight(cudaStream_t st) {
+// Kind of the library's latest launch on the stream (a stream never noted, or whose note was displaced: unknown).
+int tq_last_launch(cudaStream_t st) {
     const int dev = tq_current_device();
-    if (dev < 0 || dev >= TQ_MAX_DEVICES) return true;
+    if (dev < 0 || dev >= TQ_MAX_DEVICES) return TQ_LAUNCH_UNKNOWN;
     std::lock_guard<std::mutex> lock(g_note_mu);
     for (int i = 0; i < g_note_count[dev]; ++i)
-        if (g_notes[dev][i].st == st) return g_notes[dev][i].writes_rows;
-    return true;
+        if (g_notes[dev][i].st == st) return g_notes[dev][i].kind;
+    return TQ_LAUNCH_UNKNOWN;
 }
 
 extern "C" int tq_get_layout(const tq_config* cfg, tq_layout* out) {

@@ -221,14 +221,26 @@ constexpr int TQ_MAX_DEVICES = 64;
 int tq_current_device();   // ordinal of the calling thread's current device, -1 on error
 int tq_sm_count();         // multiprocessors of the current device (148 when the query fails)
 
-// Which of the library's kernels was launched last on a stream.  The store kernels fetch their key / value
-// rows before they wait for the launch ahead of them (programmatic dependent launch); that is only safe when
-// the launches still in flight cannot be writing those rows.  The decode family is the one that can - it
-// appends the new token to the ring and lets its dependents begin at once - so a store that follows a decode
-// launch on the same stream is launched with plain stream order instead.  Kernels of other libraries between
-// two of ours never start early and only make the order stricter.
-void tq_note_launch(cudaStream_t st, bool writes_caller_rows);
-bool tq_rows_may_be_in_flight(cudaStream_t st);
+// Which of the library's kernels was launched last on a stream.  Several kernels let the launch behind them
+// begin before they have finished (programmatic dependent launch) and do part of their work before they wait
+// for the launch ahead; that is only safe when the launch still in flight cannot be writing what is read early:
+//   * the tensor-core store kernels fetch their key / value rows before the wait.  The decode family appends
+//     the new token to the ring - rows a flush then reads - so a store behind a decode launch is launched in
+//     plain stream order;
+//   * the decode family reads sequence lengths, block tables and the first pool records before the wait.
+//     The tensor-core store kernels write the pool and let their dependents begin at once, so the first
+//     kernel of a decode call behind such a store is launched in plain stream order.
+// Kernels of other libraries between two of ours never start early and only make the order stricter; a
+// stream the library has not seen counts as unknown.
+enum TqLaunchKind { TQ_LAUNCH_UNKNOWN = 0, TQ_LAUNCH_DECODE = 1, TQ_LAUNCH_STORE_EARLY = 2, TQ_LAUNCH_NEUTRAL = 3 };
+void tq_note_launch(cudaStream_t st, int kind);
+int tq_last_launch(cudaStream_t st);
+// programmatic-launch attribute count (0 or 1) for a kernel of the decode family / of the early-starting stores
+inline int tq_pdl_for_decode(cudaStream_t st) { return tq_last_launch(st) == TQ_LAUNCH_STORE_EARLY ? 0 : 1; }
+inline int tq_pdl_for_store(cudaStream_t st) {
+    const int k = tq_last_launch(st);
+    return (k == TQ_LAUNCH_STORE_EARLY || k == TQ_LAUNCH_NEUTRAL) ? 1 : 0;
+}
 
 // Largest dynamic shared-memory size a kernel has been opted in for, per device.
 // A paged bf16 cache as the source of a store call (see tq_store_paged).

@@ -322,7 +322,8 @@ int launch_qprep(const void* q, int dt, int64_t nvec, int D, const float* pi_t, 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // its matrix loads may run under the previous kernel's tail
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = tq_pdl_for_decode(st);   // behind a store that is still writing the pool: plain stream order
+    tq_note_launch(st, TQ_LAUNCH_DECODE);
     cfg.stream = st;
     cfg.blockDim = dim3(256);
     if (nvec >= 4096 && ap.new_k == nullptr && !ap.early_inputs && ((uintptr_t)q & 15) == 0) {   // throughput kernel
@@ -620,6 +621,7 @@ int launch_decode(const DecodeParams& p, int B, int block_bytes, cudaStream_t st
     if (tq_opt_in_smem(kern, smem, opt_in) != TQ_OK) return TQ_ERR_CUDA;
     dim3 grid((unsigned)nslot, (unsigned)p.H, (unsigned)B);
     kern<<<grid, DEC_THREADS, smem, st>>>(p);
+    tq_note_launch(st, TQ_LAUNCH_DECODE);
     return cudaGetLastError() == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 
@@ -688,7 +690,6 @@ static int decode_impl(const tq_consts* consts, const tq_pool* pool, const tq_de
     if (!consts->pi_t || !consts->s_t) return TQ_ERR_NULL;
     int rc = tq_check_config(&consts->cfg);
     if (rc != TQ_OK) return rc;
-    if (!validate_only) tq_note_launch((cudaStream_t)stream, true);   // the ring append writes rows a later store may read
     const int D = consts->cfg.head_dim, H = pool->num_kv_heads;
     if (a->batch <= 0 || a->num_q_heads <= 0 || H <= 0 || a->max_seq_len < 0 || a->block_table_stride < 0)
         return TQ_ERR_SHAPE;
@@ -1005,7 +1006,8 @@ extern "C" int tq_decode_host_io(const tq_consts* consts, const tq_pool* pool, c
             attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
             attr[0].val.programmaticStreamSerializationAllowed = 1;
             cfg.attrs = attr;
-            cfg.numAttrs = 1;
+            cfg.numAttrs = tq_pdl_for_decode(st);
+            tq_note_launch(st, TQ_LAUNCH_DECODE);
             if (cudaLaunchKernelEx(&cfg, tq_stage_in_kernel, (const uint4*)host_in, (uint4*)dev_in, (int)(in_bytes / 16)) !=
                 cudaSuccess)
                 return TQ_ERR_CUDA;

@@ -674,7 +674,8 @@ int launch_mma_nw(const DecodeParams& p_in, int batch, cudaStream_t st) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // start while the previous kernel drains
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = tq_pdl_for_decode(st);   // behind a store that is still writing the pool: plain stream order
+    tq_note_launch(st, TQ_LAUNCH_DECODE);
     return cudaLaunchKernelEx(&cfg, kern, p) == cudaSuccess ? TQ_OK : TQ_ERR_CUDA;
 }
 

@@ -461,7 +461,7 @@ extern "C" int tq_prefill_attention(const void* query, const void* key, const vo
     p.out_stride_head = out_stride_head;
     const dim3 grid((unsigned)p.n_tiles, (unsigned)num_q_heads);
     cudaStream_t st = (cudaStream_t)stream;
-    tq_note_launch(st, false);   // plain stream order for this launch; it writes none of a later store's rows
+    tq_note_launch(st, TQ_LAUNCH_NEUTRAL);   // plain stream order for this launch; it writes neither rows nor pool
     auto smem_of = [&](int nst, int tpr) {
         return (size_t)(1 + 2 * nst) * (D / 64) * PA_BOX + (size_t)2 * tpr * PA_TOK * sizeof(float) + 11 * sizeof(uint64_t) +
                16 + 1024;

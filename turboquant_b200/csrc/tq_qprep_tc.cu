@@ -265,7 +265,8 @@ int tq_qprep_tc_launch(const tq_consts* consts, const void* q, int dt, int64_t n
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // operand loads run under the previous kernel's tail
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = tq_pdl_for_decode(st);   // behind a store that is still writing the pool: plain stream order
+    tq_note_launch(st, TQ_LAUNCH_DECODE);
     cfg.stream = st;
     cfg.gridDim = dim3((unsigned)((nvec + QT_VEC - 1) / QT_VEC));
     cfg.blockDim = dim3(QT_THREADS);

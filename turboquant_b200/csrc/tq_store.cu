@@ -308,7 +308,7 @@ extern "C" int tq_store(const tq_consts* consts, const void* key, const void* va
     rc = tq_store_tc_launch(consts, key, value, dtype, n_tokens, n_heads, stride_token, stride_head, slot_mapping,
                             block_table, start_pos, pool, st, &handled, nullptr);
     if (rc != TQ_OK || handled) return rc;
-    tq_note_launch(st, false);
+    tq_note_launch(st, TQ_LAUNCH_NEUTRAL);
 
     StoreParams p;
     p.key = key;

@@ -303,7 +303,7 @@ __device__ __forceinline__ void issue_paged_rows(uint8_t* dst, const CUtensorMap
 
 // This launch may have started while the launch ahead of it in the stream still runs (programmatic
 // dependent launch; only when that launch is one of the library's that cannot be writing key / value
-// rows, see tq_rows_may_be_in_flight): the rows may be fetched at once, but the pool - which that launch
+// rows, see TqLaunchKind): the rows may be fetched at once, but the pool - which that launch
 // may write, and whose stream order of writes the caller relies on - is touched only after this wait.
 __device__ __forceinline__ void pool_writes_may_begin() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
@@ -1347,8 +1347,8 @@ int tq_store_tc_launch(const tq_consts* consts, const void* key, const void* val
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = attr;
-    lc.numAttrs = tq_rows_may_be_in_flight(st) ? 0 : 1;   // after a decode launch (ring append): plain stream order
-    tq_note_launch(st, false);
+    lc.numAttrs = tq_pdl_for_store(st);   // behind a decode launch (ring append): plain stream order
+    tq_note_launch(st, TQ_LAUNCH_STORE_EARLY);
     lc.stream = st;
     lc.gridDim = dim3(grid);
     lc.blockDim = dim3(TC_LAUNCH);
